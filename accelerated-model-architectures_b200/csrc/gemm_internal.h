@@ -1,0 +1,77 @@
+// Internal launcher interface shared by the grouped-GEMM translation units. Not part of the C ABI.
+#pragma once
+
+#include "common.cuh"
+
+namespace xma {
+
+// How the per-expert weight is laid out relative to the product out = A * W_e.
+//   W_NK : W_e stored [N, Kd] (reduction dimension contiguous) - forward projections,
+//          weight tensor [E, out_features, in_features] used as out = A * W_e^T.
+//   W_KN : W_e stored [Kd, N] (output dimension contiguous)   - input-gradient products
+//          dA = dOut * W_e with the same stored tensor.
+enum WeightLayout { W_NK = 0, W_KN = 1 };
+
+// What happens to the fp32 accumulator tile before it is stored.
+//   EPI_PLAIN   : out[dst(r), n] = acc
+//   EPI_SWIGLU  : N = 2I. aux[r, 0:2I] = acc (gate | up halves, rounded to the storage type),
+//                 out[r, 0:I] = up * gate * sigmoid(gate) computed from the rounded halves.
+//   EPI_DSWIGLU : N = I.  aux holds gate|up [r, 0:2I]; out[r, 0:I] = d gate, out[r, I:2I] = d up,
+//                 where acc is the gradient of the activation output.
+enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2 };
+
+struct RowsGemmArgs {
+    const void* a;             // [rows_cap, Kd] grouped (padded) rows
+    int64_t a_stride;          // elements between rows of a
+    const void* w;             // [E, N, Kd] (W_NK) or [E, Kd, N] (W_KN), dense
+    int w_layout;
+    void* out;                 // see Epilogue
+    int64_t out_stride;
+    void* aux;                 // gate|up buffer for the SwiGLU epilogues, else null
+    int64_t aux_stride;
+    const int* row_map;        // null: out row = grouped row; else out row = row_map[r], rows < 0 skipped
+    const int* tile_expert;    // [tile_cap]
+    const int* tile_prefix;    // [E+1], tile_prefix[E] = tiles in use
+    int num_experts;
+    int64_t tile_cap;
+    int64_t kd;                // reduction length
+    int64_t n;                 // output columns produced by the contraction
+    int epilogue;
+    int dtype;
+    int* device_status;
+    cudaStream_t stream;
+};
+
+struct DwGemmArgs {
+    const void* x;             // [rows_cap, M] grouped rows: dW_e[m, n] = sum_r x[r, m] * y[r, n]
+    int64_t x_stride;
+    const void* y;             // [rows_cap, N]
+    int64_t y_stride;
+    const uint32_t* counts;    // [E] rows per expert
+    const int* pad_offsets;    // [E+1] first padded row per expert
+    int64_t rows_cap;          // allocated rows of x and y
+    int num_experts;
+    int64_t m;
+    int64_t n;
+    void* dw;                  // [E, M, N] dense
+    int dtype;
+    int* device_status;
+    cudaStream_t stream;
+};
+
+int rows_gemm_simt(const RowsGemmArgs& a);
+int dw_gemm_simt(const DwGemmArgs& a);
+
+// tcgen05 / TMEM / TMA path (bf16 and fp16). `*_supported` is a host-side shape/alignment check.
+bool rows_gemm_tc_supported(const RowsGemmArgs& a);
+bool dw_gemm_tc_supported(const DwGemmArgs& a);
+int rows_gemm_tc(const RowsGemmArgs& a);
+int dw_gemm_tc(const DwGemmArgs& a);
+
+// Elementwise helpers reused by the unfused epilogues (defined in swiglu.cu).
+int swiglu_fwd_launch(const void* g, int64_t gs, const void* u, int64_t us, void* y, int64_t ys, int dtype,
+                      int64_t rows, int64_t cols, cudaStream_t st);
+int swiglu_bwd_launch(const void* g, int64_t gs, const void* u, int64_t us, const void* dy, int64_t dys, void* dg,
+                      int64_t dgs, void* du, int64_t dus, int dtype, int64_t rows, int64_t cols, cudaStream_t st);
+
+}  // namespace xma

@@ -1,0 +1,221 @@
+// Row movement kernels of the MoE hot path (pure HBM-bandwidth work, 128-bit accesses):
+//   * gather_rows   : token rows -> expert-sorted (padded) rows, optional per-row coefficient.
+//                     Replaces `group` (xma/layers/moe/triton_implementation/group_kernel.py:69-100).
+//   * combine_rows  : y[t] = sum_k w[t,k] * Ys[t*K+k]  (fp32 accumulate, one rounding). Replaces the
+//                     `bmm` combine of xma/layers/moe/triton_implementation/__init__.py:100-101 and
+//                     the `.view(T,K,H).sum(-2)` of :70.
+//   * combine_bwd   : d_router_weights[t,k] = <Ys[t*K+k], dY[t]> (same file, :130-131).
+#include "common.cuh"
+
+namespace xma {
+
+constexpr int ROW_THREADS = 256;
+
+// out[p, :] = src[row_src[p] / fan_out, :] * coeff[row_src[p]]   (zeros where row_src[p] < 0)
+template <typename T, bool HAS_COEFF>
+__global__ void __launch_bounds__(ROW_THREADS)
+gather_rows_kernel(const T* __restrict__ src, int64_t src_stride, const int* __restrict__ row_src,
+                   const T* __restrict__ coeff, int fan_out, int64_t rows, const int* __restrict__ rows_in_use,
+                   int64_t width, T* __restrict__ out, int64_t out_stride) {
+    constexpr int V = Vec16<T>::N;
+    const int64_t limit = rows_in_use ? min(rows, static_cast<int64_t>(*rows_in_use)) : rows;
+    const int64_t nvec = width / V;
+    for (int64_t p = blockIdx.x; p < limit; p += gridDim.x) {
+        const int f = row_src[p];
+        T* dst = out + p * out_stride;
+        if (f < 0) {
+            Vec16<T> z;
+#pragma unroll
+            for (int j = 0; j < V; ++j) z.v[j] = from_f32<T>(0.0f);
+            for (int64_t c = threadIdx.x; c < nvec; c += ROW_THREADS) store16(dst + c * V, z);
+            continue;
+        }
+        const T* s = src + static_cast<int64_t>(f / fan_out) * src_stride;
+        float cf = 1.0f;
+        if (HAS_COEFF) cf = to_f32(coeff[f]);
+        for (int64_t c = threadIdx.x; c < nvec; c += ROW_THREADS) {
+            Vec16<T> x = load16(s + c * V);
+            if (HAS_COEFF) {
+#pragma unroll
+                for (int j = 0; j < V; ++j) x.v[j] = from_f32<T>(to_f32(x.v[j]) * cf);
+            }
+            store16_stream(dst + c * V, x);
+        }
+    }
+}
+
+// y[t, :] = sum_k w[t,k] * ys[t*K + k, :]; w == nullptr means plain sum.
+template <typename T, bool HAS_W>
+__global__ void __launch_bounds__(ROW_THREADS)
+combine_rows_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restrict__ w, int K, int64_t tokens,
+                    int64_t width, T* __restrict__ y, int64_t y_stride) {
+    constexpr int V = Vec16<T>::N;
+    const int64_t nvec = width / V;
+    for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+        for (int64_t c = threadIdx.x; c < nvec; c += ROW_THREADS) {
+            float acc[V];
+#pragma unroll
+            for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+            for (int k = 0; k < K; ++k) {
+                const float wk = HAS_W ? to_f32(w[t * K + k]) : 1.0f;
+                Vec16<T> x = load16_stream(ys + (t * K + k) * ys_stride + c * V);
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc[j] = fmaf(wk, to_f32(x.v[j]), acc[j]);
+            }
+            Vec16<T> o;
+#pragma unroll
+            for (int j = 0; j < V; ++j) o.v[j] = from_f32<T>(acc[j]);
+            store16(y + t * y_stride + c * V, o);
+        }
+    }
+}
+
+// dw[t, k] = sum_h ys[t*K+k, h] * dy[t, h]
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+combine_bwd_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restrict__ dy, int64_t dy_stride, int K,
+                   int64_t tokens, int64_t width, T* __restrict__ dw) {
+    constexpr int V = Vec16<T>::N;
+    __shared__ float s_part[ROW_THREADS / 32];
+    const int64_t nvec = width / V;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+        for (int k = 0; k < K; ++k) {
+            float acc = 0.0f;
+            for (int64_t c = threadIdx.x; c < nvec; c += ROW_THREADS) {
+                Vec16<T> a = load16_stream(ys + (t * K + k) * ys_stride + c * V);
+                Vec16<T> b = load16(dy + t * dy_stride + c * V);
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc = fmaf(to_f32(a.v[j]), to_f32(b.v[j]), acc);
+            }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) s_part[warp] = acc;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float s = 0.0f;
+#pragma unroll
+                for (int i = 0; i < ROW_THREADS / 32; ++i) s += s_part[i];
+                dw[t * K + k] = from_f32<T>(s);
+            }
+            __syncthreads();
+        }
+    }
+}
+
+static int row_grid(int64_t rows) {
+    int64_t cap = static_cast<int64_t>(num_sms()) * 8;
+    return static_cast<int>(rows < 1 ? 1 : (rows > cap ? cap : rows));
+}
+
+template <typename T>
+static int gather_impl(const void* src, int64_t src_stride, const int* row_src, const void* coeff, int fan_out,
+                       int64_t rows, const int* rows_in_use, int64_t width, void* out, int64_t out_stride,
+                       cudaStream_t stream) {
+    constexpr int V = Vec16<T>::N;
+    if (width % V || src_stride % V || out_stride % V || !is_aligned16(src) || !is_aligned16(out))
+        return XMA_ERR_MISALIGNED;
+    const int grid = row_grid(rows);
+    if (coeff)
+        gather_rows_kernel<T, true><<<grid, ROW_THREADS, 0, stream>>>(
+            static_cast<const T*>(src), src_stride, row_src, static_cast<const T*>(coeff), fan_out, rows,
+            rows_in_use, width, static_cast<T*>(out), out_stride);
+    else
+        gather_rows_kernel<T, false><<<grid, ROW_THREADS, 0, stream>>>(
+            static_cast<const T*>(src), src_stride, row_src, nullptr, fan_out, rows, rows_in_use, width,
+            static_cast<T*>(out), out_stride);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+static int combine_impl(const void* ys, int64_t ys_stride, const void* w, int K, int64_t tokens, int64_t width,
+                        void* y, int64_t y_stride, cudaStream_t stream) {
+    constexpr int V = Vec16<T>::N;
+    if (width % V || ys_stride % V || y_stride % V || !is_aligned16(ys) || !is_aligned16(y))
+        return XMA_ERR_MISALIGNED;
+    const int grid = row_grid(tokens);
+    if (w)
+        combine_rows_kernel<T, true><<<grid, ROW_THREADS, 0, stream>>>(
+            static_cast<const T*>(ys), ys_stride, static_cast<const T*>(w), K, tokens, width, static_cast<T*>(y),
+            y_stride);
+    else
+        combine_rows_kernel<T, false><<<grid, ROW_THREADS, 0, stream>>>(
+            static_cast<const T*>(ys), ys_stride, nullptr, K, tokens, width, static_cast<T*>(y), y_stride);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+static int combine_bwd_impl(const void* ys, int64_t ys_stride, const void* dy, int64_t dy_stride, int K,
+                            int64_t tokens, int64_t width, void* dw, cudaStream_t stream) {
+    constexpr int V = Vec16<T>::N;
+    if (width % V || ys_stride % V || dy_stride % V || !is_aligned16(ys) || !is_aligned16(dy))
+        return XMA_ERR_MISALIGNED;
+    combine_bwd_kernel<T><<<row_grid(tokens), ROW_THREADS, 0, stream>>>(
+        static_cast<const T*>(ys), ys_stride, static_cast<const T*>(dy), dy_stride, K, tokens, width,
+        static_cast<T*>(dw));
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace xma
+
+extern "C" {
+
+int xma_b200_gather_rows(const void* src, int dtype, int64_t src_row_stride, const int32_t* row_src,
+                         const void* coeff, int fan_out, int64_t rows, const int32_t* rows_in_use, int64_t width,
+                         void* out, int64_t out_row_stride, cudaStream_t stream) {
+    if (rows > 0 && (!src || !row_src || !out)) return XMA_ERR_NULL_POINTER;
+    if (rows < 0 || width <= 0 || fan_out <= 0) return XMA_ERR_BAD_SHAPE;
+    if (rows == 0) return XMA_OK;
+    switch (dtype) {
+        case XMA_F32:
+            return xma::gather_impl<float>(src, src_row_stride, row_src, coeff, fan_out, rows, rows_in_use, width,
+                                           out, out_row_stride, stream);
+        case XMA_F16:
+            return xma::gather_impl<__half>(src, src_row_stride, row_src, coeff, fan_out, rows, rows_in_use, width,
+                                            out, out_row_stride, stream);
+        case XMA_BF16:
+            return xma::gather_impl<__nv_bfloat16>(src, src_row_stride, row_src, coeff, fan_out, rows, rows_in_use,
+                                                   width, out, out_row_stride, stream);
+    }
+    return XMA_ERR_BAD_DTYPE;
+}
+
+int xma_b200_combine_rows(const void* ys, int dtype, int64_t ys_row_stride, const void* weights, int top_k,
+                          int64_t tokens, int64_t width, void* y, int64_t y_row_stride, cudaStream_t stream) {
+    if (tokens > 0 && (!ys || !y)) return XMA_ERR_NULL_POINTER;
+    if (tokens < 0 || width <= 0 || top_k <= 0) return XMA_ERR_BAD_SHAPE;
+    if (tokens == 0) return XMA_OK;
+    switch (dtype) {
+        case XMA_F32:
+            return xma::combine_impl<float>(ys, ys_row_stride, weights, top_k, tokens, width, y, y_row_stride,
+                                            stream);
+        case XMA_F16:
+            return xma::combine_impl<__half>(ys, ys_row_stride, weights, top_k, tokens, width, y, y_row_stride,
+                                             stream);
+        case XMA_BF16:
+            return xma::combine_impl<__nv_bfloat16>(ys, ys_row_stride, weights, top_k, tokens, width, y,
+                                                    y_row_stride, stream);
+    }
+    return XMA_ERR_BAD_DTYPE;
+}
+
+int xma_b200_combine_bwd(const void* ys, int dtype, int64_t ys_row_stride, const void* dy, int64_t dy_row_stride,
+                         int top_k, int64_t tokens, int64_t width, void* d_weights, cudaStream_t stream) {
+    if (tokens > 0 && (!ys || !dy || !d_weights)) return XMA_ERR_NULL_POINTER;
+    if (tokens < 0 || width <= 0 || top_k <= 0) return XMA_ERR_BAD_SHAPE;
+    if (tokens == 0) return XMA_OK;
+    switch (dtype) {
+        case XMA_F32:
+            return xma::combine_bwd_impl<float>(ys, ys_row_stride, dy, dy_row_stride, top_k, tokens, width,
+                                                d_weights, stream);
+        case XMA_F16:
+            return xma::combine_bwd_impl<__half>(ys, ys_row_stride, dy, dy_row_stride, top_k, tokens, width,
+                                                 d_weights, stream);
+        case XMA_BF16:
+            return xma::combine_bwd_impl<__nv_bfloat16>(ys, ys_row_stride, dy, dy_row_stride, top_k, tokens, width,
+                                                        d_weights, stream);
+    }
+    return XMA_ERR_BAD_DTYPE;
+}
+
+}  // extern "C"

@@ -1,0 +1,671 @@
+// Routing kernels of the MoE hot path for sm_100a:
+//   * continuous_count : histogram of expert ids (xma/functional/continuous_count/__init__.py:16)
+//   * route_topk_softmax (+ backward): top-k over router logits and softmax over the k picked
+//     values (xma/layers/moe/__init__.py:182-195, 256-262)
+//   * count_sort : replaces `selected_experts.flatten().sort()` + continuous_count + cumsum
+//     (xma/layers/moe/__init__.py:210-217) by a stable counting sort: histogram -> table kernel
+//     -> one-pass scatter whose cross-tile prefix is a decoupled look-back scan.
+//
+// Integer outputs are bit-exact functions of the input: counts equal bincount, the permutation is
+// the stable ascending order (ties by flat index), top-k ties go to the lowest expert index.
+#include "common.cuh"
+
+namespace xma {
+
+// ------------------------------------------------------------------------------------------------
+// Histogram
+// ------------------------------------------------------------------------------------------------
+
+constexpr int HIST_THREADS = 512;
+constexpr int HIST_SMEM_BYTES = 48 * 1024;
+
+template <typename IdT, bool USE_SMEM>
+__device__ __forceinline__ void hist_add(IdT id, int bins, unsigned* __restrict__ my, unsigned* __restrict__ out,
+                                         bool& bad) {
+    if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(bins)) {
+        if (USE_SMEM) {
+            atomicAdd(&my[id], 1u);
+        } else {
+            atomicAdd(&out[id], 1u);
+        }
+    } else {
+        bad = true;
+    }
+}
+
+// Each CTA keeps `copies` private histograms in shared memory (one per group of warps) to spread
+// same-bin contention, streams its share of the ids with 128-bit loads, and adds its non-zero
+// partial counts to the global counters once at the end. Ids outside [0, bins) are skipped and
+// flagged in the status word.
+template <typename IdT, bool USE_SMEM>
+__global__ void __launch_bounds__(HIST_THREADS)
+histogram_kernel(const IdT* __restrict__ ids, int64_t n, int bins, int copies, unsigned* __restrict__ out,
+                 int* __restrict__ status) {
+    extern __shared__ unsigned s_hist[];
+    const int tid = threadIdx.x;
+    unsigned* my = nullptr;
+    if (USE_SMEM) {
+        for (int i = tid; i < copies * bins; i += HIST_THREADS) s_hist[i] = 0u;
+        __syncthreads();
+        my = s_hist + ((tid >> 5) % copies) * bins;
+    }
+
+    constexpr int V = 16 / sizeof(IdT);
+    bool bad = false;
+
+    // Elements in front of the first 16-byte boundary, and behind the last full packet, go one by one.
+    int64_t head = ((16 - (reinterpret_cast<uintptr_t>(ids) & 15u)) & 15u) / sizeof(IdT);
+    if (head > n) head = n;
+    const int64_t nvec = (n - head) / V;
+    const int64_t tail_start = head + nvec * V;
+
+    if (blockIdx.x == 0) {
+        for (int64_t i = tid; i < head; i += HIST_THREADS) hist_add<IdT, USE_SMEM>(ids[i], bins, my, out, bad);
+        for (int64_t i = tail_start + tid; i < n; i += HIST_THREADS)
+            hist_add<IdT, USE_SMEM>(ids[i], bins, my, out, bad);
+    }
+
+    const IdT* body = ids + head;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * HIST_THREADS;
+    int64_t v = static_cast<int64_t>(blockIdx.x) * HIST_THREADS + tid;
+    // Two packets in flight per thread.
+    for (; v + stride < nvec; v += 2 * stride) {
+        Vec16<IdT> a = load16_stream(body + v * V);
+        Vec16<IdT> b = load16_stream(body + (v + stride) * V);
+#pragma unroll
+        for (int j = 0; j < V; ++j) hist_add<IdT, USE_SMEM>(a.v[j], bins, my, out, bad);
+#pragma unroll
+        for (int j = 0; j < V; ++j) hist_add<IdT, USE_SMEM>(b.v[j], bins, my, out, bad);
+    }
+    for (; v < nvec; v += stride) {
+        Vec16<IdT> a = load16_stream(body + v * V);
+#pragma unroll
+        for (int j = 0; j < V; ++j) hist_add<IdT, USE_SMEM>(a.v[j], bins, my, out, bad);
+    }
+
+    if (USE_SMEM) {
+        __syncthreads();
+        for (int b = tid; b < bins; b += HIST_THREADS) {
+            unsigned s = 0;
+            for (int c = 0; c < copies; ++c) s += s_hist[c * bins + b];
+            if (s) atomicAdd(&out[b], s);
+        }
+    }
+    if (bad && status) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
+}
+
+template <typename IdT>
+static int launch_histogram(const IdT* ids, int64_t n, int bins, unsigned* out, int* status, cudaStream_t stream) {
+    XMA_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(unsigned) * bins, stream));
+    if (n == 0) return XMA_OK;
+    constexpr int V = 16 / sizeof(IdT);
+    int64_t want = ceil_div(n, static_cast<int64_t>(HIST_THREADS) * V * 2);
+    int64_t cap = static_cast<int64_t>(num_sms()) * 4;
+    int grid = static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+    const int warps = HIST_THREADS / 32;
+    int64_t per_copy = static_cast<int64_t>(bins) * sizeof(unsigned);
+    if (per_copy <= HIST_SMEM_BYTES) {
+        int copies = static_cast<int>(HIST_SMEM_BYTES / per_copy);
+        if (copies > warps) copies = warps;
+        size_t smem = static_cast<size_t>(copies) * per_copy;
+        histogram_kernel<IdT, true><<<grid, HIST_THREADS, smem, stream>>>(ids, n, bins, copies, out, status);
+    } else {
+        histogram_kernel<IdT, false><<<grid, HIST_THREADS, 0, stream>>>(ids, n, bins, 1, out, status);
+    }
+    return static_cast<int>(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------------
+// Table kernel: everything the later stages need from the counts, in one tiny launch.
+//   offsets_incl[e] : inclusive prefix sum (expert e owns sorted rows [offsets[e-1], offsets[e]))
+//   pad_offsets[e]  : first row of expert e in the padded grouped layout (multiples of XMA_ROW_PAD)
+//   tile_prefix[e]  : number of 128-row tiles in front of expert e; tile_prefix[E] = tiles in use
+//   tile_expert[t]  : expert that owns padded tile t
+// ------------------------------------------------------------------------------------------------
+__global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __restrict__ offsets_incl,
+                            int* __restrict__ pad_offsets, int* __restrict__ tile_prefix,
+                            int* __restrict__ tile_expert, int tile_cap, int* __restrict__ status) {
+    __shared__ int s_tiles_total;
+    if (threadIdx.x == 0) {
+        int run = 0, pad = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            int c = static_cast<int>(counts[e]);
+            run += c;
+            offsets_incl[e] = run;
+            pad_offsets[e] = pad;
+            tile_prefix[e] = tiles;
+            int t = (c + XMA_ROW_PAD - 1) / XMA_ROW_PAD;
+            tiles += t;
+            pad += t * XMA_ROW_PAD;
+        }
+        pad_offsets[E] = pad;
+        if (tiles > tile_cap) {  // cannot happen when the caller sized the tables from n and E
+            if (status) atomicOr(status, XMA_DEV_BAD_TILE);
+            tiles = tile_cap;
+        }
+        tile_prefix[E] = tiles;
+        s_tiles_total = tiles;
+    }
+    __syncthreads();
+    const int total = s_tiles_total;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int t0 = tile_prefix[e];
+        int t1 = t0 + (static_cast<int>(counts[e]) + XMA_ROW_PAD - 1) / XMA_ROW_PAD;
+        if (t1 > total) t1 = total;
+        for (int t = t0; t < t1; ++t) tile_expert[t] = e;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Stable scatter with a decoupled look-back scan
+// ------------------------------------------------------------------------------------------------
+constexpr int SORT_THREADS = 256;
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+constexpr int SORT_ITEMS = 16;
+constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 4096 ids per CTA
+constexpr int SORT_MAX_BINS = 1024;
+
+// Look-back status word: [63:62] state, [31:0] value. One 64-bit store/load moves both at once,
+// so no fence is needed between flag and payload.
+constexpr unsigned long long LB_AGGREGATE = 1ull << 62;
+constexpr unsigned long long LB_PREFIX = 2ull << 62;
+constexpr unsigned long long LB_STATE_MASK = 3ull << 62;
+constexpr unsigned LB_MAX_POLLS = 1u << 22;  // bounded wait; on expiry the status word gets the timeout bit
+
+__host__ __device__ inline size_t sort_smem_bytes(int E) {
+    // s_bin[TILE] u16, s_loc[TILE] u16, s_sbin[TILE] u16, warp_cnt[WARPS][E+1] u32,
+    // bin_start[E+1] u32, goff[E] u32, pad_goff[E] u32, scan scratch[32] u32, tile id
+    size_t b = 3 * static_cast<size_t>(SORT_TILE) * sizeof(uint16_t);
+    b += static_cast<size_t>(SORT_WARPS) * (E + 1) * sizeof(unsigned);
+    b += static_cast<size_t>(E + 1) * sizeof(unsigned);
+    b += 2 * static_cast<size_t>(E) * sizeof(unsigned);
+    b += 40 * sizeof(unsigned);
+    return (b + 15) & ~static_cast<size_t>(15);
+}
+
+__host__ __device__ inline size_t sort_scratch_bytes(int64_t n, int E) {
+    int64_t tiles = (n + SORT_TILE - 1) / SORT_TILE;
+    if (tiles < 1) tiles = 1;
+    return 256 + static_cast<size_t>(tiles) * E * sizeof(unsigned long long);
+}
+
+// The scratch area starts with the dynamic tile counter (256 bytes reserved), followed by
+// status[tile][bin]. The whole area must be zero when the kernel starts.
+template <typename IdT>
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __restrict__ offsets_incl,
+                    const int* __restrict__ pad_offsets, int* __restrict__ sorted_expert,
+                    int* __restrict__ sorted_scattered, int* __restrict__ row_src,
+                    unsigned char* __restrict__ scratch, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    uint16_t* s_bin = reinterpret_cast<uint16_t*>(s_raw);
+    uint16_t* s_loc = s_bin + SORT_TILE;
+    uint16_t* s_sbin = s_loc + SORT_TILE;
+    unsigned* s_warp_cnt = reinterpret_cast<unsigned*>(s_sbin + SORT_TILE);  // [WARPS][E+1]
+    unsigned* s_bin_start = s_warp_cnt + SORT_WARPS * (E + 1);               // [E+1]
+    unsigned* s_goff = s_bin_start + (E + 1);                                // [E]
+    unsigned* s_pad_goff = s_goff + E;                                       // [E]
+    unsigned* s_scan = s_pad_goff + E;                                       // [32] + tile id at [32]
+
+    unsigned* tile_counter = reinterpret_cast<unsigned*>(scratch);
+    unsigned long long* lb = reinterpret_cast<unsigned long long*>(scratch + 256);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int EB = E + 1;  // bin E collects ids that are out of range (dropped)
+
+    if (tid == 0) s_scan[32] = atomicAdd(tile_counter, 1u);
+    for (int i = tid; i < SORT_WARPS * EB; i += SORT_THREADS) s_warp_cnt[i] = 0u;
+    __syncthreads();
+    const unsigned tile = s_scan[32];
+    const int64_t base = static_cast<int64_t>(tile) * SORT_TILE;
+    if (base >= n) return;  // uniform for the CTA
+    const int cnt = static_cast<int>((n - base) < SORT_TILE ? (n - base) : SORT_TILE);
+
+    // 1. stage the tile's bins in shared memory (coalesced, SORT_ITEMS independent loads per thread)
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < SORT_ITEMS; ++j) {
+        int i = j * SORT_THREADS + tid;
+        uint16_t b = static_cast<uint16_t>(E);
+        if (i < cnt) {
+            IdT id = __ldcs(ids + base + i);
+            if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(E)) {
+                b = static_cast<uint16_t>(id);
+            } else {
+                bad = true;
+            }
+        }
+        s_bin[i] = b;
+    }
+    __syncthreads();
+
+    // 2. each warp ranks its contiguous 512 ids row by row; equal bins inside a row are ordered
+    //    by lane, rows are processed in order, so the rank is stable.
+    uint16_t my_bin[SORT_ITEMS];
+    uint16_t my_rank[SORT_ITEMS];
+    unsigned* wc = s_warp_cnt + warp * EB;
+    const unsigned lt_mask = (1u << lane) - 1u;
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; ++r) {
+        const int i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
+        const unsigned b = s_bin[i];
+        const unsigned peers = __match_any_sync(0xffffffffu, b);
+        const unsigned before = wc[b];
+        __syncwarp();
+        if ((peers & lt_mask) == 0u) wc[b] = before + __popc(peers);
+        __syncwarp();
+        my_bin[r] = static_cast<uint16_t>(b);
+        my_rank[r] = static_cast<uint16_t>(before + __popc(peers & lt_mask));
+    }
+    __syncthreads();
+
+    // 3. per bin: exclusive scan over warps, publish the tile aggregate, look back for the prefix
+    for (int b = tid; b < E; b += SORT_THREADS) {
+        unsigned run = 0;
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; ++w) {
+            unsigned t = s_warp_cnt[w * EB + b];
+            s_warp_cnt[w * EB + b] = run;
+            run += t;
+        }
+        s_bin_start[b] = run;  // tile count for now, scanned below
+
+        unsigned long long* mine = lb + static_cast<size_t>(tile) * E + b;
+        unsigned excl = 0;
+        if (tile == 0) {
+            atomicExch(mine, LB_PREFIX | run);
+        } else {
+            atomicExch(mine, LB_AGGREGATE | run);
+            int64_t prev = static_cast<int64_t>(tile) - 1;
+            unsigned polls = 0;
+            bool gave_up = false;
+            while (true) {
+                unsigned long long v =
+                    *reinterpret_cast<volatile unsigned long long*>(lb + static_cast<size_t>(prev) * E + b);
+                unsigned long long st = v & LB_STATE_MASK;
+                if (st == 0ull) {
+                    if (++polls > LB_MAX_POLLS) {
+                        gave_up = true;
+                        break;
+                    }
+                    __nanosleep(32);
+                    continue;
+                }
+                excl += static_cast<unsigned>(v & 0xffffffffull);
+                if (st == LB_PREFIX) break;
+                --prev;  // an aggregate: keep walking (tile 0 always publishes a prefix)
+            }
+            if (gave_up) {
+                if (status) atomicOr(status, XMA_DEV_WAIT_TIMEOUT);
+                excl = 0;
+            }
+            atomicExch(mine, LB_PREFIX | static_cast<unsigned long long>(excl + run));
+        }
+        const unsigned gbase = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
+        s_goff[b] = gbase + excl;
+        s_pad_goff[b] = static_cast<unsigned>(pad_offsets[b]) + excl;
+    }
+    __syncthreads();
+
+    // 4. exclusive scan of the tile's bin counts -> start of each bin inside the tile
+    {
+        constexpr int PER = SORT_MAX_BINS / SORT_THREADS;  // 4 bins per thread
+        unsigned v[PER];
+        unsigned sum = 0;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            int b = tid * PER + j;
+            v[j] = (b < E) ? s_bin_start[b] : 0u;
+            sum += v[j];
+        }
+        unsigned incl = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) s_scan[warp] = incl;
+        __syncthreads();
+        unsigned warp_base = 0;
+        for (int w = 0; w < warp; ++w) warp_base += s_scan[w];
+        unsigned run = warp_base + incl - sum;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            int b = tid * PER + j;
+            if (b < E) s_bin_start[b] = run;
+            run += v[j];
+            if (b == E - 1) s_bin_start[E] = run;  // number of in-range ids in the tile
+        }
+    }
+    __syncthreads();
+
+    // 5. local stable sort into shared memory
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; ++r) {
+        const unsigned b = my_bin[r];
+        if (b < static_cast<unsigned>(E)) {
+            const int i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
+            const unsigned lp = s_bin_start[b] + s_warp_cnt[warp * EB + b] + my_rank[r];
+            s_loc[lp] = static_cast<uint16_t>(i);
+            s_sbin[lp] = static_cast<uint16_t>(b);
+        }
+    }
+    __syncthreads();
+
+    // 6. write runs of equal bins to their global positions (consecutive threads, consecutive
+    //    addresses inside a run)
+    const int valid = static_cast<int>(s_bin_start[E]);
+    for (int j = tid; j < valid; j += SORT_THREADS) {
+        const unsigned b = s_sbin[j];
+        const unsigned off = static_cast<unsigned>(j) - s_bin_start[b];
+        const int f = static_cast<int>(base + s_loc[j]);
+        const unsigned g = s_goff[b] + off;
+        sorted_scattered[g] = f;
+        sorted_expert[g] = static_cast<int>(b);
+        if (row_src) row_src[s_pad_goff[b] + off] = f;
+    }
+    if (bad && status) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
+}
+
+// ------------------------------------------------------------------------------------------------
+// top-k + softmax over the k selected logits
+// ------------------------------------------------------------------------------------------------
+
+// Total order used for the selection: NaN above everything (as torch.topk), then larger value,
+// then lower expert index.
+__device__ __forceinline__ bool cand_better(float a, int ai, float b, int bi) {
+    const bool an = (a != a), bn = (b != b);
+    if (an != bn) return an;
+    if (!an && a != b) return a > b;
+    return ai < bi;
+}
+
+constexpr int TOPK_WARPS = 8;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(TOPK_WARPS * 32)
+topk_softmax_kernel(const T* __restrict__ logits, int64_t logits_stride, int64_t tokens, int E, int K,
+                    T* __restrict__ weights, int* __restrict__ selected32, long long* __restrict__ selected64) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * TOPK_WARPS + (threadIdx.x >> 5);
+    if (row >= tokens) return;
+    const T* src = logits + row * logits_stride;
+
+    float v[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        int e = j * 32 + lane;
+        v[j] = (e < E) ? to_f32(src[e]) : 0.0f;
+    }
+    unsigned taken = 0u;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (j * 32 + lane >= E) taken |= (1u << j);
+
+    float sel_v = 0.0f;
+    int sel_i = 0;
+    for (int k = 0; k < K; ++k) {
+        float bv = 0.0f;
+        int bi = 0x7fffffff;  // "no candidate"
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            if (!((taken >> j) & 1u)) {
+                int e = j * 32 + lane;
+                if (bi == 0x7fffffff || cand_better(v[j], e, bv, bi)) {
+                    bv = v[j];
+                    bi = e;
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || cand_better(ov, oi, bv, bi))) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if ((bi & 31) == lane) taken |= (1u << (bi >> 5));
+        if (lane == k) {
+            sel_v = bv;
+            sel_i = bi;
+        }
+    }
+
+    // softmax over the K selected values, fp32
+    const float vmax = __shfl_sync(0xffffffffu, sel_v, 0);
+    float p = (lane < K) ? expf(sel_v - vmax) : 0.0f;
+    float s = p;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane < K) {
+        weights[row * K + lane] = from_f32<T>(p / s);
+        if (selected32) selected32[row * K + lane] = sel_i;
+        if (selected64) selected64[row * K + lane] = sel_i;
+    }
+}
+
+// d_logits[t, e] = w_k (dw_k - sum_j w_j dw_j) where e is the k-th selected expert of token t, else 0.
+// w is recomputed in fp32 from the logits exactly as the forward did.
+template <typename T, int NV>
+__global__ void __launch_bounds__(TOPK_WARPS * 32)
+topk_softmax_bwd_kernel(const T* __restrict__ logits, int64_t logits_stride, const int* __restrict__ selected,
+                        const T* __restrict__ d_weights, int64_t tokens, int E, int K, T* __restrict__ d_logits) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * TOPK_WARPS + (threadIdx.x >> 5);
+    if (row >= tokens) return;
+
+    int sel = -1;
+    float val = 0.0f, dw = 0.0f;
+    if (lane < K) {
+        sel = selected[row * K + lane];
+        val = to_f32(logits[row * logits_stride + sel]);
+        dw = to_f32(d_weights[row * K + lane]);
+    }
+    const float vmax = __shfl_sync(0xffffffffu, val, 0);
+    float p = (lane < K) ? expf(val - vmax) : 0.0f;
+    float s = p;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float w = p / s;
+    float dot = w * dw;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float dv = w * (dw - dot);
+
+    float out[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) out[j] = 0.0f;
+    for (int k = 0; k < K; ++k) {
+        const int sk = __shfl_sync(0xffffffffu, sel, k);
+        const float gk = __shfl_sync(0xffffffffu, dv, k);
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+            if (sk == j * 32 + lane) out[j] = gk;
+    }
+    T* dst = d_logits + row * static_cast<int64_t>(E);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        int e = j * 32 + lane;
+        if (e < E) dst[e] = from_f32<T>(out[j]);
+    }
+}
+
+template <typename T>
+static int launch_topk(const void* logits, int64_t stride, int64_t tokens, int E, int K, void* weights, int* sel32,
+                       long long* sel64, cudaStream_t stream) {
+    if (tokens == 0) return XMA_OK;
+    const int64_t grid64 = ceil_div(tokens, TOPK_WARPS);
+    if (grid64 > 0x7fffffff) return XMA_ERR_TOO_LARGE;
+    const int grid = static_cast<int>(grid64);
+    const T* l = static_cast<const T*>(logits);
+    T* w = static_cast<T*>(weights);
+#define XMA_TOPK_CASE(NV)                                                                                   \
+    topk_softmax_kernel<T, NV><<<grid, TOPK_WARPS * 32, 0, stream>>>(l, stride, tokens, E, K, w, sel32, sel64)
+    if (E <= 32) XMA_TOPK_CASE(1);
+    else if (E <= 64) XMA_TOPK_CASE(2);
+    else if (E <= 128) XMA_TOPK_CASE(4);
+    else if (E <= 256) XMA_TOPK_CASE(8);
+    else if (E <= 512) XMA_TOPK_CASE(16);
+    else XMA_TOPK_CASE(32);
+#undef XMA_TOPK_CASE
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+static int launch_topk_bwd(const void* logits, int64_t stride, const int* selected, const void* d_weights,
+                           int64_t tokens, int E, int K, void* d_logits, cudaStream_t stream) {
+    if (tokens == 0) return XMA_OK;
+    const int64_t grid64 = ceil_div(tokens, TOPK_WARPS);
+    if (grid64 > 0x7fffffff) return XMA_ERR_TOO_LARGE;
+    const int grid = static_cast<int>(grid64);
+    const T* l = static_cast<const T*>(logits);
+    const T* dw = static_cast<const T*>(d_weights);
+    T* dl = static_cast<T*>(d_logits);
+#define XMA_TOPKB_CASE(NV)                                                                                    \
+    topk_softmax_bwd_kernel<T, NV><<<grid, TOPK_WARPS * 32, 0, stream>>>(l, stride, selected, dw, tokens, E, K, dl)
+    if (E <= 32) XMA_TOPKB_CASE(1);
+    else if (E <= 64) XMA_TOPKB_CASE(2);
+    else if (E <= 128) XMA_TOPKB_CASE(4);
+    else if (E <= 256) XMA_TOPKB_CASE(8);
+    else if (E <= 512) XMA_TOPKB_CASE(16);
+    else XMA_TOPKB_CASE(32);
+#undef XMA_TOPKB_CASE
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace xma
+
+namespace {
+template <typename IdT>
+int count_sort_impl(const IdT* ids, int64_t n, int E, uint32_t* counts, int* offsets_incl, int* pad_offsets,
+                    int* tile_prefix, int* tile_expert, int64_t tile_cap, int* sorted_expert, int* sorted_scattered,
+                    int* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes, int* device_status,
+                    cudaStream_t stream) {
+    int rc = xma::launch_histogram(ids, n, E, counts, device_status, stream);
+    if (rc) return rc;
+    xma::plan_kernel<<<1, 256, 0, stream>>>(counts, E, offsets_incl, pad_offsets, tile_prefix, tile_expert,
+                                            static_cast<int>(tile_cap), device_status);
+    XMA_CUDA_TRY(cudaGetLastError());
+    if (row_src) XMA_CUDA_TRY(cudaMemsetAsync(row_src, 0xff, sizeof(int) * row_cap, stream));
+    if (n == 0) return XMA_OK;
+    const size_t need = xma::sort_scratch_bytes(n, E);
+    XMA_CUDA_TRY(cudaMemsetAsync(scratch, 0, need, stream));
+    const size_t smem = xma::sort_smem_bytes(E);
+    auto kernel = xma::sort_scatter_kernel<IdT>;
+    if (smem > 48 * 1024) {
+        XMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    }
+    const int64_t tiles = xma::ceil_div(n, xma::SORT_TILE);
+    kernel<<<static_cast<int>(tiles), xma::SORT_THREADS, smem, stream>>>(
+        ids, n, E, offsets_incl, pad_offsets, sorted_expert, sorted_scattered, row_src,
+        static_cast<unsigned char*>(scratch), device_status);
+    (void)scratch_bytes;
+    return static_cast<int>(cudaGetLastError());
+}
+}  // namespace
+
+// ================================================================================================
+// C ABI
+// ================================================================================================
+extern "C" {
+
+int xma_b200_continuous_count(const void* ids, int id_dtype, int64_t n, int bins, uint32_t* counts,
+                              int* device_status, cudaStream_t stream) {
+    if (!counts || (n > 0 && !ids)) return XMA_ERR_NULL_POINTER;
+    if (n < 0 || bins <= 0) return XMA_ERR_BAD_SHAPE;
+    if (id_dtype == XMA_I32) {
+        if (reinterpret_cast<uintptr_t>(ids) & 3u) return XMA_ERR_MISALIGNED;
+        return xma::launch_histogram(static_cast<const int*>(ids), n, bins, counts, device_status, stream);
+    }
+    if (id_dtype == XMA_I64) {
+        if (reinterpret_cast<uintptr_t>(ids) & 7u) return XMA_ERR_MISALIGNED;
+        return xma::launch_histogram(static_cast<const long long*>(ids), n, bins, counts, device_status, stream);
+    }
+    return XMA_ERR_BAD_DTYPE;
+}
+
+int64_t xma_b200_count_sort_scratch_bytes(int64_t n, int num_experts) {
+    if (n < 0 || num_experts <= 0 || num_experts > xma::SORT_MAX_BINS) return XMA_ERR_BAD_SHAPE;
+    return static_cast<int64_t>(xma::sort_scratch_bytes(n, num_experts));
+}
+
+int64_t xma_b200_tile_capacity(int64_t n, int num_experts) {
+    if (n < 0 || num_experts <= 0) return XMA_ERR_BAD_SHAPE;
+    return n / XMA_ROW_PAD + num_experts;
+}
+
+
+int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_experts, uint32_t* counts,
+                        int32_t* offsets_incl, int32_t* pad_offsets, int32_t* tile_prefix, int32_t* tile_expert,
+                        int64_t tile_cap, int32_t* sorted_expert_idxs, int32_t* sorted_scattered_idxs,
+                        int32_t* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes, int* device_status,
+                        cudaStream_t stream) {
+    if (!counts || !offsets_incl || !pad_offsets || !tile_prefix || !tile_expert || !sorted_expert_idxs ||
+        !sorted_scattered_idxs || !scratch || (n > 0 && !ids))
+        return XMA_ERR_NULL_POINTER;
+    if (n < 0 || num_experts <= 0 || num_experts > xma::SORT_MAX_BINS) return XMA_ERR_BAD_SHAPE;
+    if (n > 0x7fffffffLL - xma::SORT_TILE) return XMA_ERR_TOO_LARGE;
+    if (tile_cap < n / XMA_ROW_PAD + num_experts) return XMA_ERR_BAD_SHAPE;
+    if (row_src && row_cap < tile_cap * XMA_ROW_PAD) return XMA_ERR_BAD_SHAPE;
+    if (scratch_bytes < static_cast<int64_t>(xma::sort_scratch_bytes(n, num_experts))) return XMA_ERR_SCRATCH_TOO_SMALL;
+    if (reinterpret_cast<uintptr_t>(scratch) & 255u) return XMA_ERR_MISALIGNED;
+    if (id_dtype == XMA_I32)
+        return count_sort_impl(static_cast<const int*>(ids), n, num_experts, counts, offsets_incl, pad_offsets,
+                               tile_prefix, tile_expert, tile_cap, sorted_expert_idxs, sorted_scattered_idxs,
+                               row_src, row_cap, scratch, scratch_bytes, device_status, stream);
+    if (id_dtype == XMA_I64)
+        return count_sort_impl(static_cast<const long long*>(ids), n, num_experts, counts, offsets_incl,
+                               pad_offsets, tile_prefix, tile_expert, tile_cap, sorted_expert_idxs,
+                               sorted_scattered_idxs, row_src, row_cap, scratch, scratch_bytes, device_status,
+                               stream);
+    return XMA_ERR_BAD_DTYPE;
+}
+
+int xma_b200_route_topk_softmax(const void* logits, int dtype, int64_t logits_row_stride, int64_t tokens,
+                                int num_experts, int top_k, void* weights, int32_t* selected_i32,
+                                int64_t* selected_i64, cudaStream_t stream) {
+    if (tokens > 0 && (!logits || !weights || (!selected_i32 && !selected_i64))) return XMA_ERR_NULL_POINTER;
+    if (tokens < 0 || num_experts <= 0 || num_experts > 1024 || top_k <= 0 || top_k > 32 || top_k > num_experts ||
+        logits_row_stride < num_experts)
+        return XMA_ERR_BAD_SHAPE;
+    long long* s64 = reinterpret_cast<long long*>(selected_i64);
+    switch (dtype) {
+        case XMA_F32:
+            return xma::launch_topk<float>(logits, logits_row_stride, tokens, num_experts, top_k, weights,
+                                           selected_i32, s64, stream);
+        case XMA_F16:
+            return xma::launch_topk<__half>(logits, logits_row_stride, tokens, num_experts, top_k, weights,
+                                            selected_i32, s64, stream);
+        case XMA_BF16:
+            return xma::launch_topk<__nv_bfloat16>(logits, logits_row_stride, tokens, num_experts, top_k, weights,
+                                                   selected_i32, s64, stream);
+    }
+    return XMA_ERR_BAD_DTYPE;
+}
+
+int xma_b200_route_topk_softmax_bwd(const void* logits, int dtype, int64_t logits_row_stride,
+                                    const int32_t* selected_i32, const void* d_weights, int64_t tokens,
+                                    int num_experts, int top_k, void* d_logits, cudaStream_t stream) {
+    if (tokens > 0 && (!logits || !selected_i32 || !d_weights || !d_logits)) return XMA_ERR_NULL_POINTER;
+    if (tokens < 0 || num_experts <= 0 || num_experts > 1024 || top_k <= 0 || top_k > 32 || top_k > num_experts ||
+        logits_row_stride < num_experts)
+        return XMA_ERR_BAD_SHAPE;
+    switch (dtype) {
+        case XMA_F32:
+            return xma::launch_topk_bwd<float>(logits, logits_row_stride, selected_i32, d_weights, tokens,
+                                               num_experts, top_k, d_logits, stream);
+        case XMA_F16:
+            return xma::launch_topk_bwd<__half>(logits, logits_row_stride, selected_i32, d_weights, tokens,
+                                                num_experts, top_k, d_logits, stream);
+        case XMA_BF16:
+            return xma::launch_topk_bwd<__nv_bfloat16>(logits, logits_row_stride, selected_i32, d_weights, tokens,
+                                                       num_experts, top_k, d_logits, stream);
+    }
+    return XMA_ERR_BAD_DTYPE;
+}
+
+}  // extern "C"

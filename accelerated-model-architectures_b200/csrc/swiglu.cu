@@ -1,0 +1,290 @@
+// Stand-alone SwiGLU kernels behind xma.functional.swiglu / swiglu_packed
+// (xma/functional/swiglu/__init__.py:39-87; math as in swiglu/torch_implementation.py:9-30):
+//   y  = up * gate * sigmoid(gate)                       computed in fp32, rounded once
+//   dg = dy * up * sigmoid(gate) * (1 + gate * (1 - sigmoid(gate)))
+//   du = dy * gate * sigmoid(gate)
+// The packed form reads gate/up interleaved along the last dimension (g,u,g,u,...).
+// Inputs may be row-strided views (e.g. the two halves of `chunk(2, -1)`), so no copy is needed.
+// HBM-bound: 128-bit accesses whenever widths, strides and base addresses allow, scalar otherwise.
+#include "gemm_internal.h"
+
+#include <initializer_list>
+
+namespace xma {
+
+constexpr int EW_THREADS = 256;
+
+__device__ __forceinline__ float swiglu_f(float g, float u) { return u * g * sigmoid_f32(g); }
+
+__device__ __forceinline__ void swiglu_b(float g, float u, float dy, float& dg, float& du) {
+    const float s = sigmoid_f32(g);
+    dg = dy * u * s * (1.0f + g * (1.0f - s));
+    du = dy * g * s;
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS)
+swiglu_fwd_kernel(const T* __restrict__ g, int64_t g_stride, const T* __restrict__ u, int64_t u_stride,
+                  T* __restrict__ y, int64_t y_stride, int64_t rows, int64_t cols) {
+    constexpr int V = VEC ? Vec16<T>::N : 1;
+    const int64_t cv = cols / V;
+    const int64_t total = rows * cv;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total; i += step) {
+        const int64_t r = i / cv, c = (i - r * cv) * V;
+        if (VEC) {
+            Vec16<T> a = load16_stream(g + r * g_stride + c);
+            Vec16<T> b = load16_stream(u + r * u_stride + c);
+            Vec16<T> o;
+#pragma unroll
+            for (int j = 0; j < Vec16<T>::N; ++j) o.v[j] = from_f32<T>(swiglu_f(to_f32(a.v[j]), to_f32(b.v[j])));
+            store16_stream(y + r * y_stride + c, o);
+        } else {
+            y[r * y_stride + c] = from_f32<T>(swiglu_f(to_f32(g[r * g_stride + c]), to_f32(u[r * u_stride + c])));
+        }
+    }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS)
+swiglu_bwd_kernel(const T* __restrict__ g, int64_t g_stride, const T* __restrict__ u, int64_t u_stride,
+                  const T* __restrict__ dy, int64_t dy_stride, T* __restrict__ dg, int64_t dg_stride,
+                  T* __restrict__ du, int64_t du_stride, int64_t rows, int64_t cols) {
+    constexpr int V = VEC ? Vec16<T>::N : 1;
+    const int64_t cv = cols / V;
+    const int64_t total = rows * cv;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total; i += step) {
+        const int64_t r = i / cv, c = (i - r * cv) * V;
+        if (VEC) {
+            Vec16<T> a = load16_stream(g + r * g_stride + c);
+            Vec16<T> b = load16_stream(u + r * u_stride + c);
+            Vec16<T> d = load16_stream(dy + r * dy_stride + c);
+            Vec16<T> og, ou;
+#pragma unroll
+            for (int j = 0; j < Vec16<T>::N; ++j) {
+                float x, z;
+                swiglu_b(to_f32(a.v[j]), to_f32(b.v[j]), to_f32(d.v[j]), x, z);
+                og.v[j] = from_f32<T>(x);
+                ou.v[j] = from_f32<T>(z);
+            }
+            store16_stream(dg + r * dg_stride + c, og);
+            store16_stream(du + r * du_stride + c, ou);
+        } else {
+            float x, z;
+            swiglu_b(to_f32(g[r * g_stride + c]), to_f32(u[r * u_stride + c]), to_f32(dy[r * dy_stride + c]), x, z);
+            dg[r * dg_stride + c] = from_f32<T>(x);
+            du[r * du_stride + c] = from_f32<T>(z);
+        }
+    }
+}
+
+// Packed: x[r, 2c] = gate, x[r, 2c+1] = up; y[r, c]. `cols` is the width of y.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS)
+swiglu_packed_fwd_kernel(const T* __restrict__ x, int64_t x_stride, T* __restrict__ y, int64_t y_stride,
+                         int64_t rows, int64_t cols) {
+    constexpr int V = VEC ? Vec16<T>::N : 1;  // outputs per thread step
+    const int64_t cv = cols / V;
+    const int64_t total = rows * cv;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total; i += step) {
+        const int64_t r = i / cv, c = (i - r * cv) * V;
+        if (VEC) {
+            Vec16<T> a = load16_stream(x + r * x_stride + 2 * c);
+            Vec16<T> b = load16_stream(x + r * x_stride + 2 * c + Vec16<T>::N);
+            Vec16<T> o;
+#pragma unroll
+            for (int j = 0; j < Vec16<T>::N / 2; ++j) {
+                o.v[j] = from_f32<T>(swiglu_f(to_f32(a.v[2 * j]), to_f32(a.v[2 * j + 1])));
+                o.v[j + Vec16<T>::N / 2] = from_f32<T>(swiglu_f(to_f32(b.v[2 * j]), to_f32(b.v[2 * j + 1])));
+            }
+            store16_stream(y + r * y_stride + c, o);
+        } else {
+            y[r * y_stride + c] =
+                from_f32<T>(swiglu_f(to_f32(x[r * x_stride + 2 * c]), to_f32(x[r * x_stride + 2 * c + 1])));
+        }
+    }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS)
+swiglu_packed_bwd_kernel(const T* __restrict__ x, int64_t x_stride, const T* __restrict__ dy, int64_t dy_stride,
+                         T* __restrict__ dx, int64_t dx_stride, int64_t rows, int64_t cols) {
+    constexpr int V = VEC ? Vec16<T>::N : 1;
+    const int64_t cv = cols / V;
+    const int64_t total = rows * cv;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total; i += step) {
+        const int64_t r = i / cv, c = (i - r * cv) * V;
+        if (VEC) {
+            Vec16<T> a = load16_stream(x + r * x_stride + 2 * c);
+            Vec16<T> b = load16_stream(x + r * x_stride + 2 * c + Vec16<T>::N);
+            Vec16<T> d = load16_stream(dy + r * dy_stride + c);
+            Vec16<T> oa, ob;
+#pragma unroll
+            for (int j = 0; j < Vec16<T>::N / 2; ++j) {
+                float p, q;
+                swiglu_b(to_f32(a.v[2 * j]), to_f32(a.v[2 * j + 1]), to_f32(d.v[j]), p, q);
+                oa.v[2 * j] = from_f32<T>(p);
+                oa.v[2 * j + 1] = from_f32<T>(q);
+                swiglu_b(to_f32(b.v[2 * j]), to_f32(b.v[2 * j + 1]), to_f32(d.v[j + Vec16<T>::N / 2]), p, q);
+                ob.v[2 * j] = from_f32<T>(p);
+                ob.v[2 * j + 1] = from_f32<T>(q);
+            }
+            store16_stream(dx + r * dx_stride + 2 * c, oa);
+            store16_stream(dx + r * dx_stride + 2 * c + Vec16<T>::N, ob);
+        } else {
+            float p, q;
+            swiglu_b(to_f32(x[r * x_stride + 2 * c]), to_f32(x[r * x_stride + 2 * c + 1]),
+                     to_f32(dy[r * dy_stride + c]), p, q);
+            dx[r * dx_stride + 2 * c] = from_f32<T>(p);
+            dx[r * dx_stride + 2 * c + 1] = from_f32<T>(q);
+        }
+    }
+}
+
+static int ew_grid(int64_t work_items) {
+    int64_t want = ceil_div(work_items, EW_THREADS);
+    int64_t cap = static_cast<int64_t>(num_sms()) * 16;
+    return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+template <typename T>
+static bool vec_ok(int64_t cols, std::initializer_list<int64_t> strides, std::initializer_list<const void*> ptrs) {
+    constexpr int V = Vec16<T>::N;
+    if (cols % V) return false;
+    for (int64_t s : strides)
+        if (s % V) return false;
+    for (const void* p : ptrs)
+        if (!is_aligned16(p)) return false;
+    return true;
+}
+
+template <typename T>
+static int swiglu_fwd_impl(const void* g, int64_t gs, const void* u, int64_t us, void* y, int64_t ys, int64_t rows,
+                           int64_t cols, cudaStream_t st) {
+    const T* gp = static_cast<const T*>(g);
+    const T* up = static_cast<const T*>(u);
+    T* yp = static_cast<T*>(y);
+    if (vec_ok<T>(cols, {gs, us, ys}, {g, u, y}))
+        swiglu_fwd_kernel<T, true><<<ew_grid(rows * cols / Vec16<T>::N), EW_THREADS, 0, st>>>(gp, gs, up, us, yp, ys,
+                                                                                               rows, cols);
+    else
+        swiglu_fwd_kernel<T, false><<<ew_grid(rows * cols), EW_THREADS, 0, st>>>(gp, gs, up, us, yp, ys, rows, cols);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+static int swiglu_bwd_impl(const void* g, int64_t gs, const void* u, int64_t us, const void* dy, int64_t dys,
+                           void* dg, int64_t dgs, void* du, int64_t dus, int64_t rows, int64_t cols,
+                           cudaStream_t st) {
+    const T* gp = static_cast<const T*>(g);
+    const T* up = static_cast<const T*>(u);
+    const T* dyp = static_cast<const T*>(dy);
+    T* dgp = static_cast<T*>(dg);
+    T* dup = static_cast<T*>(du);
+    if (vec_ok<T>(cols, {gs, us, dys, dgs, dus}, {g, u, dy, dg, du}))
+        swiglu_bwd_kernel<T, true><<<ew_grid(rows * cols / Vec16<T>::N), EW_THREADS, 0, st>>>(
+            gp, gs, up, us, dyp, dys, dgp, dgs, dup, dus, rows, cols);
+    else
+        swiglu_bwd_kernel<T, false><<<ew_grid(rows * cols), EW_THREADS, 0, st>>>(gp, gs, up, us, dyp, dys, dgp, dgs,
+                                                                                 dup, dus, rows, cols);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+static int swiglu_packed_fwd_impl(const void* x, int64_t xs, void* y, int64_t ys, int64_t rows, int64_t cols,
+                                  cudaStream_t st) {
+    const T* xp = static_cast<const T*>(x);
+    T* yp = static_cast<T*>(y);
+    if (vec_ok<T>(cols, {xs, ys}, {x, y}))
+        swiglu_packed_fwd_kernel<T, true><<<ew_grid(rows * cols / Vec16<T>::N), EW_THREADS, 0, st>>>(xp, xs, yp, ys,
+                                                                                                      rows, cols);
+    else
+        swiglu_packed_fwd_kernel<T, false><<<ew_grid(rows * cols), EW_THREADS, 0, st>>>(xp, xs, yp, ys, rows, cols);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+static int swiglu_packed_bwd_impl(const void* x, int64_t xs, const void* dy, int64_t dys, void* dx, int64_t dxs,
+                                  int64_t rows, int64_t cols, cudaStream_t st) {
+    const T* xp = static_cast<const T*>(x);
+    const T* dyp = static_cast<const T*>(dy);
+    T* dxp = static_cast<T*>(dx);
+    if (vec_ok<T>(cols, {xs, dys, dxs}, {x, dy, dx}))
+        swiglu_packed_bwd_kernel<T, true><<<ew_grid(rows * cols / Vec16<T>::N), EW_THREADS, 0, st>>>(
+            xp, xs, dyp, dys, dxp, dxs, rows, cols);
+    else
+        swiglu_packed_bwd_kernel<T, false><<<ew_grid(rows * cols), EW_THREADS, 0, st>>>(xp, xs, dyp, dys, dxp, dxs,
+                                                                                        rows, cols);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace xma
+
+#define XMA_DISPATCH_FLOAT(dtype, CALL)             \
+    switch (dtype) {                                \
+        case XMA_F32: { using T = float; return CALL; }            \
+        case XMA_F16: { using T = __half; return CALL; }           \
+        case XMA_BF16: { using T = __nv_bfloat16; return CALL; }   \
+        default: return XMA_ERR_BAD_DTYPE;          \
+    }
+
+namespace xma {
+
+int swiglu_fwd_launch(const void* g, int64_t gs, const void* u, int64_t us, void* y, int64_t ys, int dtype,
+                      int64_t rows, int64_t cols, cudaStream_t st) {
+    if (rows <= 0 || cols <= 0) return XMA_OK;
+    XMA_DISPATCH_FLOAT(dtype, swiglu_fwd_impl<T>(g, gs, u, us, y, ys, rows, cols, st));
+}
+
+int swiglu_bwd_launch(const void* g, int64_t gs, const void* u, int64_t us, const void* dy, int64_t dys, void* dg,
+                      int64_t dgs, void* du, int64_t dus, int dtype, int64_t rows, int64_t cols, cudaStream_t st) {
+    if (rows <= 0 || cols <= 0) return XMA_OK;
+    XMA_DISPATCH_FLOAT(dtype, swiglu_bwd_impl<T>(g, gs, u, us, dy, dys, dg, dgs, du, dus, rows, cols, st));
+}
+
+}  // namespace xma
+
+extern "C" {
+
+int xma_b200_swiglu_fwd(const void* gate, int64_t gate_row_stride, const void* up, int64_t up_row_stride, void* y,
+                        int64_t y_row_stride, int dtype, int64_t rows, int64_t cols, cudaStream_t stream) {
+    if (rows < 0 || cols < 0) return XMA_ERR_BAD_SHAPE;
+    if (rows == 0 || cols == 0) return XMA_OK;
+    if (!gate || !up || !y) return XMA_ERR_NULL_POINTER;
+    XMA_DISPATCH_FLOAT(dtype, xma::swiglu_fwd_impl<T>(gate, gate_row_stride, up, up_row_stride, y, y_row_stride,
+                                                      rows, cols, stream));
+}
+
+int xma_b200_swiglu_bwd(const void* gate, int64_t gate_row_stride, const void* up, int64_t up_row_stride,
+                        const void* dy, int64_t dy_row_stride, void* dgate, int64_t dgate_row_stride, void* dup,
+                        int64_t dup_row_stride, int dtype, int64_t rows, int64_t cols, cudaStream_t stream) {
+    if (rows < 0 || cols < 0) return XMA_ERR_BAD_SHAPE;
+    if (rows == 0 || cols == 0) return XMA_OK;
+    if (!gate || !up || !dy || !dgate || !dup) return XMA_ERR_NULL_POINTER;
+    XMA_DISPATCH_FLOAT(dtype,
+                       xma::swiglu_bwd_impl<T>(gate, gate_row_stride, up, up_row_stride, dy, dy_row_stride, dgate,
+                                               dgate_row_stride, dup, dup_row_stride, rows, cols, stream));
+}
+
+int xma_b200_swiglu_packed_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, int dtype,
+                               int64_t rows, int64_t out_cols, cudaStream_t stream) {
+    if (rows < 0 || out_cols < 0) return XMA_ERR_BAD_SHAPE;
+    if (rows == 0 || out_cols == 0) return XMA_OK;
+    if (!x || !y) return XMA_ERR_NULL_POINTER;
+    XMA_DISPATCH_FLOAT(dtype, xma::swiglu_packed_fwd_impl<T>(x, x_row_stride, y, y_row_stride, rows, out_cols, stream));
+}
+
+int xma_b200_swiglu_packed_bwd(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride, void* dx,
+                               int64_t dx_row_stride, int dtype, int64_t rows, int64_t out_cols,
+                               cudaStream_t stream) {
+    if (rows < 0 || out_cols < 0) return XMA_ERR_BAD_SHAPE;
+    if (rows == 0 || out_cols == 0) return XMA_OK;
+    if (!x || !dy || !dx) return XMA_ERR_NULL_POINTER;
+    XMA_DISPATCH_FLOAT(dtype, xma::swiglu_packed_bwd_impl<T>(x, x_row_stride, dy, dy_row_stride, dx, dx_row_stride,
+                                                             rows, out_cols, stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,237 @@
+"""`torch.library` custom ops over the C ABI (namespace `xma_b200::`).
+
+Same convention as the reference's `xma_op` (xma/custom_op.py:72-108): the caller allocates every
+output with torch, the op mutates it and returns None, so no fake implementation is needed and the
+ops trace under `torch.compile(fullgraph=True)`. Each op forwards raw device pointers, sizes and
+the current CUDA stream to one `extern "C"` function of libxma_b200.so.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import check, current_stream, dtype_code, lib, ptr, require_cuda, status_word
+
+_NS = "xma_b200"
+
+
+def _row_stride(t: Tensor) -> int:
+    if t.dim() != 2 or (t.size(1) > 1 and t.stride(1) != 1):
+        raise ValueError("expected a 2-D tensor whose last dimension is contiguous")
+    return t.stride(0) if t.size(0) > 1 else max(t.stride(0), t.size(1))
+
+
+@torch.library.custom_op(f"{_NS}::continuous_count", mutates_args={"counts"}, device_types="cuda")
+def continuous_count_(ids: Tensor, counts: Tensor) -> None:
+    require_cuda(ids, counts)
+    check(
+        lib.xma_b200_continuous_count(
+            ptr(ids), dtype_code(ids.dtype), ids.numel(), counts.numel(), ptr(counts), ptr(status_word(ids.device)),
+            current_stream(ids.device)
+        ),
+        "xma_b200_continuous_count",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::route_topk_softmax", mutates_args={"weights", "selected"}, device_types="cuda")
+def route_topk_softmax_(logits: Tensor, top_k: int, weights: Tensor, selected: Tensor) -> None:
+    require_cuda(logits, weights, selected)
+    sel32 = ptr(selected) if selected.dtype == torch.int32 else None
+    sel64 = ptr(selected) if selected.dtype == torch.int64 else None
+    check(
+        lib.xma_b200_route_topk_softmax(
+            ptr(logits), dtype_code(logits.dtype), _row_stride(logits), logits.size(0), logits.size(1), top_k,
+            ptr(weights), sel32, sel64, current_stream(logits.device)
+        ),
+        "xma_b200_route_topk_softmax",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::route_topk_softmax_bwd", mutates_args={"d_logits"}, device_types="cuda")
+def route_topk_softmax_bwd_(logits: Tensor, selected: Tensor, d_weights: Tensor, d_logits: Tensor) -> None:
+    require_cuda(logits, selected, d_weights, d_logits)
+    check(
+        lib.xma_b200_route_topk_softmax_bwd(
+            ptr(logits), dtype_code(logits.dtype), _row_stride(logits), ptr(selected), ptr(d_weights),
+            logits.size(0), logits.size(1), selected.size(1), ptr(d_logits), current_stream(logits.device)
+        ),
+        "xma_b200_route_topk_softmax_bwd",
+    )
+
+
+@torch.library.custom_op(
+    f"{_NS}::count_sort",
+    mutates_args={"counts", "offsets_incl", "pad_offsets", "tile_prefix", "tile_expert", "sorted_expert_idxs",
+                  "sorted_scattered_idxs", "row_src"},
+    device_types="cuda",
+)
+def count_sort_(
+    ids: Tensor,
+    num_experts: int,
+    counts: Tensor,
+    offsets_incl: Tensor,
+    pad_offsets: Tensor,
+    tile_prefix: Tensor,
+    tile_expert: Tensor,
+    sorted_expert_idxs: Tensor,
+    sorted_scattered_idxs: Tensor,
+    row_src: Tensor,
+) -> None:
+    require_cuda(ids)
+    n = ids.numel()
+    scratch_bytes = lib.xma_b200_count_sort_scratch_bytes(n, num_experts)
+    if scratch_bytes < 0:
+        check(int(scratch_bytes), "xma_b200_count_sort_scratch_bytes")
+    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=ids.device)
+    check(
+        lib.xma_b200_count_sort(
+            ptr(ids), dtype_code(ids.dtype), n, num_experts, ptr(counts), ptr(offsets_incl), ptr(pad_offsets),
+            ptr(tile_prefix), ptr(tile_expert), tile_expert.numel(), ptr(sorted_expert_idxs),
+            ptr(sorted_scattered_idxs), ptr(row_src), row_src.numel(), ptr(scratch), scratch_bytes,
+            ptr(status_word(ids.device)), current_stream(ids.device)
+        ),
+        "xma_b200_count_sort",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::gather_rows", mutates_args={"out"}, device_types="cuda")
+def gather_rows_(
+    src: Tensor, row_src: Tensor, coeff: Optional[Tensor], fan_out: int, rows_in_use: Optional[Tensor], out: Tensor
+) -> None:
+    require_cuda(src, row_src, out)
+    check(
+        lib.xma_b200_gather_rows(
+            ptr(src), dtype_code(src.dtype), _row_stride(src), ptr(row_src), ptr(coeff), fan_out, out.size(0),
+            ptr(rows_in_use), src.size(1), ptr(out), _row_stride(out), current_stream(src.device)
+        ),
+        "xma_b200_gather_rows",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::combine_rows", mutates_args={"y"}, device_types="cuda")
+def combine_rows_(ys: Tensor, weights: Optional[Tensor], top_k: int, y: Tensor) -> None:
+    require_cuda(ys, y)
+    check(
+        lib.xma_b200_combine_rows(
+            ptr(ys), dtype_code(ys.dtype), _row_stride(ys), ptr(weights), top_k, y.size(0), y.size(1), ptr(y),
+            _row_stride(y), current_stream(ys.device)
+        ),
+        "xma_b200_combine_rows",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::combine_bwd", mutates_args={"d_weights"}, device_types="cuda")
+def combine_bwd_(ys: Tensor, dy: Tensor, top_k: int, d_weights: Tensor) -> None:
+    require_cuda(ys, dy, d_weights)
+    check(
+        lib.xma_b200_combine_bwd(
+            ptr(ys), dtype_code(ys.dtype), _row_stride(ys), ptr(dy), _row_stride(dy), top_k, dy.size(0),
+            dy.size(1), ptr(d_weights), current_stream(ys.device)
+        ),
+        "xma_b200_combine_bwd",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::grouped_gemm_rows", mutates_args={"out", "aux"}, device_types="cuda")
+def grouped_gemm_rows_(
+    a: Tensor,
+    w: Tensor,
+    w_layout: int,
+    out: Tensor,
+    aux: Optional[Tensor],
+    row_map: Optional[Tensor],
+    tile_expert: Tensor,
+    tile_prefix: Tensor,
+    kd: int,
+    n: int,
+    epilogue: int,
+    impl: int,
+) -> None:
+    require_cuda(a, w, out)
+    if not w.is_contiguous():
+        raise ValueError("expert weights must be contiguous [E, out_features, in_features]")
+    check(
+        lib.xma_b200_grouped_gemm_rows(
+            ptr(a), _row_stride(a), ptr(w), w_layout, ptr(out), _row_stride(out), ptr(aux),
+            0 if aux is None else _row_stride(aux), ptr(row_map), ptr(tile_expert), ptr(tile_prefix), w.size(0),
+            tile_expert.numel(), kd, n, epilogue, dtype_code(a.dtype), impl, ptr(status_word(a.device)),
+            current_stream(a.device)
+        ),
+        "xma_b200_grouped_gemm_rows",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::grouped_gemm_dw", mutates_args={"dw"}, device_types="cuda")
+def grouped_gemm_dw_(x: Tensor, y: Tensor, counts: Tensor, pad_offsets: Tensor, dw: Tensor, impl: int) -> None:
+    require_cuda(x, y, dw)
+    check(
+        lib.xma_b200_grouped_gemm_dw(
+            ptr(x), _row_stride(x), ptr(y), _row_stride(y), ptr(counts), ptr(pad_offsets), x.size(0), dw.size(0),
+            dw.size(1), dw.size(2), ptr(dw), dtype_code(x.dtype), impl, ptr(status_word(x.device)),
+            current_stream(x.device)
+        ),
+        "xma_b200_grouped_gemm_dw",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::swiglu_fwd", mutates_args={"y"}, device_types="cuda")
+def swiglu_fwd_(g: Tensor, u: Tensor, y: Tensor) -> None:
+    require_cuda(g, u, y)
+    check(
+        lib.xma_b200_swiglu_fwd(
+            ptr(g), _row_stride(g), ptr(u), _row_stride(u), ptr(y), _row_stride(y), dtype_code(g.dtype), g.size(0),
+            g.size(1), current_stream(g.device)
+        ),
+        "xma_b200_swiglu_fwd",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::swiglu_bwd", mutates_args={"dg", "du"}, device_types="cuda")
+def swiglu_bwd_(g: Tensor, u: Tensor, dy: Tensor, dg: Tensor, du: Tensor) -> None:
+    require_cuda(g, u, dy, dg, du)
+    check(
+        lib.xma_b200_swiglu_bwd(
+            ptr(g), _row_stride(g), ptr(u), _row_stride(u), ptr(dy), _row_stride(dy), ptr(dg), _row_stride(dg),
+            ptr(du), _row_stride(du), dtype_code(g.dtype), g.size(0), g.size(1), current_stream(g.device)
+        ),
+        "xma_b200_swiglu_bwd",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::swiglu_packed_fwd", mutates_args={"y"}, device_types="cuda")
+def swiglu_packed_fwd_(x: Tensor, y: Tensor) -> None:
+    require_cuda(x, y)
+    check(
+        lib.xma_b200_swiglu_packed_fwd(
+            ptr(x), _row_stride(x), ptr(y), _row_stride(y), dtype_code(x.dtype), y.size(0), y.size(1),
+            current_stream(x.device)
+        ),
+        "xma_b200_swiglu_packed_fwd",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::swiglu_packed_bwd", mutates_args={"dx"}, device_types="cuda")
+def swiglu_packed_bwd_(x: Tensor, dy: Tensor, dx: Tensor) -> None:
+    require_cuda(x, dy, dx)
+    check(
+        lib.xma_b200_swiglu_packed_bwd(
+            ptr(x), _row_stride(x), ptr(dy), _row_stride(dy), ptr(dx), _row_stride(dx), dtype_code(x.dtype),
+            dy.size(0), dy.size(1), current_stream(x.device)
+        ),
+        "xma_b200_swiglu_packed_bwd",
+    )
+
+
+# Kernel-family override for the grouped GEMMs, used by tests: 0 automatic, 1 CUDA cores, 2 tcgen05.
+GEMM_IMPL = _lib.IMPL_AUTO
+
+
+def set_gemm_impl(impl: int) -> int:
+    global GEMM_IMPL
+    previous = GEMM_IMPL
+    GEMM_IMPL = int(impl)
+    return previous

@@ -1,0 +1,160 @@
+/*
+ * xma_b200.h - C ABI of libxma_b200.so: the MoE hot path of XMA
+ * (open-lm-engine/accelerated-model-architectures) as hand-written sm_100a CUDA.
+ *
+ * Conventions
+ *   - Plain pointers and sizes only; every pointer is a DEVICE pointer unless stated otherwise.
+ *   - The caller owns and allocates every buffer (outputs included); nothing here allocates device
+ *     memory. All work is enqueued on `stream` and is asynchronous.
+ *   - Return value: 0 = enqueued; < 0 = argument error found on the host, nothing enqueued
+ *     (XMA_ERR_* below); > 0 = cudaError_t of a failed runtime call or launch.
+ *     xma_b200_error_string() turns any of them into text.
+ *   - `device_status` (may be NULL) is an int32 in device memory that kernels OR bits into:
+ *       1 = an id outside [0, bins) was skipped, 2 = a bounded device-side wait expired,
+ *       4 = an inconsistent tile table entry was skipped. The caller clears and polls it.
+ *   - dtype codes: 0 = fp32, 1 = fp16, 2 = bf16, 3 = int32, 4 = int64.
+ *   - Strides are in ELEMENTS. "grouped" buffers hold the routed rows sorted by expert, each
+ *     expert's block padded to a multiple of 128 rows (pad rows are zero / ignored).
+ *
+ * Each entry point names the reference interface (file:line inside the XMA repository) it replaces.
+ */
+#ifndef XMA_B200_H_
+#define XMA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __CUDA_RUNTIME_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+#define XMA_B200_ROW_PAD 128
+
+int xma_b200_abi_version(void);
+const char* xma_b200_error_string(int code);
+
+/* ---- routing -------------------------------------------------------------------------------- */
+
+/* counts[b] = number of ids equal to b, for b in [0, bins); ids outside the range are skipped
+ * (status bit 1). `counts` is overwritten (no pre-zeroing needed).
+ * Replaces continuous_count / _continuous_count_cuda:
+ *   xma/functional/continuous_count/__init__.py:16-51,
+ *   xma/functional/continuous_count/cuda_implementation.py:19-197. */
+int xma_b200_continuous_count(const void* ids, int id_dtype, int64_t n, int bins, uint32_t* counts,
+                              int* device_status, cudaStream_t stream);
+
+/* logits [tokens, num_experts] (row stride given) -> weights [tokens, top_k] (same dtype as the
+ * logits: softmax in fp32 over the top_k selected values, rounded once) and the selected expert
+ * ids in descending-logit order (ties: lowest expert id first; NaN sorts above everything).
+ * Either index output may be NULL.
+ * Replaces MoE._compute_routing_weights after the gate projection and MoE._get_topk:
+ *   xma/layers/moe/__init__.py:182-195, 256-262. */
+int xma_b200_route_topk_softmax(const void* logits, int dtype, int64_t logits_row_stride, int64_t tokens,
+                                int num_experts, int top_k, void* weights, int32_t* selected_i32,
+                                int64_t* selected_i64, cudaStream_t stream);
+
+/* d_logits [tokens, num_experts] (dense, fully written) from d_weights [tokens, top_k]: the
+ * backward of softmax-over-top-k scattered to the selected columns. The reference gets this from
+ * autograd through F.softmax and Tensor.topk (xma/layers/moe/__init__.py:192, 260). */
+int xma_b200_route_topk_softmax_bwd(const void* logits, int dtype, int64_t logits_row_stride,
+                                    const int32_t* selected_i32, const void* d_weights, int64_t tokens,
+                                    int num_experts, int top_k, void* d_logits, cudaStream_t stream);
+
+/* Sizes of the tables and scratch that xma_b200_count_sort needs for n routed ids and E experts. */
+int64_t xma_b200_count_sort_scratch_bytes(int64_t n, int num_experts);
+int64_t xma_b200_tile_capacity(int64_t n, int num_experts); /* 128-row tiles: n / 128 + E */
+
+/* Stable counting sort of the n routed expert ids (id i belongs to flat index i = token*top_k+slot):
+ *   counts[E]                 rows per expert (== bincount)
+ *   offsets_incl[E]           inclusive prefix sum of counts
+ *   pad_offsets[E+1]          first row of each expert in the padded grouped layout
+ *   tile_prefix[E+1]          128-row tiles in front of each expert; [E] = tiles in use
+ *   tile_expert[tile_cap]     owner of each padded tile
+ *   sorted_expert_idxs[n]     ids ascending
+ *   sorted_scattered_idxs[n]  flat index of each sorted row (stable: ties by flat index)
+ *   row_src[row_cap]          flat index of each PADDED grouped row, -1 for pad rows (may be NULL)
+ * tile_cap >= xma_b200_tile_capacity(n, E); row_cap >= 128 * tile_cap; scratch is 256-byte
+ * aligned, scratch_bytes >= xma_b200_count_sort_scratch_bytes(n, E); num_experts <= 1024.
+ * Replaces `selected_experts.flatten().sort()`, continuous_count and cumsum in
+ *   xma/layers/moe/__init__.py:210-217. */
+int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_experts, uint32_t* counts,
+                        int32_t* offsets_incl, int32_t* pad_offsets, int32_t* tile_prefix, int32_t* tile_expert,
+                        int64_t tile_cap, int32_t* sorted_expert_idxs, int32_t* sorted_scattered_idxs,
+                        int32_t* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes,
+                        int* device_status, cudaStream_t stream);
+
+/* ---- row movement --------------------------------------------------------------------------- */
+
+/* out[p, :] = src[row_src[p] / fan_out, :] * coeff[row_src[p]]  (coeff may be NULL; rows with
+ * row_src[p] < 0 are written as zeros). Only the first *rows_in_use rows are touched when that
+ * device pointer is non-NULL. width and strides must keep rows 16-byte aligned.
+ * Replaces group: xma/layers/moe/triton_implementation/group_kernel.py:69-100. */
+int xma_b200_gather_rows(const void* src, int dtype, int64_t src_row_stride, const int32_t* row_src,
+                         const void* coeff, int fan_out, int64_t rows, const int32_t* rows_in_use, int64_t width,
+                         void* out, int64_t out_row_stride, cudaStream_t stream);
+
+/* y[t, :] = sum_k weights[t, k] * ys[t * top_k + k, :], fp32 accumulate, one rounding
+ * (weights NULL: plain sum over the top_k slots).
+ * Replaces the bmm combine and the K-slot sum:
+ *   xma/layers/moe/triton_implementation/__init__.py:100-101 and :70. */
+int xma_b200_combine_rows(const void* ys, int dtype, int64_t ys_row_stride, const void* weights, int top_k,
+                          int64_t tokens, int64_t width, void* y, int64_t y_row_stride, cudaStream_t stream);
+
+/* d_weights[t, k] = <ys[t * top_k + k, :], dy[t, :]>.
+ * Replaces the bmm of xma/layers/moe/triton_implementation/__init__.py:130-131. */
+int xma_b200_combine_bwd(const void* ys, int dtype, int64_t ys_row_stride, const void* dy, int64_t dy_row_stride,
+                         int top_k, int64_t tokens, int64_t width, void* d_weights, cudaStream_t stream);
+
+/* ---- expert grouped GEMMs ------------------------------------------------------------------- */
+
+/* w_layout: 0 = weight stored [E, n, kd] (out = a * w_e^T), 1 = weight stored [E, kd, n] (out = a * w_e).
+ * epilogue: 0 = plain store (rows optionally scattered through row_map, negative entries skipped);
+ *           1 = SwiGLU forward, n = 2I: aux[r, 0:2I] = gate|up (rounded), out[r, 0:I] = up*gate*sigmoid(gate);
+ *           2 = SwiGLU backward, n = I: aux holds gate|up, the contraction is d(activation),
+ *               out[r, 0:I] = d gate, out[r, I:2I] = d up.
+ * impl: 0 = automatic, 1 = CUDA cores, 2 = tcgen05 tensor cores (bf16/fp16, widths multiple of 8).
+ * a is grouped [128 * tile_cap, kd]. fp32 accumulation everywhere.
+ * Replaces scatter2scatter: xma/layers/moe/triton_implementation/scatter_kernel.py:137-183,
+ * with swiglu fused as in xma/functional/swiglu/__init__.py:39. */
+int xma_b200_grouped_gemm_rows(const void* a, int64_t a_row_stride, const void* w, int w_layout, void* out,
+                               int64_t out_row_stride, void* aux, int64_t aux_row_stride, const int32_t* row_map,
+                               const int32_t* tile_expert, const int32_t* tile_prefix, int num_experts,
+                               int64_t tile_cap, int64_t kd, int64_t n, int epilogue, int dtype, int impl,
+                               int* device_status, cudaStream_t stream);
+
+/* dw[e, m, n] = sum over the rows r of expert e of x[r, m] * y[r, n]; x, y grouped (rows_cap rows
+ * allocated); experts without rows get zeros, so dw needs no pre-zeroing.
+ * Replaces group_bwd_W: xma/layers/moe/triton_implementation/group_backward_kernel.py:102-128. */
+int xma_b200_grouped_gemm_dw(const void* x, int64_t x_row_stride, const void* y, int64_t y_row_stride,
+                             const uint32_t* counts, const int32_t* pad_offsets, int64_t rows_cap, int num_experts,
+                             int64_t m, int64_t n, void* dw, int dtype, int impl, int* device_status,
+                             cudaStream_t stream);
+
+int xma_b200_grouped_gemm_uses_tensor_cores(int dtype, int64_t kd, int64_t n);
+
+/* ---- stand-alone SwiGLU --------------------------------------------------------------------- */
+
+/* y = up * gate * sigmoid(gate) in fp32, rounded once; row-strided operands allowed.
+ * Replaces _swiglu_forward_cuda / _swiglu_backward_cuda and the packed variants:
+ *   xma/functional/swiglu/__init__.py:39-87,
+ *   xma/functional/swiglu/cuda_implementation/__init__.py:13-63. */
+int xma_b200_swiglu_fwd(const void* gate, int64_t gate_row_stride, const void* up, int64_t up_row_stride, void* y,
+                        int64_t y_row_stride, int dtype, int64_t rows, int64_t cols, cudaStream_t stream);
+int xma_b200_swiglu_bwd(const void* gate, int64_t gate_row_stride, const void* up, int64_t up_row_stride,
+                        const void* dy, int64_t dy_row_stride, void* dgate, int64_t dgate_row_stride, void* dup,
+                        int64_t dup_row_stride, int dtype, int64_t rows, int64_t cols, cudaStream_t stream);
+/* x[r, 2c] = gate, x[r, 2c + 1] = up; out_cols is the width of y (half the width of x). */
+int xma_b200_swiglu_packed_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, int dtype,
+                               int64_t rows, int64_t out_cols, cudaStream_t stream);
+int xma_b200_swiglu_packed_bwd(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
+                               void* dx, int64_t dx_row_stride, int dtype, int64_t rows, int64_t out_cols,
+                               cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* XMA_B200_H_ */
