@@ -604,8 +604,8 @@ int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_expert
                         int64_t tile_cap, int32_t* sorted_expert_idxs, int32_t* sorted_scattered_idxs,
                         int32_t* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes, int* device_status,
                         cudaStream_t stream) {
-    if (!counts || !offsets_incl || !pad_offsets || !tile_prefix || !tile_expert || !sorted_expert_idxs ||
-        !sorted_scattered_idxs || !scratch || (n > 0 && !ids))
+    if (!counts || !offsets_incl || !pad_offsets || !tile_prefix || !tile_expert || !scratch ||
+        (n > 0 && (!ids || !sorted_expert_idxs || !sorted_scattered_idxs)))
         return XMA_ERR_NULL_POINTER;
     if (n < 0 || num_experts <= 0 || num_experts > xma::SORT_MAX_BINS) return XMA_ERR_BAD_SHAPE;
     if (n > 0x7fffffffLL - xma::SORT_TILE) return XMA_ERR_TOO_LARGE;

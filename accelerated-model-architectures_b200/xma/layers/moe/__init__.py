@@ -223,9 +223,11 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         ops.gather_rows_(x, row_src, None, K, pad_offsets[E:], xs)
         gu = torch.empty(row_cap, two_i, **opts)
         act = torch.empty(row_cap, I, **opts)
-        ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, tile_expert, tile_prefix, H, two_i, EPI_SWIGLU, impl)
+        ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, tile_expert, tile_prefix, H, two_i, EPI_SWIGLU, impl,
+                               tag="gemm_up_swiglu")
         ys = torch.empty(T * K, H, **opts)
-        ops.grouped_gemm_rows_(act, w2, W_NK, ys, None, row_src, tile_expert, tile_prefix, I, H, EPI_PLAIN, impl)
+        ops.grouped_gemm_rows_(act, w2, W_NK, ys, None, row_src, tile_expert, tile_prefix, I, H, EPI_PLAIN, impl,
+                               tag="gemm_down")
         router_weights = router_weights.contiguous()
         y = torch.empty(T, H, **opts)
         ops.combine_rows_(ys, router_weights, K, y)
@@ -258,19 +260,20 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         d_w2 = None
         if need_w2:
             d_w2 = torch.empty_like(w2)
-            ops.grouped_gemm_dw_(dys, act, counts, pad_offsets, d_w2, impl)
+            ops.grouped_gemm_dw_(dys, act, counts, pad_offsets, d_w2, impl, tag="gemm_dw2")
 
         d_x = d_w1 = None
         if need_x or need_w1:
             dgu = torch.empty(row_cap, two_i, **opts)
-            ops.grouped_gemm_rows_(dys, w2, W_KN, dgu, gu, None, tile_expert, tile_prefix, H, I, EPI_DSWIGLU, impl)
+            ops.grouped_gemm_rows_(dys, w2, W_KN, dgu, gu, None, tile_expert, tile_prefix, H, I, EPI_DSWIGLU, impl,
+                                   tag="gemm_dact_dswiglu")
             if need_w1:
                 d_w1 = torch.empty_like(w1)
-                ops.grouped_gemm_dw_(dgu, xs, counts, pad_offsets, d_w1, impl)
+                ops.grouped_gemm_dw_(dgu, xs, counts, pad_offsets, d_w1, impl, tag="gemm_dw1")
             if need_x:
                 dxs = torch.empty(T * K, H, **opts)
                 ops.grouped_gemm_rows_(dgu, w1, W_KN, dxs, None, row_src, tile_expert, tile_prefix, two_i, H,
-                                       EPI_PLAIN, impl)
+                                       EPI_PLAIN, impl, tag="gemm_dx")
                 d_x = torch.empty(T, H, **opts)
                 ops.combine_rows_(dxs, None, K, d_x)
         return d_x, d_w1, d_w2, d_rw, None, None, None, None, None

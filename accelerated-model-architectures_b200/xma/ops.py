@@ -26,7 +26,7 @@ def _row_stride(t: Tensor) -> int:
 
 
 @torch.library.custom_op(f"{_NS}::continuous_count", mutates_args={"counts"}, device_types="cuda")
-def continuous_count_(ids: Tensor, counts: Tensor) -> None:
+def _continuous_count_op(ids: Tensor, counts: Tensor) -> None:
     require_cuda(ids, counts)
     check(
         lib.xma_b200_continuous_count(
@@ -38,7 +38,7 @@ def continuous_count_(ids: Tensor, counts: Tensor) -> None:
 
 
 @torch.library.custom_op(f"{_NS}::route_topk_softmax", mutates_args={"weights", "selected"}, device_types="cuda")
-def route_topk_softmax_(logits: Tensor, top_k: int, weights: Tensor, selected: Tensor) -> None:
+def _route_topk_softmax_op(logits: Tensor, top_k: int, weights: Tensor, selected: Tensor) -> None:
     require_cuda(logits, weights, selected)
     sel32 = ptr(selected) if selected.dtype == torch.int32 else None
     sel64 = ptr(selected) if selected.dtype == torch.int64 else None
@@ -52,7 +52,7 @@ def route_topk_softmax_(logits: Tensor, top_k: int, weights: Tensor, selected: T
 
 
 @torch.library.custom_op(f"{_NS}::route_topk_softmax_bwd", mutates_args={"d_logits"}, device_types="cuda")
-def route_topk_softmax_bwd_(logits: Tensor, selected: Tensor, d_weights: Tensor, d_logits: Tensor) -> None:
+def _route_topk_softmax_bwd_op(logits: Tensor, selected: Tensor, d_weights: Tensor, d_logits: Tensor) -> None:
     require_cuda(logits, selected, d_weights, d_logits)
     check(
         lib.xma_b200_route_topk_softmax_bwd(
@@ -69,7 +69,7 @@ def route_topk_softmax_bwd_(logits: Tensor, selected: Tensor, d_weights: Tensor,
                   "sorted_scattered_idxs", "row_src"},
     device_types="cuda",
 )
-def count_sort_(
+def _count_sort_op(
     ids: Tensor,
     num_experts: int,
     counts: Tensor,
@@ -99,7 +99,7 @@ def count_sort_(
 
 
 @torch.library.custom_op(f"{_NS}::gather_rows", mutates_args={"out"}, device_types="cuda")
-def gather_rows_(
+def _gather_rows_op(
     src: Tensor, row_src: Tensor, coeff: Optional[Tensor], fan_out: int, rows_in_use: Optional[Tensor], out: Tensor
 ) -> None:
     require_cuda(src, row_src, out)
@@ -113,7 +113,7 @@ def gather_rows_(
 
 
 @torch.library.custom_op(f"{_NS}::combine_rows", mutates_args={"y"}, device_types="cuda")
-def combine_rows_(ys: Tensor, weights: Optional[Tensor], top_k: int, y: Tensor) -> None:
+def _combine_rows_op(ys: Tensor, weights: Optional[Tensor], top_k: int, y: Tensor) -> None:
     require_cuda(ys, y)
     check(
         lib.xma_b200_combine_rows(
@@ -125,7 +125,7 @@ def combine_rows_(ys: Tensor, weights: Optional[Tensor], top_k: int, y: Tensor) 
 
 
 @torch.library.custom_op(f"{_NS}::combine_bwd", mutates_args={"d_weights"}, device_types="cuda")
-def combine_bwd_(ys: Tensor, dy: Tensor, top_k: int, d_weights: Tensor) -> None:
+def _combine_bwd_op(ys: Tensor, dy: Tensor, top_k: int, d_weights: Tensor) -> None:
     require_cuda(ys, dy, d_weights)
     check(
         lib.xma_b200_combine_bwd(
@@ -137,7 +137,7 @@ def combine_bwd_(ys: Tensor, dy: Tensor, top_k: int, d_weights: Tensor) -> None:
 
 
 @torch.library.custom_op(f"{_NS}::grouped_gemm_rows", mutates_args={"out", "aux"}, device_types="cuda")
-def grouped_gemm_rows_(
+def _grouped_gemm_rows_op(
     a: Tensor,
     w: Tensor,
     w_layout: int,
@@ -166,7 +166,7 @@ def grouped_gemm_rows_(
 
 
 @torch.library.custom_op(f"{_NS}::grouped_gemm_dw", mutates_args={"dw"}, device_types="cuda")
-def grouped_gemm_dw_(x: Tensor, y: Tensor, counts: Tensor, pad_offsets: Tensor, dw: Tensor, impl: int) -> None:
+def _grouped_gemm_dw_op(x: Tensor, y: Tensor, counts: Tensor, pad_offsets: Tensor, dw: Tensor, impl: int) -> None:
     require_cuda(x, y, dw)
     check(
         lib.xma_b200_grouped_gemm_dw(
@@ -179,7 +179,7 @@ def grouped_gemm_dw_(x: Tensor, y: Tensor, counts: Tensor, pad_offsets: Tensor, 
 
 
 @torch.library.custom_op(f"{_NS}::swiglu_fwd", mutates_args={"y"}, device_types="cuda")
-def swiglu_fwd_(g: Tensor, u: Tensor, y: Tensor) -> None:
+def _swiglu_fwd_op(g: Tensor, u: Tensor, y: Tensor) -> None:
     require_cuda(g, u, y)
     check(
         lib.xma_b200_swiglu_fwd(
@@ -191,7 +191,7 @@ def swiglu_fwd_(g: Tensor, u: Tensor, y: Tensor) -> None:
 
 
 @torch.library.custom_op(f"{_NS}::swiglu_bwd", mutates_args={"dg", "du"}, device_types="cuda")
-def swiglu_bwd_(g: Tensor, u: Tensor, dy: Tensor, dg: Tensor, du: Tensor) -> None:
+def _swiglu_bwd_op(g: Tensor, u: Tensor, dy: Tensor, dg: Tensor, du: Tensor) -> None:
     require_cuda(g, u, dy, dg, du)
     check(
         lib.xma_b200_swiglu_bwd(
@@ -203,7 +203,7 @@ def swiglu_bwd_(g: Tensor, u: Tensor, dy: Tensor, dg: Tensor, du: Tensor) -> Non
 
 
 @torch.library.custom_op(f"{_NS}::swiglu_packed_fwd", mutates_args={"y"}, device_types="cuda")
-def swiglu_packed_fwd_(x: Tensor, y: Tensor) -> None:
+def _swiglu_packed_fwd_op(x: Tensor, y: Tensor) -> None:
     require_cuda(x, y)
     check(
         lib.xma_b200_swiglu_packed_fwd(
@@ -215,7 +215,7 @@ def swiglu_packed_fwd_(x: Tensor, y: Tensor) -> None:
 
 
 @torch.library.custom_op(f"{_NS}::swiglu_packed_bwd", mutates_args={"dx"}, device_types="cuda")
-def swiglu_packed_bwd_(x: Tensor, dy: Tensor, dx: Tensor) -> None:
+def _swiglu_packed_bwd_op(x: Tensor, dy: Tensor, dx: Tensor) -> None:
     require_cuda(x, dy, dx)
     check(
         lib.xma_b200_swiglu_packed_bwd(
@@ -224,6 +224,61 @@ def swiglu_packed_bwd_(x: Tensor, dy: Tensor, dx: Tensor) -> None:
         ),
         "xma_b200_swiglu_packed_bwd",
     )
+
+
+# ---- launch accounting and per-kernel timing ------------------------------------------------------
+class KernelStats:
+    """Counts the kernels this library launches and, when `timing` is on, brackets every op with
+    CUDA events on the launching stream (used by bench.py for the per-kernel roofline)."""
+
+    def __init__(self) -> None:
+        self.enabled = False
+        self.timing = False
+        self.launches = 0
+        self.events: dict[str, list] = {}
+
+    def reset(self) -> None:
+        self.launches = 0
+        self.events = {}
+
+    def elapsed_ms(self) -> dict[str, list[float]]:
+        return {k: [a.elapsed_time(b) for a, b in v] for k, v in self.events.items()}
+
+
+STATS = KernelStats()
+
+
+def _wrap(op, name: str, kernels: int):
+    def call(*args, tag: str | None = None):
+        if not STATS.enabled:
+            return op(*args)
+        STATS.launches += kernels
+        if not STATS.timing:
+            return op(*args)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        op(*args)
+        end.record()
+        STATS.events.setdefault(tag or name, []).append((start, end))
+        return None
+
+    call.__name__ = name
+    return call
+
+
+continuous_count_ = _wrap(_continuous_count_op, "continuous_count", 1)
+route_topk_softmax_ = _wrap(_route_topk_softmax_op, "route_topk_softmax", 1)
+route_topk_softmax_bwd_ = _wrap(_route_topk_softmax_bwd_op, "route_topk_softmax_bwd", 1)
+count_sort_ = _wrap(_count_sort_op, "count_sort", 3)
+gather_rows_ = _wrap(_gather_rows_op, "gather_rows", 1)
+combine_rows_ = _wrap(_combine_rows_op, "combine_rows", 1)
+combine_bwd_ = _wrap(_combine_bwd_op, "combine_bwd", 1)
+grouped_gemm_rows_ = _wrap(_grouped_gemm_rows_op, "grouped_gemm_rows", 1)
+grouped_gemm_dw_ = _wrap(_grouped_gemm_dw_op, "grouped_gemm_dw", 1)
+swiglu_fwd_ = _wrap(_swiglu_fwd_op, "swiglu_fwd", 1)
+swiglu_bwd_ = _wrap(_swiglu_bwd_op, "swiglu_bwd", 1)
+swiglu_packed_fwd_ = _wrap(_swiglu_packed_fwd_op, "swiglu_packed_fwd", 1)
+swiglu_packed_bwd_ = _wrap(_swiglu_packed_bwd_op, "swiglu_packed_bwd", 1)
 
 
 # Kernel-family override for the grouped GEMMs, used by tests: 0 automatic, 1 CUDA cores, 2 tcgen05.

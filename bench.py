@@ -1,0 +1,424 @@
+"""MoE forward+backward throughput on B200 (tokens/s), one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1] [--impl reference]
+
+N = 1 runs the Mixtral-shaped layer of BASELINE.json configs[1] (16384 tokens, hidden 4096,
+intermediate 14336, 8 experts, top-2, bf16) through `xma.layers.MoE`. For N > 1 the script is
+launched by torchrun, one rank per GPU, and runs the same per-GPU workload expert-parallel
+(experts sharded over ranks, NCCL all-to-all dispatch/combine): weak scaling.
+A step = one forward + backward of the layer on one batch of seeded synthetic inputs.
+
+`value`  : tokens/s with inputs resident in HBM (CUDA events around exactly K steps, max over ranks)
+`e2e`    : the same metric with the step's inputs copied from pinned host memory and its results
+           copied back inside the timed region
+`roofline`: the dominant kernel family against the measured cuBLAS bf16 peak (MEASURED_PEAKS.json)
+`cpu_baseline`: the CPU oracle (restatement of the reference's torch path) on a bounded sample
+`--impl reference`: the reference's CPU implementation of the path = the oracle port (the reference
+           is a Python package that cannot travel to the GPU box), on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "accelerated-model-architectures_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+# name -> tokens per GPU, hidden, intermediate, experts (global), top_k
+WORKLOADS = {
+    "c1": dict(tokens=512, hidden=256, inter=512, experts=8, top_k=2, dtype="f32",
+               desc="configs[0] tiny fp32"),
+    "c2": dict(tokens=16384, hidden=4096, inter=14336, experts=8, top_k=2, dtype="bf16",
+               desc="configs[1] Mixtral-shaped: 4x4096 tokens, 8 experts top-2, SwiGLU"),
+    "c2e2": dict(tokens=4096, hidden=4096, inter=14336, experts=2, top_k=2, dtype="bf16",
+                 desc="profiling slice of configs[1]: same per-expert GEMM shapes (4096 rows/expert), 2 experts"),
+    "c3": dict(tokens=32768, hidden=2048, inter=1024, experts=64, top_k=8, dtype="bf16",
+               desc="configs[2] fine-grained: 64 experts top-8, Zipf(1.2)-skewed load"),
+    "c4": dict(tokens=16384, hidden=4096, inter=1536, experts=128, top_k=8, dtype="bf16",
+               desc="configs[3] expert-parallel: 128 experts top-8, uniform random logits"),
+}
+PEAK_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+METRIC = "moe_fwd_bwd_tokens_per_s"
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(PEAK_FALLBACK), "fallback"
+
+
+def expert_flops(w: dict, tokens: int) -> float:
+    """Algorithmic FLOPs of the expert GEMMs, forward + backward: 18 * R * H * I (R = tokens * top_k)."""
+    return 18.0 * tokens * w["top_k"] * w["hidden"] * w["inter"]
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of this rank's GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        # samples taken under load: the upper half of the observed clocks is not assumed; use all
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# synthetic inputs
+# ---------------------------------------------------------------------------------------------------
+def make_layer(w: dict, device: torch.device, dtype: torch.dtype, seed: int, local_experts: tuple[int, int] | None):
+    """Random-init layer of the named shape. Weights ~ N(0, 0.02) (gate included: with N(0,1) inputs
+    this gives near-uniform expert loads); the Zipf workload adds a per-expert logit bias through an
+    extra constant input feature folded into the gate weight's last column."""
+    from xma.layers import MoE, SwiGLU
+
+    torch.manual_seed(seed)
+    e0, e1 = local_experts if local_experts else (0, w["experts"])
+    with torch.device(device):
+        moe = MoE(e1 - e0, w["top_k"], w["hidden"], w["inter"], SwiGLU(), True, False, 0.02)
+    moe = moe.to(dtype)
+    # the router always sees every expert
+    gen = torch.Generator(device="cpu").manual_seed(1234)
+    gate = torch.randn(w["experts"], w["hidden"], generator=gen) * 0.02
+    if w is WORKLOADS["c3"]:
+        ranks = torch.randperm(w["experts"], generator=gen).float() + 1.0
+        bias = -1.2 * torch.log(ranks)
+        gate[:, -1] = bias  # paired with x[:, -1] = 1
+    if w is WORKLOADS["c4"]:
+        gate.zero_()  # logits come from uniform random features instead (see make_inputs)
+    return moe, gate.to(device=device, dtype=dtype)
+
+
+def make_inputs(w: dict, device: torch.device, dtype: torch.dtype, seed: int, pinned: bool):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    T, H = w["tokens"], w["hidden"]
+    x = torch.randn(T, H, generator=gen)
+    if w is WORKLOADS["c3"]:
+        x[:, -1] = 1.0
+    dy = torch.randn(T, H, generator=gen)
+    x, dy = x.to(dtype), dy.to(dtype)
+    if pinned:
+        return x.pin_memory(), dy.pin_memory()
+    return x.to(device), dy.to(device)
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's torch path
+# ---------------------------------------------------------------------------------------------------
+def cpu_step_tokens_per_s(w: dict, sample_tokens: int, steps: int, warmup: int) -> tuple[float, float, int]:
+    """Times the oracle's forward+backward on `sample_tokens` tokens of the workload (same shapes per
+    expert, same dtype) with all host threads. Returns (tokens/s, seconds per step, threads)."""
+    from oracle import moe_oracle as orc
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    dtype = torch.float32 if w["dtype"] == "f32" else torch.bfloat16
+    gen = torch.Generator().manual_seed(0)
+    E, H, I, K = w["experts"], w["hidden"], w["inter"], w["top_k"]
+    x = torch.randn(sample_tokens, H, generator=gen).to(dtype)
+    dy = torch.randn(sample_tokens, H, generator=gen).to(dtype)
+    gate = (torch.randn(E, H, generator=gen) * 0.02).to(dtype)
+    w1 = torch.empty(E, 2 * I, H, dtype=dtype).normal_(0, 0.02, generator=gen)
+    w2 = torch.empty(E, H, I, dtype=dtype).normal_(0, 0.02, generator=gen)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.moe_forward_backward(x, gate, w1, w2, K, "swiglu", dy=dy)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    return sample_tokens / sec, sec, threads
+
+
+def cpu_sample_tokens(w: dict) -> int:
+    # about 10-30 s of CPU work in total: the survey measured ~0.26 TFLOP/s bf16 on 8 cores
+    target_flops = 2.0e12
+    per_token = expert_flops(w, 1)
+    return int(max(64, min(w["tokens"], 2 ** int(np.log2(max(target_flops / per_token, 64))))))
+
+
+def run_reference_arm(args, w: dict, name: str) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = cpu_sample_tokens(w)
+    value, sec, threads = cpu_step_tokens_per_s(w, sample, max(1, args.steps), max(0, min(args.warmup, 1)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": f"{name}: {w['desc']}", "tokens_per_step_sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample} of {w['tokens']} tokens per step, full expert shapes, "
+                                   "oracle/moe_oracle.py (CPU restatement of the reference torch path)"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, args.workload)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the B200 kernels are the only implementation (no CPU path)")
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    from xma import _lib, ops
+
+    dtype = torch.float32 if w["dtype"] == "f32" else torch.bfloat16
+    E = w["experts"]
+    if E % world:
+        raise SystemExit(f"{E} experts do not shard over {world} ranks")
+    local = (rank * E // world, (rank + 1) * E // world)
+    moe, gate = make_layer(w, device, dtype, seed=100 + rank, local_experts=local if world > 1 else None)
+    if world > 1:
+        from xma.distributed import ExpertParallelMoE
+
+        layer = ExpertParallelMoE(moe, gate, world_group=dist.group.WORLD)
+    else:
+        with torch.no_grad():
+            moe.gate.weight.copy_(gate)
+        layer = moe
+    x_dev, dy_dev = make_inputs(w, device, dtype, seed=rank, pinned=False)
+    if w is WORKLOADS["c4"]:
+        # uniform random router logits: bypass the gate projection by making it an identity on E features
+        gen = torch.Generator(device="cpu").manual_seed(77 + rank)
+        x_dev[:, :E] = torch.rand(w["tokens"], E, generator=gen).to(device=device, dtype=dtype)
+        with torch.no_grad():
+            g = torch.zeros(E, w["hidden"], device=device, dtype=dtype)
+            g[:, :E] = torch.eye(E, device=device, dtype=dtype)
+            (layer.gate_weight if world > 1 else moe.gate.weight).copy_(g)
+
+    params = [p for p in moe.parameters()]
+
+    def step(x: torch.Tensor, dy: torch.Tensor):
+        for p in params:
+            p.grad = None
+        xin = x.detach().requires_grad_()
+        y, _ = layer(xin)
+        y.backward(dy)
+        return y, xin.grad
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing --------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step(x_dev, dy_dev)
+    barrier()
+    _lib.raise_on_device_status(device)
+
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    ops.STATS.enabled, ops.STATS.timing = True, True
+    ops.STATS.reset()
+    sampler.start()
+    barrier()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for _ in range(args.steps):
+        step(x_dev, dy_dev)
+    t_end.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_total = max_over_ranks(t_start.elapsed_time(t_end))
+    launches = ops.STATS.launches
+    kernel_ms = ops.STATS.elapsed_ms()
+    ops.STATS.enabled = ops.STATS.timing = False
+    _lib.raise_on_device_status(device)
+    ms_per_step = ms_total / args.steps
+    tokens_per_step = w["tokens"] * world
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---- end to end: pinned host inputs in, results out, every step ------------------------------
+    x_pin, dy_pin = make_inputs(w, device, dtype, seed=rank, pinned=True)
+    if w is WORKLOADS["c4"]:
+        x_pin.copy_(x_dev.cpu())
+    y_host = torch.empty_like(x_pin).pin_memory()
+    dx_host = torch.empty_like(x_pin).pin_memory()
+
+    def e2e_step():
+        xd = x_pin.to(device, non_blocking=True)
+        dyd = dy_pin.to(device, non_blocking=True)
+        y, dx = step(xd, dyd)
+        y_host.copy_(y, non_blocking=True)
+        dx_host.copy_(dx, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e_end.record()
+    barrier()
+    e2e_ms = max_over_ranks(e_start.elapsed_time(e_end)) / args.steps
+    e2e_value = tokens_per_step / (e2e_ms * 1e-3)
+    bytes_in = (x_pin.numel() + dy_pin.numel()) * x_pin.element_size()
+    bytes_out = (y_host.numel() + dx_host.numel()) * y_host.element_size()
+
+    # ---- roofline of the dominant kernel family ----------------------------------------------------
+    peaks, peak_kind = measured_peaks()
+    T_local = w["tokens"] * (world if world > 1 else 1) // world  # tokens routed through this rank on average
+    R = T_local * w["top_k"]
+    H, I = w["hidden"], w["inter"]
+    gemm_flops = {  # algorithmic FLOPs per launch
+        "gemm_up_swiglu": 2.0 * R * H * 2 * I, "gemm_down": 2.0 * R * I * H, "gemm_dact_dswiglu": 2.0 * R * H * I,
+        "gemm_dx": 2.0 * R * 2 * I * H, "gemm_dw1": 2.0 * R * 2 * I * H, "gemm_dw2": 2.0 * R * H * I,
+    }
+    per_kernel = {}
+    for name, times in kernel_ms.items():
+        per_kernel[name] = {"launches": len(times), "ms_total": sum(times), "ms_avg": sum(times) / len(times)}
+        if name in gemm_flops:
+            per_kernel[name]["tflops"] = gemm_flops[name] / (per_kernel[name]["ms_avg"] * 1e-3) / 1e12
+    gemm_ms = sum(v["ms_total"] for k, v in per_kernel.items() if k in gemm_flops)
+    gemm_launches = sum(v["launches"] for k, v in per_kernel.items() if k in gemm_flops)
+    roofline = None
+    if gemm_launches:
+        flops_per_step = sum(gemm_flops.values())
+        achieved = flops_per_step * args.steps / (gemm_ms * 1e-3) / 1e12
+        peak = float(peaks.get("bf16_tflops_sustained", PEAK_FALLBACK["bf16_tflops_sustained"]))
+        roofline = {
+            "bound": "tensor", "kernel": "grouped GEMM (tcgen05): up+SwiGLU, down, d-act+dSwiGLU, dX, dW1, dW2",
+            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "peak_source": f"{peak_kind} cuBLAS bf16 sustained", "traffic": None,
+            "share_of_step": gemm_ms / (ms_per_step * args.steps),
+            "frac_of_nominal_2250": achieved / 2250.0,
+        }
+    step_tflops = expert_flops(w, tokens_per_step // world) / (ms_per_step * 1e-3) / 1e12
+
+    # ---- CPU baseline (rank 0, N = 1 only) -----------------------------------------------------------
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        sample = cpu_sample_tokens(w)
+        v, sec, threads = cpu_step_tokens_per_s(w, sample, 1, 1)
+        cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"{sample} of {w['tokens']} tokens, full expert shapes, {sec:.1f} s per step, "
+                         "oracle/moe_oracle.py on the host cores"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['desc']}", "tokens_per_gpu": w["tokens"],
+                       "hidden": H, "intermediate": I, "experts": E, "top_k": w["top_k"],
+                       "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world}, NCCL all-to-all",
+                       "l2_policy": "inputs_exceed_l2 (weights + activations >> 126 MB)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
+            "gpu_launches": launches,
+            "roofline": roofline,
+            "step_tflops_per_gpu": step_tflops,
+            "kernels": per_kernel,
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

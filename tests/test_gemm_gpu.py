@@ -1,0 +1,164 @@
+"""GPU parity of the expert grouped GEMMs: every operand layout and epilogue, on the CUDA-core
+kernels (all dtypes) and on the tcgen05 kernels (bf16 / fp16), against fp64 torch matmuls on the
+same values. Ragged experts, empty experts and widths that are not multiples of the tile."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import REL_TOL, assert_close_rel
+from oracle import moe_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+SIMT, TC = 1, 2
+IMPLS = [pytest.param(SIMT, torch.float32, id="cudacore-f32"), pytest.param(SIMT, torch.bfloat16, id="cudacore-bf16"),
+         pytest.param(TC, torch.bfloat16, id="tcgen05-bf16"), pytest.param(TC, torch.float16, id="tcgen05-f16")]
+
+
+def _plan(counts, E):
+    from xma.layers.moe import build_route_plan
+
+    ids = np.repeat(np.arange(E, dtype=np.int32), counts)
+    np.random.RandomState(0).shuffle(ids)
+    return build_route_plan(torch.from_numpy(ids).cuda().view(-1, 1), E), ids
+
+
+def _grouped(plan, R, width, dtype, seed):
+    """Random grouped buffer whose pad rows are zero (as the gather kernel leaves them)."""
+    rng = np.random.RandomState(seed)
+    full = torch.from_numpy(rng.standard_normal((R, width)).astype(np.float32)).to(dtype).cuda()
+    buf = torch.zeros(plan.row_cap, width, dtype=dtype, device="cuda")
+    src = plan.row_src.long()
+    valid = src >= 0
+    buf[valid] = full[src[valid]]
+    return buf, full
+
+
+CASES = [
+    # counts per expert, Kd, N
+    ([5, 0, 130, 1], 64, 256),
+    ([128, 256, 3], 192, 512),
+    ([300, 7, 0, 0, 129, 64], 576, 264),
+    ([1000, 24], 1024, 2048),
+]
+
+
+@pytest.mark.parametrize("impl,dtype", IMPLS)
+@pytest.mark.parametrize("counts,kd,n", CASES)
+def test_rows_gemm_plain_both_layouts(impl, dtype, counts, kd, n):
+    from xma import _lib, ops
+
+    E, R = len(counts), int(sum(counts))
+    plan, _ = _plan(counts, E)
+    a, a_full = _grouped(plan, R, kd, dtype, seed=1)
+    rng = np.random.RandomState(2)
+    w = torch.from_numpy((rng.standard_normal((E, n, kd)) * 0.05).astype(np.float32)).to(dtype).cuda()
+    src = plan.row_src.long().cpu()
+    tol = REL_TOL[dtype]
+
+    # expected, per grouped row
+    exp = torch.zeros(plan.row_cap, n, dtype=torch.float64)
+    pad = plan.pad_offsets.cpu().tolist()
+    for e in range(E):
+        r0, c = pad[e], counts[e]
+        if c:
+            exp[r0 : r0 + c] = a[r0 : r0 + c].double().cpu() @ w[e].double().cpu().t()
+
+    # weight stored [E, n, kd], grouped output
+    out = torch.full((plan.row_cap, n), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(a, w, _lib.W_NK, out, None, None, plan.tile_expert, plan.tile_prefix, kd, n,
+                           _lib.EPI_PLAIN, impl)
+    used = pad[-1]
+    assert_close_rel(out[:used].cpu(), exp[:used], tol, "grouped out")
+
+    # same product, rows scattered to flat order through row_src
+    ys = torch.full((R, n), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(a, w, _lib.W_NK, ys, None, plan.row_src, plan.tile_expert, plan.tile_prefix, kd, n,
+                           _lib.EPI_PLAIN, impl)
+    valid = src[:used] >= 0
+    exp_scat = torch.zeros(R, n, dtype=torch.float64)
+    exp_scat[src[:used][valid]] = exp[:used][valid]
+    assert_close_rel(ys.cpu(), exp_scat, tol, "scattered out")
+
+    # weight stored [E, kd, n]: out = a @ w_e
+    wt = w.transpose(1, 2).contiguous()
+    out2 = torch.full((plan.row_cap, n), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(a, wt, _lib.W_KN, out2, None, None, plan.tile_expert, plan.tile_prefix, kd, n,
+                           _lib.EPI_PLAIN, impl)
+    assert_close_rel(out2[:used].cpu(), exp[:used], tol, "kn layout")
+    assert _lib.read_and_clear_device_status() == 0
+
+
+@pytest.mark.parametrize("impl,dtype", IMPLS)
+@pytest.mark.parametrize("counts,kd,inter", [([5, 0, 130, 1], 64, 128), ([300, 7, 0, 129], 192, 200),
+                                             ([700, 100], 512, 1024)])
+def test_rows_gemm_swiglu_epilogues(impl, dtype, counts, kd, inter):
+    from xma import _lib, ops
+
+    E, R = len(counts), int(sum(counts))
+    plan, _ = _plan(counts, E)
+    used = int(plan.pad_offsets[-1])
+    a, _ = _grouped(plan, R, kd, dtype, seed=3)
+    rng = np.random.RandomState(4)
+    w1 = torch.from_numpy((rng.standard_normal((E, 2 * inter, kd)) * 0.05).astype(np.float32)).to(dtype).cuda()
+    gu = torch.full((plan.row_cap, 2 * inter), float("nan"), dtype=dtype, device="cuda")
+    act = torch.full((plan.row_cap, inter), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(a, w1, _lib.W_NK, act, gu, None, plan.tile_expert, plan.tile_prefix, kd, 2 * inter,
+                           _lib.EPI_SWIGLU, impl)
+    pad = plan.pad_offsets.cpu().tolist()
+    exp_gu = torch.zeros(plan.row_cap, 2 * inter, dtype=torch.float64)
+    for e in range(E):
+        r0, c = pad[e], counts[e]
+        if c:
+            exp_gu[r0 : r0 + c] = a[r0 : r0 + c].double().cpu() @ w1[e].double().cpu().t()
+    tol = REL_TOL[dtype]
+    assert_close_rel(gu[:used].cpu(), exp_gu[:used], tol, "gate|up")
+    g, u = gu[:used].cpu().float().chunk(2, dim=-1)
+    exp_act = u.double() * g.double() * torch.sigmoid(g.double())  # from the stored (rounded) halves
+    assert_close_rel(act[:used].cpu(), exp_act, 2e-6 if dtype == torch.float32 else tol / 2, "activation")
+
+    # backward epilogue: d(activation) = dys @ W2_e with W2 stored [E, H, I]
+    H = kd
+    dys, _ = _grouped(plan, R, H, dtype, seed=5)
+    w2 = torch.from_numpy((rng.standard_normal((E, H, inter)) * 0.05).astype(np.float32)).to(dtype).cuda()
+    dgu = torch.full((plan.row_cap, 2 * inter), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(dys, w2, _lib.W_KN, dgu, gu, None, plan.tile_expert, plan.tile_prefix, H, inter,
+                           _lib.EPI_DSWIGLU, impl)
+    d_act = torch.zeros(plan.row_cap, inter, dtype=torch.float64)
+    for e in range(E):
+        r0, c = pad[e], counts[e]
+        if c:
+            d_act[r0 : r0 + c] = dys[r0 : r0 + c].double().cpu() @ w2[e].double().cpu()
+    gd, ud = g.double(), u.double()
+    s = torch.sigmoid(gd)
+    exp_dg = d_act[:used] * ud * s * (1 + gd * (1 - s))
+    exp_du = d_act[:used] * gd * s
+    assert_close_rel(dgu[:used, :inter].cpu(), exp_dg, 2 * tol, "d gate")
+    assert_close_rel(dgu[:used, inter:].cpu(), exp_du, 2 * tol, "d up")
+    assert _lib.read_and_clear_device_status() == 0
+
+
+@pytest.mark.parametrize("impl,dtype", IMPLS)
+@pytest.mark.parametrize("counts,m,n", [([5, 0, 130, 1], 64, 256), ([300, 7, 0, 129], 136, 264),
+                                        ([1000, 24, 64], 512, 384)])
+def test_dw_gemm(impl, dtype, counts, m, n):
+    from xma import _lib, ops
+
+    E, R = len(counts), int(sum(counts))
+    plan, _ = _plan(counts, E)
+    x, _ = _grouped(plan, R, m, dtype, seed=6)
+    y, _ = _grouped(plan, R, n, dtype, seed=7)
+    dw = torch.full((E, m, n), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_dw_(x, y, plan.counts, plan.pad_offsets, dw, impl)
+    pad = plan.pad_offsets.cpu().tolist()
+    exp = torch.zeros(E, m, n, dtype=torch.float64)
+    for e in range(E):
+        r0, c = pad[e], counts[e]
+        if c:
+            exp[e] = x[r0 : r0 + c].double().cpu().t() @ y[r0 : r0 + c].double().cpu()
+    assert_close_rel(dw.cpu(), exp, REL_TOL[dtype], "dW")
+    for e in range(E):
+        if counts[e] == 0:
+            assert bool((dw[e] == 0).all()), "experts without rows must get exactly zero"
+    assert _lib.read_and_clear_device_status() == 0

@@ -1,0 +1,61 @@
+"""GPU parity of the row-movement kernels (gather into expert order, weighted combine, its backward)."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close_rel
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,K,H", [(7, 2, 64), (300, 8, 576), (1000, 4, 2048)])
+def test_gather_combine(dtype, T, K, H):
+    from xma import ops
+
+    rng = np.random.RandomState(T + K)
+    x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(dtype).cuda()
+    R = T * K
+    rows = R + 256
+    row_src = np.full(rows, -1, dtype=np.int32)
+    pos = np.sort(rng.choice(rows, size=R, replace=False))
+    perm = rng.permutation(R).astype(np.int32)
+    row_src[pos] = perm
+    row_src_d = torch.from_numpy(row_src).cuda()
+    coeff = torch.from_numpy(rng.standard_normal(R).astype(np.float32)).to(dtype).cuda()
+
+    out = torch.full((rows, H), 7.0, dtype=dtype, device="cuda")
+    ops.gather_rows_(x, row_src_d, None, K, None, out)
+    ref = torch.zeros(rows, H, dtype=dtype, device="cuda")
+    ref[torch.from_numpy(pos).cuda()] = x[torch.from_numpy(perm // K).long().cuda()]
+    assert torch.equal(out, ref)
+
+    out2 = torch.full((rows, H), 7.0, dtype=dtype, device="cuda")
+    ops.gather_rows_(x, row_src_d, coeff, K, None, out2)
+    ref2 = torch.zeros(rows, H, dtype=torch.float32, device="cuda")
+    idx = torch.from_numpy(perm).long().cuda()
+    ref2[torch.from_numpy(pos).cuda()] = x[idx // K].float() * coeff[idx].float().unsqueeze(-1)
+    assert torch.equal(out2, ref2.to(dtype))
+
+    # rows_in_use limits the rows that are touched
+    lim = torch.tensor([128], dtype=torch.int32, device="cuda")
+    out3 = torch.full((rows, H), 7.0, dtype=dtype, device="cuda")
+    ops.gather_rows_(x, row_src_d, None, K, lim, out3)
+    assert torch.equal(out3[:128], ref[:128]) and bool((out3[128:] == 7.0).all())
+
+    ys = torch.from_numpy(rng.standard_normal((R, H)).astype(np.float32)).to(dtype).cuda()
+    w = torch.from_numpy(rng.random_sample((T, K)).astype(np.float32)).to(dtype).cuda()
+    y = torch.empty(T, H, dtype=dtype, device="cuda")
+    ops.combine_rows_(ys, w, K, y)
+    y_ref = (ys.double().view(T, K, H) * w.double().unsqueeze(-1)).sum(1)
+    tol = 1e-6 if dtype == torch.float32 else (2e-3 if dtype == torch.float16 else 1e-2)
+    assert_close_rel(y, y_ref, tol, "combine")
+    ops.combine_rows_(ys, None, K, y)
+    assert_close_rel(y, ys.double().view(T, K, H).sum(1), tol, "combine (plain sum)")
+
+    dy = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(dtype).cuda()
+    dw = torch.empty(T, K, dtype=dtype, device="cuda")
+    ops.combine_bwd_(ys, dy, K, dw)
+    dw_ref = (ys.double().view(T, K, H) * dy.double().unsqueeze(1)).sum(-1)
+    assert_close_rel(dw, dw_ref, 1e-5 if dtype == torch.float32 else tol, "combine backward")
