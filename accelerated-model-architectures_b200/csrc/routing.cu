@@ -10,6 +10,8 @@
 // the stable ascending order (ties by flat index), top-k ties go to the lowest expert index.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace xma {
 
 // ------------------------------------------------------------------------------------------------
@@ -666,6 +668,66 @@ int xma_b200_route_topk_softmax_bwd(const void* logits, int dtype, int64_t logit
                                                        num_experts, top_k, d_logits, stream);
     }
     return XMA_ERR_BAD_DTYPE;
+}
+
+}  // extern "C"
+
+// ================================================================================================
+// Counting sort without caller-provided scratch
+// ================================================================================================
+// Some hosts of this library must not allocate device memory while they run: a serving engine that
+// has handed its whole memory budget to a pool at start-up, or a step that sits between other
+// frameworks' allocators and may not disturb them. For those callers the look-back scan's scratch
+// lives in this fixed array instead of a caller buffer. Every GPU that loads the library holds it
+// until the process exits.
+#define XMA_STATIC_SORT_SCRATCH_BYTES (256 + 256 * 256 * 8) /* tile counter + 256 tiles x 256 experts */
+
+static __device__ __align__(256) unsigned char g_static_sort_scratch[XMA_STATIC_SORT_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" {
+
+// Largest scratch the static variant can serve; the scratch a call needs is
+// xma_b200_count_sort_scratch_bytes(n, num_experts).
+int64_t xma_b200_count_sort_static_scratch_limit(void) { return XMA_STATIC_SORT_SCRATCH_BYTES; }
+
+// Same outputs as xma_b200_count_sort, bit for bit, with the scratch taken from the library's own
+// fixed device array. Nothing is allocated or freed, here or in anything this calls.
+//  - The first call on each device looks up the array's device address (the name is only a host-side
+//    handle, not an address a kernel could use) with that device current; make that first call
+//    before any stream capture begins.
+//  - All calls on a device share the one array. It is cleared at the start of every call; two calls
+//    whose kernels overlap on the GPU (different streams, no ordering) would corrupt each other.
+//  - Problems whose scratch exceeds the limit are refused with XMA_ERR_TOO_LARGE.
+int xma_b200_count_sort_static(const void* ids, int id_dtype, int64_t n, int num_experts, uint32_t* counts,
+                               int32_t* offsets_incl, int32_t* pad_offsets, int32_t* tile_prefix,
+                               int32_t* tile_expert, int64_t tile_cap, int32_t* sorted_expert_idxs,
+                               int32_t* sorted_scattered_idxs, int32_t* row_src, int64_t row_cap,
+                               int* device_status, cudaStream_t stream) {
+    if (n < 0 || num_experts <= 0 || num_experts > xma::SORT_MAX_BINS) return XMA_ERR_BAD_SHAPE;
+    const int64_t need = static_cast<int64_t>(xma::sort_scratch_bytes(n, num_experts));
+    if (need > XMA_STATIC_SORT_SCRATCH_BYTES) return XMA_ERR_TOO_LARGE;
+    int dev = -1;
+    XMA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return XMA_ERR_UNSUPPORTED;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (!g_static_scratch_addr[dev]) {
+            void* p = nullptr;
+            XMA_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_sort_scratch));
+            g_static_scratch_addr[dev] = p;
+        }
+        scratch = g_static_scratch_addr[dev];
+    }
+    return xma_b200_count_sort(ids, id_dtype, n, num_experts, counts, offsets_incl, pad_offsets, tile_prefix,
+                               tile_expert, tile_cap, sorted_expert_idxs, sorted_scattered_idxs, row_src, row_cap,
+                               scratch, XMA_STATIC_SORT_SCRATCH_BYTES, device_status, stream);
 }
 
 }  // extern "C"

@@ -43,6 +43,9 @@ _SIGNATURES = {
     "xma_b200_tile_capacity": [c_int64, c_int],
     "xma_b200_count_sort": [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p],
+    "xma_b200_count_sort_static_scratch_limit": [],
+    "xma_b200_count_sort_static": [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     "xma_b200_gather_rows": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int64,
                              c_void_p, c_int64, c_void_p],
     "xma_b200_combine_rows": [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64,
@@ -67,6 +70,7 @@ _RESTYPES = {
     "xma_b200_error_string": c_char_p,
     "xma_b200_count_sort_scratch_bytes": c_int64,
     "xma_b200_tile_capacity": c_int64,
+    "xma_b200_count_sort_static_scratch_limit": c_int64,
 }
 
 

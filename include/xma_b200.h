@@ -86,6 +86,24 @@ int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_expert
                         int32_t* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes,
                         int* device_status, cudaStream_t stream);
 
+/* xma_b200_count_sort for callers that may not allocate device memory while they run (an engine
+ * that gave its whole budget to a pool at start-up, a step wedged between other allocators): the
+ * scratch comes from a fixed array inside the library (held by every GPU that loads it, until
+ * exit) instead of a caller buffer, and nothing is allocated or freed. Outputs are identical to
+ * xma_b200_count_sort. Limits: the scratch the problem needs
+ * (xma_b200_count_sort_scratch_bytes) must not exceed
+ * xma_b200_count_sort_static_scratch_limit() = 524544 bytes, e.g. up to 1 Mi ids with 256
+ * experts, else XMA_ERR_TOO_LARGE (-8). The first call on a device resolves the array's device
+ * address; issue it before any stream capture. Calls on one device share the array (cleared at
+ * the start of each call); calls that overlap on the GPU race.
+ * This entry point has no counterpart in the reference. */
+int64_t xma_b200_count_sort_static_scratch_limit(void);
+int xma_b200_count_sort_static(const void* ids, int id_dtype, int64_t n, int num_experts, uint32_t* counts,
+                               int32_t* offsets_incl, int32_t* pad_offsets, int32_t* tile_prefix,
+                               int32_t* tile_expert, int64_t tile_cap, int32_t* sorted_expert_idxs,
+                               int32_t* sorted_scattered_idxs, int32_t* row_src, int64_t row_cap,
+                               int* device_status, cudaStream_t stream);
+
 /* ---- row movement --------------------------------------------------------------------------- */
 
 /* out[p, :] = src[row_src[p] / fan_out, :] * coeff[row_src[p]]  (coeff may be NULL; rows with
