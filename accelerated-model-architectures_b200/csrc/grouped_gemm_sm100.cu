@@ -8,10 +8,11 @@
 // grouped layout (rows of an expert contiguous, padded to 128), outputs either stay grouped or are
 // scattered through `row_map` by the epilogue.
 //
-// One CTA per SM, 192 threads:
+// One CTA per SM, 320 threads:
 //   warp 0      : TMA producer (one lane)            -> full[stage]
 //   warp 1      : tensor-memory allocation, MMA issue (one lane) -> empty[stage], acc_full[buf]
-//   warps 2..5  : epilogue, one warp per 32-lane quarter of tensor memory -> acc_empty[buf]
+//   warps 2..9  : epilogue; warp w reads the 32-lane quarter (w & 3) of tensor memory and half of
+//                 the tile's columns -> acc_empty[buf]
 // The accumulator is double buffered (2 x 256 columns), so the epilogue of a tile overlaps the
 // main loop of the next one. Every wait is bounded: on expiry the CTA raises a flag, sets the
 // timeout bit of the device status word, leaves its loops and releases tensor memory.
@@ -29,7 +30,8 @@ constexpr int BN = 256;           // accumulator columns per tile
 constexpr int BK = 64;            // reduction elements per stage (64 x 2 bytes = one 128-byte swizzle row)
 constexpr int UMMA_K = 16;        // reduction elements per tcgen05.mma for 16-bit inputs
 constexpr int STAGES = 4;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;     // two warps per tensor-memory lane quarter, each takes half the columns
+constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -200,6 +202,10 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Logistic function for the 16-bit epilogues: ex2.approx + rcp.approx (a few ulp in fp32, far below
+// the rounding of the bf16/fp16 result it feeds).
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
 template <typename T>
 __device__ __forceinline__ float round_to(float x) {
     return to_f32(from_f32<T>(x));
@@ -260,7 +266,7 @@ __device__ __forceinline__ uint32_t prologue(const Shared& s, int warp, int lane
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s.acc_full[i], 1);
-            mbar_init(&s.acc_empty[i], 128);
+            mbar_init(&s.acc_empty[i], EPI_WARPS * 32);
         }
         *s.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -401,14 +407,13 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
         }
     } else {
-        const int quarter = warp & 3;  // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
+        const int quarter = warp & 3;          // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
+        const int col_half = (warp - 2) >> 2;  // which half of the tile's columns this warp stores
         const int row_in_tile = quarter * 32 + lane;
         uint32_t lt = 0;
         for (int64_t w = blockIdx.x; w < total; w += gridDim.x, ++lt) {
             const RowsWork wk = decode_rows(s.tile_prefix, E, n_tiles, w);
             const uint32_t buf = lt & 1u;
-            if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
-            tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
 
@@ -416,8 +421,10 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 int64_t dst = r;
                 if (row_map) dst = row_map[r];
                 const int n0 = wk.n_tile * BN;
+                if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
+                tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
                     uint32_t v[32];
                     tmem_ld32(taddr + c * 32, v);
                     tmem_ld_wait();
@@ -434,8 +441,10 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 }
             } else if (EPI == EPI_SWIGLU) {
                 const int j0 = wk.n_tile * 128;
+                if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
+                tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = col_half * 2; c < col_half * 2 + 2; ++c) {
                     uint32_t g[32], u[32];
                     tmem_ld32(taddr + c * 32, g);
                     tmem_ld32(taddr + 128 + c * 32, u);
@@ -453,7 +462,7 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                 for (int t = 0; t < 8; ++t) {
                                     gr[t] = round_to<T>(__uint_as_float(g[8 * i + t]));
                                     ur[t] = round_to<T>(__uint_as_float(u[8 * i + t]));
-                                    ac[t] = ur[t] * gr[t] * sigmoid_f32(gr[t]);
+                                    ac[t] = ur[t] * gr[t] * fast_sigmoid(gr[t]);
                                 }
                                 *reinterpret_cast<uint4*>(pg + 8 * i) = pack8<T>(gr);
                                 *reinterpret_cast<uint4*>(pu + 8 * i) = pack8<T>(ur);
@@ -464,33 +473,47 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 }
             } else {  // EPI_DSWIGLU: n is the activation width
                 const int n0 = wk.n_tile * BN;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                const T* pg_row = aux + r * aux_stride;
+                T* pd_row = out + r * out_stride;
+                // gate|up of this row do not depend on the accumulator: fetch the first chunk before
+                // waiting for it, and every later chunk while the previous one is being computed
+                uint4 gq[2][4], uq[2][4];
+                auto fetch = [&](int c, int b) {
+                    const int col = n0 + c * 32;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (col + 8 * i < n) {
+                            gq[b][i] = *reinterpret_cast<const uint4*>(pg_row + col + 8 * i);
+                            uq[b][i] = *reinterpret_cast<const uint4*>(pg_row + n + col + 8 * i);
+                        }
+                    }
+                };
+                fetch(col_half * 4, 0);
+                if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int c = col_half * 4 + cc;
+                    if (cc + 1 < 4) fetch(c + 1, (cc + 1) & 1);
                     uint32_t v[32];
                     tmem_ld32(taddr + c * 32, v);
                     tmem_ld_wait();
                     const int col = n0 + c * 32;
-                    if (col < n) {
-                        const T* pg = aux + r * aux_stride + col;
-                        const T* pu = pg + n;
-                        T* pdg = out + r * out_stride + col;
-                        T* pdu = pdg + n;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            if (col + 8 * i < n) {
-                                float gg[8], uu[8], dg[8], du[8];
-                                unpack8<T>(*reinterpret_cast<const uint4*>(pg + 8 * i), gg);
-                                unpack8<T>(*reinterpret_cast<const uint4*>(pu + 8 * i), uu);
+                    for (int i = 0; i < 4; ++i) {
+                        if (col + 8 * i < n) {
+                            float gg[8], uu[8], dg[8], du[8];
+                            unpack8<T>(gq[cc & 1][i], gg);
+                            unpack8<T>(uq[cc & 1][i], uu);
 #pragma unroll
-                                for (int t = 0; t < 8; ++t) {
-                                    const float d = __uint_as_float(v[8 * i + t]);
-                                    const float sg = sigmoid_f32(gg[t]);
-                                    dg[t] = d * uu[t] * sg * (1.0f + gg[t] * (1.0f - sg));
-                                    du[t] = d * gg[t] * sg;
-                                }
-                                *reinterpret_cast<uint4*>(pdg + 8 * i) = pack8<T>(dg);
-                                *reinterpret_cast<uint4*>(pdu + 8 * i) = pack8<T>(du);
+                            for (int t = 0; t < 8; ++t) {
+                                const float d = __uint_as_float(v[8 * i + t]);
+                                const float sg = fast_sigmoid(gg[t]);
+                                dg[t] = d * uu[t] * sg * (1.0f + gg[t] * (1.0f - sg));
+                                du[t] = d * gg[t] * sg;
                             }
+                            *reinterpret_cast<uint4*>(pd_row + col + 8 * i) = pack8<T>(dg);
+                            *reinterpret_cast<uint4*>(pd_row + n + col + 8 * i) = pack8<T>(du);
                         }
                     }
                 }
@@ -597,6 +620,7 @@ dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     } else {
         const int quarter = warp & 3;
+        const int col_half = (warp - 2) >> 2;
         const int row_in_tile = quarter * 32 + lane;
         uint32_t lt = 0;
         for (int64_t w = blockIdx.x; w < total; w += gridDim.x) {
@@ -608,7 +632,8 @@ dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (empty_expert) {
                 if (row < m) {
                     const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                    for (int c = 0; c < BN && n0 + c < n; c += 8) *reinterpret_cast<uint4*>(dst + c) = z;
+                    for (int c = col_half * (BN / 2); c < (col_half + 1) * (BN / 2) && n0 + c < n; c += 8)
+                        *reinterpret_cast<uint4*>(dst + c) = z;
                 }
                 continue;
             }
@@ -617,7 +642,7 @@ dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
                 uint32_t v[32];
                 tmem_ld32(taddr + c * 32, v);
                 tmem_ld_wait();

@@ -86,7 +86,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -280,7 +280,7 @@ def main() -> None:
             g[:, :E] = torch.eye(E, device=device, dtype=dtype)
             (layer.gate_weight if world > 1 else moe.gate.weight).copy_(g)
 
-    params = [p for p in moe.parameters()]
+    params = list(layer.parameters())
 
     def step(x: torch.Tensor, dy: torch.Tensor):
         for p in params:
@@ -337,20 +337,48 @@ def main() -> None:
     y_host = torch.empty_like(x_pin).pin_memory()
     dx_host = torch.empty_like(x_pin).pin_memory()
 
-    def e2e_step():
-        xd = x_pin.to(device, non_blocking=True)
-        dyd = dy_pin.to(device, non_blocking=True)
-        y, dx = step(xd, dyd)
-        y_host.copy_(y, non_blocking=True)
-        dx_host.copy_(dx, non_blocking=True)
+    # Every step's inputs come from pinned host memory and its results go back to pinned host memory.
+    # The copies run on their own streams so that the upload of step s+1 and the download of step s-1
+    # overlap the kernels of step s (double-buffered device inputs); all of it is inside the timed region.
+    main_stream = torch.cuda.current_stream()
+    h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
+    x_buf = [torch.empty_like(x_dev) for _ in range(2)]
+    dy_buf = [torch.empty_like(dy_dev) for _ in range(2)]
+    uploaded = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
 
-    for _ in range(2):
-        e2e_step()
+    def upload(s: int) -> None:
+        b = s & 1
+        h2d.wait_event(consumed[b])  # the step that last read this buffer pair has finished
+        with torch.cuda.stream(h2d):
+            x_buf[b].copy_(x_pin, non_blocking=True)
+            dy_buf[b].copy_(dy_pin, non_blocking=True)
+            uploaded[b].record(h2d)
+
+    def e2e_run(steps: int) -> None:
+        for ev in consumed:
+            ev.record(main_stream)
+        upload(0)
+        for s in range(steps):
+            b = s & 1
+            if s + 1 < steps:
+                upload(s + 1)
+            main_stream.wait_event(uploaded[b])
+            y, dx = step(x_buf[b], dy_buf[b])
+            consumed[b].record(main_stream)
+            d2h.wait_event(consumed[b])
+            with torch.cuda.stream(d2h):
+                y_host.copy_(y, non_blocking=True)
+                dx_host.copy_(dx, non_blocking=True)
+            y.record_stream(d2h)
+            dx.record_stream(d2h)
+        main_stream.wait_stream(d2h)
+
+    e2e_run(2)
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
-    for _ in range(args.steps):
-        e2e_step()
+    e2e_run(args.steps)
     e_end.record()
     barrier()
     e2e_ms = max_over_ranks(e_start.elapsed_time(e_end)) / args.steps
