@@ -8,16 +8,17 @@
 // grouped layout (rows of an expert contiguous, padded to 128), outputs either stay grouped or are
 // scattered through `row_map` by the epilogue.
 //
-// One CTA per SM, 320 threads:
+// One CTA per SM, 192 or 320 threads:
 //   warp 0      : TMA producer (one lane)            -> full[stage]
 //   warp 1      : tensor-memory allocation, MMA issue (one lane) -> empty[stage], acc_full[buf]
-//   warps 2..9  : epilogue; warp w reads the 32-lane quarter (w & 3) of tensor memory and half of
-//                 the tile's columns -> acc_empty[buf]
+//   warps 2..   : epilogue (4 or 8 warps); warp w reads the 32-lane quarter (w & 3) of tensor memory
+//                 and, with 8 warps, half of the tile's columns -> acc_empty[buf]
 // The accumulator is double buffered (2 x 256 columns), so the epilogue of a tile overlaps the
 // main loop of the next one. Every wait is bounded: on expiry the CTA raises a flag, sets the
 // timeout bit of the device status word, leaves its loops and releases tensor memory.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "gemm_internal.h"
@@ -30,8 +31,9 @@ constexpr int BN = 256;           // accumulator columns per tile
 constexpr int BK = 64;            // reduction elements per stage (64 x 2 bytes = one 128-byte swizzle row)
 constexpr int UMMA_K = 16;        // reduction elements per tcgen05.mma for 16-bit inputs
 constexpr int STAGES = 4;
-constexpr int EPI_WARPS = 8;     // two warps per tensor-memory lane quarter, each takes half the columns
-constexpr int THREADS = 64 + EPI_WARPS * 32;
+constexpr int MAX_EPI_WARPS = 8;  // 4 or 8 epilogue warps (block size 192 or 320): with 8, two warps share a
+                                  // tensor-memory lane quarter and each takes half of the tile's columns
+constexpr int THREADS = 64 + MAX_EPI_WARPS * 32;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -266,7 +268,7 @@ __device__ __forceinline__ uint32_t prologue(const Shared& s, int warp, int lane
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s.acc_full[i], 1);
-            mbar_init(&s.acc_empty[i], EPI_WARPS * 32);
+            mbar_init(&s.acc_empty[i], blockDim.x - 64);
         }
         *s.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -338,7 +340,7 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const Shared s = carve_smem(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    for (int i = threadIdx.x; i <= E; i += THREADS) s.tile_prefix[i] = g_tile_prefix[i];
+    for (int i = threadIdx.x; i <= E; i += blockDim.x) s.tile_prefix[i] = g_tile_prefix[i];
     const uint32_t tmem_base = prologue(s, warp, lane);
 
     constexpr bool B_MN = (WL == W_KN);
@@ -408,7 +410,9 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
     } else {
         const int quarter = warp & 3;          // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
-        const int col_half = (warp - 2) >> 2;  // which half of the tile's columns this warp stores
+        const int parts = (static_cast<int>(blockDim.x) - 64) >> 7;  // warps per lane quarter: 1 or 2
+        const int part = (warp - 2) >> 2;                            // which share of the columns this warp stores
+        const int chunks = (BN / 32) / parts;                        // 32-column chunks per warp
         const int row_in_tile = quarter * 32 + lane;
         uint32_t lt = 0;
         for (int64_t w = blockIdx.x; w < total; w += gridDim.x, ++lt) {
@@ -424,7 +428,7 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
+                for (int c = part * chunks; c < (part + 1) * chunks; ++c) {
                     uint32_t v[32];
                     tmem_ld32(taddr + c * 32, v);
                     tmem_ld_wait();
@@ -444,7 +448,7 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = col_half * 2; c < col_half * 2 + 2; ++c) {
+                for (int c = part * (chunks / 2); c < (part + 1) * (chunks / 2); ++c) {
                     uint32_t g[32], u[32];
                     tmem_ld32(taddr + c * 32, g);
                     tmem_ld32(taddr + 128 + c * 32, u);
@@ -488,13 +492,14 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                     }
                 };
-                fetch(col_half * 4, 0);
+                fetch(part * chunks, 0);
                 if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int c = col_half * 4 + cc;
-                    if (cc + 1 < 4) fetch(c + 1, (cc + 1) & 1);
+                for (int cc = 0; cc < BN / 32; ++cc) {
+                    if (cc >= chunks) break;
+                    const int c = part * chunks + cc;
+                    if (cc + 1 < chunks) fetch(c + 1, (cc + 1) & 1);
                     uint32_t v[32];
                     tmem_ld32(taddr + c * 32, v);
                     tmem_ld_wait();
@@ -620,7 +625,9 @@ dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     } else {
         const int quarter = warp & 3;
-        const int col_half = (warp - 2) >> 2;
+        const int parts = (static_cast<int>(blockDim.x) - 64) >> 7;
+        const int part = (warp - 2) >> 2;
+        const int chunks = (BN / 32) / parts;
         const int row_in_tile = quarter * 32 + lane;
         uint32_t lt = 0;
         for (int64_t w = blockIdx.x; w < total; w += gridDim.x) {
@@ -632,7 +639,7 @@ dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (empty_expert) {
                 if (row < m) {
                     const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                    for (int c = col_half * (BN / 2); c < (col_half + 1) * (BN / 2) && n0 + c < n; c += 8)
+                    for (int c = part * chunks * 32; c < (part + 1) * chunks * 32 && n0 + c < n; c += 8)
                         *reinterpret_cast<uint4*>(dst + c) = z;
                 }
                 continue;
@@ -642,7 +649,7 @@ dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
+            for (int c = part * chunks; c < (part + 1) * chunks; ++c) {
                 uint32_t v[32];
                 tmem_ld32(taddr + c * 32, v);
                 tmem_ld_wait();
@@ -719,6 +726,18 @@ static bool device_is_sm100() {
     return cached == 1;
 }
 
+// Epilogue warps per kernel: 4 (block of 192 threads) or 8 (320). XMA_B200_EPI_WARPS=4|8 overrides
+// the per-kernel default (tuning knob).
+static int block_threads(int default_epi_warps) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("XMA_B200_EPI_WARPS");
+        forced = (e && (e[0] == '4' || e[0] == '8')) ? (e[0] - '0') : 0;
+    }
+    const int warps = forced ? forced : default_epi_warps;
+    return 64 + 32 * warps;
+}
+
 template <typename K>
 static int set_smem(K kernel) {
     return static_cast<int>(
@@ -731,7 +750,7 @@ static int launch_rows(const RowsGemmArgs& g, const CUtensorMap& ta, const CUten
     int rc = set_smem(kernel);
     if (rc) return rc;
     const uint32_t idesc = make_idesc(g.dtype, false, WL == W_KN);
-    kernel<<<num_sms(), THREADS, SMEM_BYTES, g.stream>>>(
+    kernel<<<num_sms(), block_threads(EPI == EPI_DSWIGLU ? 8 : 4), SMEM_BYTES, g.stream>>>(
         ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
         g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
     return static_cast<int>(cudaGetLastError());
@@ -806,14 +825,14 @@ int dw_gemm_tc(const DwGemmArgs& g) {
         auto kernel = tc::dw_gemm_tc_kernel<__nv_bfloat16>;
         int rc = tc::set_smem(kernel);
         if (rc) return rc;
-        kernel<<<num_sms(), tc::THREADS, tc::SMEM_BYTES, g.stream>>>(
+        kernel<<<num_sms(), tc::block_threads(4), tc::SMEM_BYTES, g.stream>>>(
             tx, ty, g.counts, g.pad_offsets, g.num_experts, static_cast<int>(g.m), static_cast<int>(g.n),
             static_cast<__nv_bfloat16*>(g.dw), idesc, g.device_status);
     } else {
         auto kernel = tc::dw_gemm_tc_kernel<__half>;
         int rc = tc::set_smem(kernel);
         if (rc) return rc;
-        kernel<<<num_sms(), tc::THREADS, tc::SMEM_BYTES, g.stream>>>(
+        kernel<<<num_sms(), tc::block_threads(4), tc::SMEM_BYTES, g.stream>>>(
             tx, ty, g.counts, g.pad_offsets, g.num_experts, static_cast<int>(g.m), static_cast<int>(g.n),
             static_cast<__half*>(g.dw), idesc, g.device_status);
     }

@@ -155,8 +155,7 @@ class ExpertParallelMoE(nn.Module):
 
         with torch.no_grad():
             local_plan = build_route_plan(local_ids.view(-1, 1), e_local)
-        ones = torch.ones(recv.size(0), 1, dtype=x.dtype, device=x.device)
-        out = _FusedSwiGLUExperts.apply(recv, self.local.c_fc.weight, self.local.c_proj.weight, ones,
+        out = _FusedSwiGLUExperts.apply(recv, self.local.c_fc.weight, self.local.c_proj.weight, None,
                                         *_plan_tensors(local_plan))
 
         back = _AllToAllRows.apply(out, recv_splits, send_splits, self.group)

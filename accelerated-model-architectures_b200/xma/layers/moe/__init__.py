@@ -208,13 +208,16 @@ class _DownProjectionExperts(torch.autograd.Function):
 
 class _FusedSwiGLUExperts(torch.autograd.Function):
     """Whole expert block with SwiGLU fused into the GEMM epilogues:
-    y[t] = sum_k w[t,k] * (swiglu(x[t] @ W1_e^T) @ W2_e^T), e = selected_experts[t, k]."""
+    y[t] = sum_k w[t,k] * (swiglu(x[t] @ W1_e^T) @ W2_e^T), e = selected_experts[t, k].
+    With `router_weights=None` every row of x is one routed row (top_k = 1) and the unweighted expert
+    output is returned in the order of x (the expert-parallel layer combines on the home rank)."""
 
     @staticmethod
     def forward(ctx, x, w1, w2, router_weights, counts, pad_offsets, tile_prefix, tile_expert, row_src):
         E, two_i, H = w1.shape
         I = two_i // 2
-        T, K = router_weights.shape
+        weighted = router_weights is not None
+        T, K = router_weights.shape if weighted else (x.size(0), 1)
         row_cap = row_src.numel()
         opts = dict(dtype=x.dtype, device=x.device)
         impl = ops.GEMM_IMPL
@@ -228,21 +231,30 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         ys = torch.empty(T * K, H, **opts)
         ops.grouped_gemm_rows_(act, w2, W_NK, ys, None, row_src, tile_expert, tile_prefix, I, H, EPI_PLAIN, impl,
                                tag="gemm_down")
-        router_weights = router_weights.contiguous()
-        y = torch.empty(T, H, **opts)
-        ops.combine_rows_(ys, router_weights, K, y)
-
-        ctx.save_for_backward(xs, gu, act, ys, w1, w2, router_weights, counts, pad_offsets, tile_prefix,
-                              tile_expert, row_src)
+        if weighted:
+            router_weights = router_weights.contiguous()
+            y = torch.empty(T, H, **opts)
+            ops.combine_rows_(ys, router_weights, K, y)
+            ctx.save_for_backward(xs, gu, act, ys, w1, w2, router_weights, counts, pad_offsets, tile_prefix,
+                                  tile_expert, row_src)
+        else:
+            y = ys
+            ctx.save_for_backward(xs, gu, act, w1, w2, counts, pad_offsets, tile_prefix, tile_expert, row_src)
+        ctx.weighted = weighted
+        ctx.tokens, ctx.top_k = T, K
         return y
 
     @staticmethod
     def backward(ctx, grad_out):
-        (xs, gu, act, ys, w1, w2, router_weights, counts, pad_offsets, tile_prefix, tile_expert,
-         row_src) = ctx.saved_tensors
+        if ctx.weighted:
+            (xs, gu, act, ys, w1, w2, router_weights, counts, pad_offsets, tile_prefix, tile_expert,
+             row_src) = ctx.saved_tensors
+        else:
+            xs, gu, act, w1, w2, counts, pad_offsets, tile_prefix, tile_expert, row_src = ctx.saved_tensors
+            ys = router_weights = None
         E, two_i, H = w1.shape
         I = two_i // 2
-        T, K = router_weights.shape
+        T, K = ctx.tokens, ctx.top_k
         row_cap = row_src.numel()
         opts = dict(dtype=xs.dtype, device=xs.device)
         impl = ops.GEMM_IMPL
@@ -250,12 +262,13 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         need_x, need_w1, need_w2, need_rw = ctx.needs_input_grad[:4]
 
         d_rw = None
-        if need_rw:
+        if need_rw and ctx.weighted:
             d_rw = torch.empty_like(router_weights)
             ops.combine_bwd_(ys, grad_out, K, d_rw)
 
         dys = torch.empty(row_cap, H, **opts)
-        ops.gather_rows_(grad_out, row_src, router_weights.view(-1), K, pad_offsets[E:], dys)
+        coeff = router_weights.view(-1) if ctx.weighted else None
+        ops.gather_rows_(grad_out, row_src, coeff, K, pad_offsets[E:], dys)
 
         d_w2 = None
         if need_w2:
@@ -274,8 +287,11 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
                 dxs = torch.empty(T * K, H, **opts)
                 ops.grouped_gemm_rows_(dgu, w1, W_KN, dxs, None, row_src, tile_expert, tile_prefix, two_i, H,
                                        EPI_PLAIN, impl, tag="gemm_dx")
-                d_x = torch.empty(T, H, **opts)
-                ops.combine_rows_(dxs, None, K, d_x)
+                if K == 1:
+                    d_x = dxs
+                else:
+                    d_x = torch.empty(T, H, **opts)
+                    ops.combine_rows_(dxs, None, K, d_x)
         return d_x, d_w1, d_w2, d_rw, None, None, None, None, None
 
 

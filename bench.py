@@ -221,6 +221,90 @@ def run_reference_arm(args, w: dict, name: str) -> None:
 
 
 # ---------------------------------------------------------------------------------------------------
+# configs[4]: routing microbench (HBM-bound kernels only)
+# ---------------------------------------------------------------------------------------------------
+def zipf_ids(n: int, bins: int, s: float, seed: int) -> np.ndarray:
+    rng = np.random.RandomState(seed)
+    p = 1.0 / np.arange(1, bins + 1) ** s
+    cdf = np.cumsum(p / p.sum())
+    ranks = np.searchsorted(cdf, rng.random_sample(n), side="right").clip(0, bins - 1)
+    return rng.permutation(bins)[ranks].astype(np.int32)
+
+
+def run_routing_microbench(args) -> None:
+    """continuous_count, the counting sort and the row permute of BASELINE configs[4]: 64 Mi int32 ids
+    over 256 bins (uniform and Zipf(1.1)) and rows of 2048 bf16. The 64 Mi x 2048 token buffer of the
+    config is 256 GiB and does not fit a B200, so the permute moves the first `rows` rows (8 Mi =
+    32 GiB in + 32 GiB out) with the sort permutation of the first `rows` ids; GB/s does not depend on
+    the row count at this size."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    from xma import ops
+    from xma.functional import continuous_count
+    from xma.layers.moe import build_route_plan
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks.get("hbm_gbs", PEAK_FALLBACK["hbm_gbs"]))
+    n, bins, width = 1 << 26, 256, 2048
+    rows = 1 << 23
+    steps, warm = max(args.steps, 5), max(args.warmup, 3)
+
+    def timed(fn) -> float:
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    out = {}
+    for dist_name, ids_np in (("uniform", np.random.RandomState(0).randint(0, bins, size=n).astype(np.int32)),
+                              ("zipf1.1", zipf_ids(n, bins, 1.1, 1))):
+        ids = torch.from_numpy(ids_np).to(device)
+        ms = timed(lambda: continuous_count(ids, bins))
+        out[f"continuous_count_{dist_name}"] = {"ms": ms, "gbs": n * 4 / ms / 1e6, "frac": n * 4 / ms / 1e6 / hbm,
+                                               "bytes": n * 4}
+        ms = timed(lambda: build_route_plan(ids.view(-1, 1), bins))
+        # algorithmic bytes: ids read by the histogram and by the scatter pass (8 B/id), sorted ids,
+        # permutation and padded row map written (12 B/id)
+        out[f"count_sort_{dist_name}"] = {"ms": ms, "gbs": n * 20 / ms / 1e6, "frac": n * 20 / ms / 1e6 / hbm,
+                                         "bytes": n * 20}
+        if dist_name == "uniform":
+            plan = build_route_plan(ids[:rows].view(-1, 1), bins)
+    src = torch.randn(rows, width, device=device, dtype=torch.bfloat16)
+    dst = torch.empty(plan.row_cap, width, device=device, dtype=torch.bfloat16)
+    ms = timed(lambda: ops.gather_rows_(src, plan.row_src, None, 1, plan.rows_in_use, dst))
+    moved = rows * width * 2 * 2 + rows * 4
+    out["permute_rows_2048_bf16"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / ms / 1e6 / hbm,
+                                     "bytes": moved, "rows": rows}
+    del dst
+    w8 = torch.rand(rows // 8, 8, device=device, dtype=torch.bfloat16)
+    y = torch.empty(rows // 8, width, device=device, dtype=torch.bfloat16)
+    ms = timed(lambda: ops.combine_rows_(src, w8, 8, y))
+    moved = rows * width * 2 + (rows // 8) * width * 2
+    out["combine_rows_top8_2048_bf16"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / ms / 1e6 / hbm,
+                                          "bytes": moved}
+    best = out["permute_rows_2048_bf16"]
+    print(json.dumps({
+        "metric": "routing_hbm_gb_per_s", "value": best["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
+        "warmup": warm, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int32/bf16", "data": "synthetic",
+        "config": {"workload": "c5: configs[4] routing microbench, 64 Mi ids over 256 bins; permute of 8 Mi x 2048 bf16 rows",
+                   "l2_policy": "inputs_exceed_l2"},
+        "roofline": {"bound": "hbm", "kernel": "gather_rows_kernel", "achieved": best["gbs"], "peak": hbm,
+                     "unit": "GB/s", "frac": best["frac"], "peak_source": f"{peak_kind} copy bandwidth",
+                     "traffic": None},
+        "kernels": out,
+    }), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
 def main() -> None:
@@ -228,10 +312,13 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.workload == "c5":
+        run_routing_microbench(args)
+        return
     w = WORKLOADS[args.workload]
 
     if args.impl == "reference":
@@ -400,20 +487,52 @@ def main() -> None:
         per_kernel[name] = {"launches": len(times), "ms_total": sum(times), "ms_avg": sum(times) / len(times)}
         if name in gemm_flops:
             per_kernel[name]["tflops"] = gemm_flops[name] / (per_kernel[name]["ms_avg"] * 1e-3) / 1e12
-    gemm_ms = sum(v["ms_total"] for k, v in per_kernel.items() if k in gemm_flops)
-    gemm_launches = sum(v["launches"] for k, v in per_kernel.items() if k in gemm_flops)
+    # One entry per kernel function; the dominant one (largest share of the timed region) gets the roofline.
+    kernel_functions = {
+        "rows_gemm_tc_kernel<T, W_NK, SwiGLU> (up projection)": ["gemm_up_swiglu"],
+        "rows_gemm_tc_kernel<T, W_NK, plain> (down projection)": ["gemm_down"],
+        "rows_gemm_tc_kernel<T, W_KN, dSwiGLU> (d activation)": ["gemm_dact_dswiglu"],
+        "rows_gemm_tc_kernel<T, W_KN, plain> (d input)": ["gemm_dx"],
+        "dw_gemm_tc_kernel<T> (dW1 and dW2)": ["gemm_dw1", "gemm_dw2"],
+    }
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures of the
+    # 2-expert slice `c2e2` summarised in profiles/ncu_grouped_gemm_tcgen05_c2e2.md; traffic grows in
+    # proportion to the number of experts at fixed rows per expert, so configs[1] moves experts/2 times this.
+    ncu_traffic_c2e2 = {"gemm_up_swiglu": 1.491e9, "gemm_down": 1.280e9, "gemm_dact_dswiglu": 1.776e9,
+                        "gemm_dw1": 1.216e9, "gemm_dw2": 1.222e9}
+    peak = float(peaks.get("bf16_tflops_sustained", PEAK_FALLBACK["bf16_tflops_sustained"]))
+    groups = {}
+    for fn, tags in kernel_functions.items():
+        tags = [t for t in tags if t in per_kernel]
+        if not tags:
+            continue
+        ms = sum(per_kernel[t]["ms_total"] for t in tags)
+        n_launch = sum(per_kernel[t]["launches"] for t in tags)
+        flops = sum(gemm_flops[t] * per_kernel[t]["launches"] for t in tags)
+        groups[fn] = {"ms_total": ms, "launches": n_launch, "tflops": flops / (ms * 1e-3) / 1e12,
+                      "share_of_step": ms / (ms_per_step * args.steps), "tags": tags}
     roofline = None
-    if gemm_launches:
-        flops_per_step = sum(gemm_flops.values())
-        achieved = flops_per_step * args.steps / (gemm_ms * 1e-3) / 1e12
-        peak = float(peaks.get("bf16_tflops_sustained", PEAK_FALLBACK["bf16_tflops_sustained"]))
+    all_gemms = None
+    if groups:
+        fn = max(groups, key=lambda k: groups[k]["ms_total"])
+        g = groups[fn]
+        traffic = None
+        if args.workload in ("c2", "c2e2") and all(t in ncu_traffic_c2e2 for t in g["tags"]):
+            scale = (E // world) / 2.0
+            traffic = scale * sum(ncu_traffic_c2e2[t] for t in g["tags"]) / len(g["tags"])
         roofline = {
-            "bound": "tensor", "kernel": "grouped GEMM (tcgen05): up+SwiGLU, down, d-act+dSwiGLU, dX, dW1, dW2",
-            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-            "peak_source": f"{peak_kind} cuBLAS bf16 sustained", "traffic": None,
-            "share_of_step": gemm_ms / (ms_per_step * args.steps),
-            "frac_of_nominal_2250": achieved / 2250.0,
+            "bound": "tensor", "kernel": fn, "achieved": g["tflops"], "peak": peak, "unit": "TFLOP/s",
+            "frac": g["tflops"] / peak, "peak_source": f"{peak_kind} cuBLAS bf16 sustained (kernel timed inside a long step)",
+            "traffic": traffic, "launches_per_step": g["launches"] // args.steps,
+            "ms_per_launch": g["ms_total"] / g["launches"], "share_of_step": g["share_of_step"],
+            "frac_of_nominal_2250": g["tflops"] / 2250.0,
         }
+        gemm_ms = sum(g["ms_total"] for g in groups.values())
+        achieved = sum(gemm_flops.values()) * args.steps / (gemm_ms * 1e-3) / 1e12
+        all_gemms = {"tflops": achieved, "frac": achieved / peak, "frac_of_nominal_2250": achieved / 2250.0,
+                     "share_of_step": gemm_ms / (ms_per_step * args.steps),
+                     "by_kernel": {k: {"tflops": v["tflops"], "share_of_step": v["share_of_step"]}
+                                   for k, v in groups.items()}}
     step_tflops = expert_flops(w, tokens_per_step // world) / (ms_per_step * 1e-3) / 1e12
 
     # ---- CPU baseline (rank 0, N = 1 only) -----------------------------------------------------------
@@ -439,6 +558,7 @@ def main() -> None:
                     "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
             "gpu_launches": launches,
             "roofline": roofline,
+            "all_grouped_gemms": all_gemms,
             "step_tflops_per_gpu": step_tflops,
             "kernels": per_kernel,
             "cpu_baseline": cpu,
