@@ -1,9 +1,17 @@
 // C-ABI entry points of the expert grouped GEMMs. `impl` selects the kernel family:
-//   0 = automatic (tcgen05 path whenever dtype, widths and alignment allow, CUDA-core path otherwise)
-//   1 = CUDA-core path        2 = tcgen05 path (XMA_ERR_UNSUPPORTED if the arguments do not qualify)
+//   0 = automatic: tcgen05 whenever dtype, widths and alignment allow (CTA pairs for the SwiGLU
+//       epilogues and the weight gradients when experts average >= 1024 rows, one CTA per tile
+//       otherwise - measured faster that way on B200), CUDA-core path for everything else
+//   1 = CUDA-core path        2 = tcgen05 path, one CTA per tile    3 = tcgen05 path, CTA pairs
+//   (2 and 3 return XMA_ERR_UNSUPPORTED if the arguments do not qualify)
 #include "gemm_internal.h"
 
 namespace {
+
+// Experts average at least 8 row tiles: a 256-row pair tile then wastes little on odd tile counts.
+bool large_experts(int64_t tiles_allocated, int num_experts) {
+    return (tiles_allocated - num_experts) >= 8 * static_cast<int64_t>(num_experts);
+}
 
 int check_rows(const xma::RowsGemmArgs& g) {
     if (!g.a || !g.w || !g.out || !g.tile_expert || !g.tile_prefix) return XMA_ERR_NULL_POINTER;
@@ -49,8 +57,12 @@ int xma_b200_grouped_gemm_rows(const void* a, int64_t a_row_stride, const void* 
     if (rc) return rc;
     if (impl == 1) return xma::rows_gemm_simt(g);
     if (impl == 2) return xma::rows_gemm_tc(g);
+    if (impl == 3) return xma::rows_gemm_tc2(g);
     if (impl != 0) return XMA_ERR_BAD_SHAPE;
-    if (xma::rows_gemm_tc_supported(g)) return xma::rows_gemm_tc(g);
+    if (xma::rows_gemm_tc_supported(g)) {
+        if (g.epilogue != xma::EPI_PLAIN && large_experts(g.tile_cap, g.num_experts)) return xma::rows_gemm_tc2(g);
+        return xma::rows_gemm_tc(g);
+    }
     return xma::rows_gemm_simt(g);
 }
 
@@ -78,8 +90,12 @@ int xma_b200_grouped_gemm_dw(const void* x, int64_t x_row_stride, const void* y,
     g.stream = stream;
     if (impl == 1) return xma::dw_gemm_simt(g);
     if (impl == 2) return xma::dw_gemm_tc(g);
+    if (impl == 3) return xma::dw_gemm_tc2(g);
     if (impl != 0) return XMA_ERR_BAD_SHAPE;
-    if (xma::dw_gemm_tc_supported(g)) return xma::dw_gemm_tc(g);
+    if (xma::dw_gemm_tc_supported(g)) {
+        if (large_experts(rows_cap / XMA_ROW_PAD, num_experts)) return xma::dw_gemm_tc2(g);
+        return xma::dw_gemm_tc(g);
+    }
     return xma::dw_gemm_simt(g);
 }
 

@@ -67,6 +67,9 @@ bool rows_gemm_tc_supported(const RowsGemmArgs& a);
 bool dw_gemm_tc_supported(const DwGemmArgs& a);
 int rows_gemm_tc(const RowsGemmArgs& a);
 int dw_gemm_tc(const DwGemmArgs& a);
+// Same contract on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles).
+int rows_gemm_tc2(const RowsGemmArgs& a);
+int dw_gemm_tc2(const DwGemmArgs& a);
 
 // Elementwise helpers reused by the unfused epilogues (defined in swiglu.cu).
 int swiglu_fwd_launch(const void* g, int64_t gs, const void* u, int64_t us, void* y, int64_t ys, int dtype,

@@ -15,220 +15,10 @@
 //                 and, with 8 warps, half of the tile's columns -> acc_empty[buf]
 // The accumulator is double buffered (2 x 256 columns), so the epilogue of a tile overlaps the
 // main loop of the next one. Every wait is bounded: on expiry the CTA raises a flag, sets the
-// timeout bit of the device status word, leaves its loops and releases tensor memory.
-#include <cuda.h>
-
-#include <cstdlib>
-#include <mutex>
-
-#include "gemm_internal.h"
+#include "sm100_common.cuh"
 
 namespace xma {
 namespace tc {
-
-constexpr int BM = 128;           // rows of a tile = tensor-memory lanes
-constexpr int BN = 256;           // accumulator columns per tile
-constexpr int BK = 64;            // reduction elements per stage (64 x 2 bytes = one 128-byte swizzle row)
-constexpr int UMMA_K = 16;        // reduction elements per tcgen05.mma for 16-bit inputs
-constexpr int STAGES = 4;
-constexpr int MAX_EPI_WARPS = 8;  // 4 or 8 epilogue warps (block size 192 or 320): with 8, two warps share a
-                                  // tensor-memory lane quarter and each takes half of the tile's columns
-constexpr int THREADS = 64 + MAX_EPI_WARPS * 32;
-constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int TMEM_COLS = 512;
-constexpr int MAX_EXPERTS = 1024;
-constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64 x 64 box of an MN-major operand: 8 KiB
-constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + static_cast<size_t>(STAGES) * STAGE_BYTES +
-                              (MAX_EXPERTS + 1) * sizeof(int) + 256 /*barriers*/;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
-
-// ---- PTX wrappers ---------------------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait. Returns false when the CTA-wide abort flag is up or the time limit ran out
-// (in which case it raises the flag).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xffu) == 0u) {
-            if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        :
-        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
-                 "r"(cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// D[tmem] (+)= A[smem] * B[smem]^T, 128 x 256 x 16, issued by one thread.
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                         uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}"
-        :
-        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// mbarrier arrives once every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-
-// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base + i).
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// ---- descriptors ------------------------------------------------------------------------------------
-
-// Shared-memory matrix descriptor, 128-byte swizzle, tile base 1024-byte aligned:
-//   bits [0,14)  start address >> 4          bits [16,30) leading-dimension byte offset >> 4
-//   bits [32,46) stride-dimension byte offset >> 4          bits [46,48) version = 1
-//   bits [61,64) layout type: 2 = 128-byte swizzle
-// K-major operand (reduction dimension contiguous, rows of 128 bytes): eight-row groups are 1024
-// bytes apart (stride offset); the leading offset is not used by swizzled K-major layouts.
-// MN-major operand (row/column index contiguous in runs of 64 elements = 128 bytes): eight
-// reduction steps are 1024 bytes apart (stride offset); the next run of 64 along M/N starts one
-// 64 x 64 box (8 KiB) later (leading offset).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, bool mn_major) {
-    const uint64_t lbo = mn_major ? (CHUNK_BYTES >> 4) : 1;
-    const uint64_t sbo = 1024 >> 4;
-    return static_cast<uint64_t>((saddr >> 4) & 0x3fffu) | (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// Descriptor step per tcgen05.mma (16 reduction elements), in units of 16 bytes.
-__device__ __forceinline__ constexpr uint32_t desc_k_step(bool mn_major) {
-    return mn_major ? ((UMMA_K * 128) >> 4) : ((UMMA_K * 2) >> 4);
-}
-
-// Instruction descriptor (kind::f16): fp32 accumulate, a/b format (0 = fp16, 1 = bf16), operand
-// majorness, N >> 3 at bit 17, M >> 4 at bit 24.
-inline uint32_t make_idesc(int dtype, bool a_mn, bool b_mn) {
-    const uint32_t fmt = (dtype == XMA_BF16) ? 1u : 0u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-           (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
-}
-
-// ---- epilogue helpers ----------------------------------------------------------------------------------
-
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi);
-template <>
-__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-template <>
-__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// Logistic function for the 16-bit epilogues: ex2.approx + rcp.approx (a few ulp in fp32, far below
-// the rounding of the bf16/fp16 result it feeds).
-__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
-
-template <typename T>
-__device__ __forceinline__ float round_to(float x) {
-    return to_f32(from_f32<T>(x));
-}
-
-template <typename T>
-__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
-    const T* p = reinterpret_cast<const T*>(&q);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = to_f32(p[i]);
-}
-
-template <typename T>
-__device__ __forceinline__ uint4 pack8(const float* f) {
-    uint4 q;
-    q.x = pack2<T>(f[0], f[1]);
-    q.y = pack2<T>(f[2], f[3]);
-    q.z = pack2<T>(f[4], f[5]);
-    q.w = pack2<T>(f[6], f[7]);
-    return q;
-}
 
 struct Shared {
     uint8_t* stage_base;  // 1024-byte aligned
@@ -421,108 +211,9 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
 
-            if (EPI == EPI_PLAIN) {
-                int64_t dst = r;
-                if (row_map) dst = row_map[r];
-                const int n0 = wk.n_tile * BN;
-                if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
-                tc_fence_after();
-#pragma unroll 1
-                for (int c = part * chunks; c < (part + 1) * chunks; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + c * 32, v);
-                    tmem_ld_wait();
-                    const int col = n0 + c * 32;
-                    if (dst >= 0 && col < n) {
-                        T* p = out + dst * out_stride + col;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            if (col + 8 * i < n)
-                                *reinterpret_cast<uint4*>(p + 8 * i) =
-                                    pack8<T>(reinterpret_cast<const float*>(&v[8 * i]));
-                        }
-                    }
-                }
-            } else if (EPI == EPI_SWIGLU) {
-                const int j0 = wk.n_tile * 128;
-                if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
-                tc_fence_after();
-#pragma unroll 1
-                for (int c = part * (chunks / 2); c < (part + 1) * (chunks / 2); ++c) {
-                    uint32_t g[32], u[32];
-                    tmem_ld32(taddr + c * 32, g);
-                    tmem_ld32(taddr + 128 + c * 32, u);
-                    tmem_ld_wait();
-                    const int col = j0 + c * 32;
-                    if (col < half_n) {
-                        T* pg = aux + r * aux_stride + col;
-                        T* pu = pg + half_n;
-                        T* po = out + r * out_stride + col;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            if (col + 8 * i < half_n) {
-                                float gr[8], ur[8], ac[8];
-#pragma unroll
-                                for (int t = 0; t < 8; ++t) {
-                                    gr[t] = round_to<T>(__uint_as_float(g[8 * i + t]));
-                                    ur[t] = round_to<T>(__uint_as_float(u[8 * i + t]));
-                                    ac[t] = ur[t] * gr[t] * fast_sigmoid(gr[t]);
-                                }
-                                *reinterpret_cast<uint4*>(pg + 8 * i) = pack8<T>(gr);
-                                *reinterpret_cast<uint4*>(pu + 8 * i) = pack8<T>(ur);
-                                *reinterpret_cast<uint4*>(po + 8 * i) = pack8<T>(ac);
-                            }
-                        }
-                    }
-                }
-            } else {  // EPI_DSWIGLU: n is the activation width
-                const int n0 = wk.n_tile * BN;
-                const T* pg_row = aux + r * aux_stride;
-                T* pd_row = out + r * out_stride;
-                // gate|up of this row do not depend on the accumulator: fetch the first chunk before
-                // waiting for it, and every later chunk while the previous one is being computed
-                uint4 gq[2][4], uq[2][4];
-                auto fetch = [&](int c, int b) {
-                    const int col = n0 + c * 32;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        if (col + 8 * i < n) {
-                            gq[b][i] = *reinterpret_cast<const uint4*>(pg_row + col + 8 * i);
-                            uq[b][i] = *reinterpret_cast<const uint4*>(pg_row + n + col + 8 * i);
-                        }
-                    }
-                };
-                fetch(part * chunks, 0);
-                if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
-                tc_fence_after();
-#pragma unroll
-                for (int cc = 0; cc < BN / 32; ++cc) {
-                    if (cc >= chunks) break;
-                    const int c = part * chunks + cc;
-                    if (cc + 1 < chunks) fetch(c + 1, (cc + 1) & 1);
-                    uint32_t v[32];
-                    tmem_ld32(taddr + c * 32, v);
-                    tmem_ld_wait();
-                    const int col = n0 + c * 32;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        if (col + 8 * i < n) {
-                            float gg[8], uu[8], dg[8], du[8];
-                            unpack8<T>(gq[cc & 1][i], gg);
-                            unpack8<T>(uq[cc & 1][i], uu);
-#pragma unroll
-                            for (int t = 0; t < 8; ++t) {
-                                const float d = __uint_as_float(v[8 * i + t]);
-                                const float sg = fast_sigmoid(gg[t]);
-                                dg[t] = d * uu[t] * sg * (1.0f + gg[t] * (1.0f - sg));
-                                du[t] = d * gg[t] * sg;
-                            }
-                            *reinterpret_cast<uint4*>(pd_row + col + 8 * i) = pack8<T>(dg);
-                            *reinterpret_cast<uint4*>(pd_row + n + col + 8 * i) = pack8<T>(du);
-                        }
-                    }
-                }
-            }
+            if (!rows_epilogue_tile<T, EPI>(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag, taddr, r, true, wk.n_tile, n,
+                                            half_n, out, out_stride, aux, aux_stride, row_map, part, chunks))
+                break;
             tc_fence_before();
             mbar_arrive(&s.acc_empty[buf]);
         }
@@ -535,27 +226,6 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 // Both operands are MN-major (the reduction runs over rows). Experts without rows get zeros.
 // Work order: expert-major, then groups of 8 row tiles x all column tiles (row tile fastest).
 // ======================================================================================================
-constexpr int DW_GROUP_M = 8;
-
-struct DwWork {
-    int e, m_tile, n_tile;
-};
-
-__device__ __forceinline__ DwWork decode_dw(int64_t w, int m_tiles, int n_tiles) {
-    DwWork r;
-    const int64_t per_e = static_cast<int64_t>(m_tiles) * n_tiles;
-    r.e = static_cast<int>(w / per_e);
-    const int local = static_cast<int>(w - r.e * per_e);
-    const int group_size = DW_GROUP_M * n_tiles;
-    const int g = local / group_size;
-    const int first_m = g * DW_GROUP_M;
-    const int gm = min(DW_GROUP_M, m_tiles - first_m);
-    const int in_g = local - g * group_size;
-    r.m_tile = first_m + in_g % gm;
-    r.n_tile = in_g / gm;
-    return r;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(THREADS, 1)
 dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
@@ -672,71 +342,6 @@ dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 }
 
 // ---- host side ---------------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-// Row-major 2-D tensor [outer, inner] of 16-bit elements, box [box_outer, 64], 128-byte swizzle,
-// out-of-range elements read as zero.
-static bool make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-                     uint64_t row_stride_elems, uint32_t box_outer) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[2] = {inner, outer};
-    const cuuint64_t strides[1] = {row_stride_elems * 2};
-    const cuuint32_t box[2] = {64, box_outer};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapDataType dt =
-        (dtype == XMA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return false;
-    // Drivers up to 13.1 mis-handle tensors below 128 KiB unless this descriptor bit is cleared
-    // (the same adjustment CUTLASS applies after encoding).
-    int drv = 0;
-    if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010) {
-        if (outer * row_stride_elems * 2 < 131072ull) reinterpret_cast<uint64_t*>(map)[1] &= ~(1ull << 21);
-    }
-    return true;
-}
-
-static bool device_is_sm100() {
-    static int cached = -1;
-    if (cached < 0) {
-        int dev = 0, major = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return false;
-        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
-        cached = (major == 10) ? 1 : 0;
-    }
-    return cached == 1;
-}
-
-// Epilogue warps per kernel: 4 (block of 192 threads) or 8 (320). XMA_B200_EPI_WARPS=4|8 overrides
-// the per-kernel default (tuning knob).
-static int block_threads(int default_epi_warps) {
-    static int forced = -1;
-    if (forced < 0) {
-        const char* e = getenv("XMA_B200_EPI_WARPS");
-        forced = (e && (e[0] == '4' || e[0] == '8')) ? (e[0] - '0') : 0;
-    }
-    const int warps = forced ? forced : default_epi_warps;
-    return 64 + 32 * warps;
-}
 
 template <typename K>
 static int set_smem(K kernel) {

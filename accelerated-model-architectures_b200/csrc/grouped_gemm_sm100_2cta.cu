@@ -1,0 +1,516 @@
+// Two-CTA (cta_group::2) variant of the tcgen05 grouped GEMMs: a pair of CTAs on neighbouring SMs
+// computes one 256 x 256 output tile. Each CTA stages its own 128 rows of A and only HALF of the B
+// tile (128 of the 256 columns); the tensor cores of both SMs read both halves. Per 64-deep reduction
+// block a CTA therefore pulls 32 KiB from L2 instead of 48 KiB (one third less L2->SM traffic and
+// shared-memory fill per FLOP than the one-CTA kernel) and the ring holds 6 stages instead of 4.
+//
+// Protocol (rank 0 = leader of the pair):
+//   producers (both CTAs)  : wait own empty[s] -> TMA A/B into own shared memory, completion bytes
+//                            are posted to the LEADER's full[s] (cp.async.bulk.tensor .cta_group::2)
+//   MMA (leader, one lane) : wait full[s] (expects the bytes of both CTAs) -> tcgen05.mma.cta_group::2
+//                            -> tcgen05.commit to empty[s] / acc_full[buf] of BOTH CTAs
+//   epilogue (both CTAs)   : wait own acc_full[buf] -> read own 128 accumulator lanes -> one arrive
+//                            per warp on the LEADER's acc_empty[buf]
+// No TMA load uses cluster multicast. Every wait is bounded as in the one-CTA kernel; both CTAs meet
+// at a cluster barrier before tensor memory is released.
+#include "sm100_common.cuh"
+
+namespace xma {
+namespace tc2 {
+
+using namespace tc;
+
+constexpr int STAGES2 = 6;
+constexpr int A2_BYTES = BM * BK * 2;         // 128 rows x 64: 16 KiB
+constexpr int B2_BYTES = (BN / 2) * BK * 2;   // this CTA's half of the B tile: 16 KiB
+constexpr int STAGE2_BYTES = A2_BYTES + B2_BYTES;
+constexpr size_t SMEM2_BYTES = 1024 + static_cast<size_t>(STAGES2) * STAGE2_BYTES +
+                               2 * (MAX_EXPERTS + 1) * sizeof(int) + 256;
+
+// ---- cluster / pair PTX ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+
+// TMA load into this CTA's shared memory; the completion bytes go to the mbarrier at `mbar_cluster_addr`,
+// which may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t mbar_cluster_addr,
+                                                 int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(mbar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t mbar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(mbar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem of both CTAs] (+)= A * B^T, 256 x 256 x 16, issued by one thread of the leader CTA.
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The mbarrier at this shared-memory offset in BOTH CTAs of the pair gets one arrival once every
+// tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"(mask)
+        : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void issue_stage_pair(uint32_t a_saddr, uint32_t b_saddr, uint32_t tmem_d, uint32_t idesc,
+                                                 bool first_block) {
+    const uint64_t da = smem_desc(a_saddr, A_MN);
+    const uint64_t db = smem_desc(b_saddr, B_MN);
+#pragma unroll
+    for (int k = 0; k < BK / UMMA_K; ++k) {
+        umma_f16_pair(tmem_d, da + static_cast<uint64_t>(k * desc_k_step(A_MN)),
+                      db + static_cast<uint64_t>(k * desc_k_step(B_MN)), idesc, (first_block && k == 0) ? 0u : 1u);
+    }
+}
+
+struct Shared2 {
+    uint8_t* stage_base;
+    int* tile_prefix;  // [E + 1] 128-row tiles in front of each expert
+    int* pair_prefix;  // [E + 1] 256-row pair tiles in front of each expert
+    uint64_t* full;
+    uint64_t* empty;
+    uint64_t* acc_full;
+    uint64_t* acc_empty;
+    uint32_t* tmem_ptr;
+    volatile int* abort_flag;
+};
+
+__device__ __forceinline__ Shared2 carve_smem2(uint8_t* raw) {
+    Shared2 s;
+    const uint32_t a = smem_u32(raw);
+    uint8_t* base = raw + ((1024u - (a & 1023u)) & 1023u);
+    s.stage_base = base;
+    uint8_t* p = base + static_cast<size_t>(STAGES2) * STAGE2_BYTES;
+    s.tile_prefix = reinterpret_cast<int*>(p);
+    p += (MAX_EXPERTS + 1) * sizeof(int);
+    s.pair_prefix = reinterpret_cast<int*>(p);
+    p += (MAX_EXPERTS + 1) * sizeof(int);
+    p = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 7) & ~static_cast<uintptr_t>(7));
+    s.full = reinterpret_cast<uint64_t*>(p);
+    s.empty = s.full + STAGES2;
+    s.acc_full = s.empty + STAGES2;
+    s.acc_empty = s.acc_full + 2;
+    s.tmem_ptr = reinterpret_cast<uint32_t*>(s.acc_empty + 2);
+    s.abort_flag = reinterpret_cast<volatile int*>(s.tmem_ptr + 1);
+    return s;
+}
+
+// Barriers + tensor-memory allocation of the pair. Must be called by all threads of both CTAs.
+__device__ __forceinline__ uint32_t prologue2(const Shared2& s, int warp) {
+    if (threadIdx.x == 0) {
+        const uint32_t epi_warps = (blockDim.x - 64) >> 5;
+        for (int i = 0; i < STAGES2; ++i) {
+            mbar_init(&s.full[i], 1);   // the leader's own producer; bytes of both CTAs
+            mbar_init(&s.empty[i], 1);  // one commit from the leader's MMA thread
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s.acc_full[i], 1);
+            mbar_init(&s.acc_empty[i], 2 * epi_warps);  // one arrival per epilogue warp of both CTAs
+        }
+        *s.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(s.tmem_ptr, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything is posted to them
+    tc_fence_after();
+    return *s.tmem_ptr;
+}
+
+__device__ __forceinline__ void teardown2(const Shared2& s, uint32_t tmem_base, int warp, int* status) {
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // neither CTA leaves while the other may still touch its shared or tensor memory
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *s.abort_flag && status) atomicOr(status, XMA_DEV_WAIT_TIMEOUT);
+}
+
+// largest e with prefix[e] * n_tiles <= w
+__device__ __forceinline__ int find_expert(const int* prefix, int E, int n_tiles, int64_t w) {
+    int lo = 0, hi = E;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (static_cast<int64_t>(prefix[mid]) * n_tiles <= w) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+
+struct PairWork {
+    int e, n_tile, m_tile;  // m_tile: this CTA's 128-row tile (global index in the padded layout)
+    bool active;            // false: this CTA's half lies beyond the expert's rows
+};
+
+__device__ __forceinline__ PairWork decode_pair(const Shared2& s, int E, int n_tiles, int64_t w, int rank) {
+    PairWork r;
+    r.e = find_expert(s.pair_prefix, E, n_tiles, w);
+    const int64_t local = w - static_cast<int64_t>(s.pair_prefix[r.e]) * n_tiles;
+    const int pt = s.pair_prefix[r.e + 1] - s.pair_prefix[r.e];
+    r.n_tile = static_cast<int>(local / pt);
+    const int pm = static_cast<int>(local % pt);
+    const int mt = s.tile_prefix[r.e + 1] - s.tile_prefix[r.e];
+    r.m_tile = s.tile_prefix[r.e] + 2 * pm + rank;
+    r.active = (2 * pm + rank) < mt;
+    return r;
+}
+
+// ======================================================================================================
+// Rows GEMM, CTA pair
+// ======================================================================================================
+template <typename T, int WL, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     T* __restrict__ out, int64_t out_stride, T* __restrict__ aux, int64_t aux_stride,
+                     const int* __restrict__ row_map, const int* __restrict__ g_tile_prefix, int E, int kd, int n,
+                     uint32_t idesc, int* __restrict__ status) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const Shared2 s = carve_smem2(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = static_cast<int>(cluster_ctarank());
+    const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    for (int i = threadIdx.x; i <= E; i += blockDim.x) s.tile_prefix[i] = g_tile_prefix[i];
+    __syncthreads();
+    if (threadIdx.x == 32) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            s.pair_prefix[e] = run;
+            run += (s.tile_prefix[e + 1] - s.tile_prefix[e] + 1) >> 1;
+        }
+        s.pair_prefix[E] = run;
+    }
+    const uint32_t tmem_base = prologue2(s, warp);
+
+    constexpr bool B_MN = (WL == W_KN);
+    const int half_n = n / 2;
+    const int n_tiles = (EPI == EPI_SWIGLU) ? (half_n + 127) / 128 : (n + BN - 1) / BN;
+    const int k_blocks = (kd + BK - 1) / BK;
+    const int64_t total = static_cast<int64_t>(s.pair_prefix[E]) * n_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int64_t w = pair; w < total; w += num_pairs) {
+                const PairWork wk = decode_pair(s, E, n_tiles, w, rank);
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int st = it % STAGES2;
+                    ok = mbar_wait(&s.empty[st], ((it / STAGES2) & 1u) ^ 1u, s.abort_flag);
+                    if (!ok) break;
+                    uint8_t* sa = s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES;
+                    uint8_t* sb = sa + A2_BYTES;
+                    const uint32_t full0 = map_to_cta(smem_u32(&s.full[st]), 0);
+                    if (rank == 0) mbar_expect_tx(&s.full[st], 2 * STAGE2_BYTES);
+                    tma_load_2d_pair(sa, &tm_a, full0, kb * BK, wk.m_tile * BM);
+                    if (!B_MN) {
+                        // weight stored [E * n, kd]: this CTA's 128 rows of the 256-row B tile
+                        int r0;
+                        if (EPI == EPI_SWIGLU) r0 = wk.e * n + wk.n_tile * 128 + rank * half_n;  // gate | up rows
+                        else r0 = wk.e * n + wk.n_tile * BN + rank * 128;
+                        tma_load_2d_pair(sb, &tm_b, full0, kb * BK, r0);
+                    } else {
+                        // weight stored [E * kd, n]: two boxes of 64 columns x 64 reduction rows
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            tma_load_2d_pair(sb + j * CHUNK_BYTES, &tm_b, full0, wk.n_tile * BN + rank * 128 + j * 64,
+                                             wk.e * kd + kb * BK);
+                    }
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0, lt = 0;
+            for (int64_t w = pair; w < total; w += num_pairs, ++lt) {
+                const uint32_t buf = lt & 1u;
+                if (!mbar_wait(&s.acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, s.abort_flag)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int st = it % STAGES2;
+                    ok = mbar_wait(&s.full[st], (it / STAGES2) & 1u, s.abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES);
+                    issue_stage_pair<false, B_MN>(sa, sa + A2_BYTES, tmem_d, idesc, kb == 0);
+                    umma_commit_pair(&s.empty[st]);
+                }
+                if (!ok) break;
+                umma_commit_pair(&s.acc_full[buf]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int parts = (static_cast<int>(blockDim.x) - 64) >> 7;
+        const int part = (warp - 2) >> 2;
+        const int chunks = (BN / 32) / parts;
+        const int row_in_tile = quarter * 32 + lane;
+        uint32_t lt = 0;
+        for (int64_t w = pair; w < total; w += num_pairs, ++lt) {
+            const PairWork wk = decode_pair(s, E, n_tiles, w, rank);
+            const uint32_t buf = lt & 1u;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
+            if (!rows_epilogue_tile<T, EPI>(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag, taddr, r, wk.active,
+                                            wk.n_tile, n, half_n, out, out_stride, aux, aux_stride, row_map, part,
+                                            chunks))
+                break;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s.acc_empty[buf]), 0));
+        }
+    }
+    teardown2(s, tmem_base, warp, status);
+}
+
+// ======================================================================================================
+// Weight-gradient GEMM, CTA pair: 256 x 256 tile of dW_e; CTA `rank` owns rows [128 * rank, +128) of it
+// and stages columns [128 * rank, +128) of the Y operand.
+// ======================================================================================================
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
+                   const uint32_t* __restrict__ counts, const int* __restrict__ pad_offsets, int E, int m, int n,
+                   T* __restrict__ dw, uint32_t idesc, int* __restrict__ status) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const Shared2 s = carve_smem2(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = static_cast<int>(cluster_ctarank());
+    const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const uint32_t tmem_base = prologue2(s, warp);
+
+    const int m_tiles = (m + 2 * BM - 1) / (2 * BM);
+    const int n_tiles = (n + BN - 1) / BN;
+    const int64_t total = static_cast<int64_t>(E) * m_tiles * n_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int64_t w = pair; w < total; w += num_pairs) {
+                const DwWork wk = decode_dw(w, m_tiles, n_tiles);
+                const int k_blocks = (static_cast<int>(counts[wk.e]) + BK - 1) / BK;
+                const int row0 = pad_offsets[wk.e];
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int st = it % STAGES2;
+                    ok = mbar_wait(&s.empty[st], ((it / STAGES2) & 1u) ^ 1u, s.abort_flag);
+                    if (!ok) break;
+                    uint8_t* sa = s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES;
+                    uint8_t* sb = sa + A2_BYTES;
+                    const uint32_t full0 = map_to_cta(smem_u32(&s.full[st]), 0);
+                    if (rank == 0) mbar_expect_tx(&s.full[st], 2 * STAGE2_BYTES);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        tma_load_2d_pair(sa + j * CHUNK_BYTES, &tm_x, full0, wk.m_tile * 2 * BM + rank * BM + j * 64,
+                                         row0 + kb * BK);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        tma_load_2d_pair(sb + j * CHUNK_BYTES, &tm_y, full0, wk.n_tile * BN + rank * 128 + j * 64,
+                                         row0 + kb * BK);
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0, lt = 0;
+            for (int64_t w = pair; w < total; w += num_pairs) {
+                const DwWork wk = decode_dw(w, m_tiles, n_tiles);
+                const int k_blocks = (static_cast<int>(counts[wk.e]) + BK - 1) / BK;
+                if (k_blocks == 0) continue;
+                const uint32_t buf = lt & 1u;
+                if (!mbar_wait(&s.acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, s.abort_flag)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int st = it % STAGES2;
+                    ok = mbar_wait(&s.full[st], (it / STAGES2) & 1u, s.abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES);
+                    issue_stage_pair<true, true>(sa, sa + A2_BYTES, tmem_d, idesc, kb == 0);
+                    umma_commit_pair(&s.empty[st]);
+                }
+                if (!ok) break;
+                umma_commit_pair(&s.acc_full[buf]);
+                ++lt;
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int parts = (static_cast<int>(blockDim.x) - 64) >> 7;
+        const int part = (warp - 2) >> 2;
+        const int chunks = (BN / 32) / parts;
+        const int row_in_tile = quarter * 32 + lane;
+        uint32_t lt = 0;
+        for (int64_t w = pair; w < total; w += num_pairs) {
+            const DwWork wk = decode_dw(w, m_tiles, n_tiles);
+            const int row = wk.m_tile * 2 * BM + rank * BM + row_in_tile;
+            const int n0 = wk.n_tile * BN;
+            T* dst = dw + (static_cast<int64_t>(wk.e) * m + row) * n + n0;
+            if (counts[wk.e] == 0u) {
+                if (row < m) {
+                    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                    for (int c = part * chunks * 32; c < (part + 1) * chunks * 32 && n0 + c < n; c += 8)
+                        *reinterpret_cast<uint4*>(dst + c) = z;
+                }
+                continue;
+            }
+            const uint32_t buf = lt & 1u;
+            if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = part * chunks; c < (part + 1) * chunks; ++c) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c * 32, v);
+                tmem_ld_wait();
+                const int col = n0 + c * 32;
+                if (row < m && col < n) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (col + 8 * i < n)
+                            *reinterpret_cast<uint4*>(dst + c * 32 + 8 * i) =
+                                pack8<T>(reinterpret_cast<const float*>(&v[8 * i]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s.acc_empty[buf]), 0));
+            ++lt;
+        }
+    }
+    teardown2(s, tmem_base, warp, status);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+
+static int pair_grid() { return num_sms() & ~1; }
+
+template <typename K>
+static int set_smem2(K kernel) {
+    return static_cast<int>(
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM2_BYTES)));
+}
+
+template <typename T, int WL, int EPI>
+static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb) {
+    auto kernel = rows_gemm_tc2_kernel<T, WL, EPI>;
+    int rc = set_smem2(kernel);
+    if (rc) return rc;
+    const uint32_t idesc = make_idesc_mn(g.dtype, false, WL == W_KN, 2 * BM, BN);
+    kernel<<<pair_grid(), block_threads(EPI == EPI_DSWIGLU ? 8 : 4), SMEM2_BYTES, g.stream>>>(
+        ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
+        g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+static int rows_dispatch2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb) {
+#define XMA_ROWS2_CASE(WL, EPI) \
+    if (g.w_layout == WL && g.epilogue == EPI) return launch_rows2<T, WL, EPI>(g, ta, tb)
+    XMA_ROWS2_CASE(W_NK, EPI_PLAIN);
+    XMA_ROWS2_CASE(W_NK, EPI_SWIGLU);
+    XMA_ROWS2_CASE(W_KN, EPI_PLAIN);
+    XMA_ROWS2_CASE(W_KN, EPI_DSWIGLU);
+#undef XMA_ROWS2_CASE
+    return XMA_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+static int launch_dw2(const DwGemmArgs& g, const CUtensorMap& tx, const CUtensorMap& ty) {
+    auto kernel = dw_gemm_tc2_kernel<T>;
+    int rc = set_smem2(kernel);
+    if (rc) return rc;
+    const uint32_t idesc = make_idesc_mn(g.dtype, true, true, 2 * BM, BN);
+    kernel<<<pair_grid(), block_threads(4), SMEM2_BYTES, g.stream>>>(
+        tx, ty, g.counts, g.pad_offsets, g.num_experts, static_cast<int>(g.m), static_cast<int>(g.n),
+        static_cast<T*>(g.dw), idesc, g.device_status);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace tc2
+
+int rows_gemm_tc2(const RowsGemmArgs& g) {
+    if (!rows_gemm_tc_supported(g)) return XMA_ERR_UNSUPPORTED;
+    if (g.tile_cap == 0) return XMA_OK;
+    CUtensorMap ta, tb;
+    const uint64_t rows_cap = static_cast<uint64_t>(g.tile_cap) * XMA_ROW_PAD;
+    if (!tc::make_map(&ta, g.dtype, g.a, g.kd, rows_cap, g.a_stride, tc::BM)) return XMA_ERR_TENSOR_MAP;
+    bool ok;
+    if (g.w_layout == W_NK)
+        ok = tc::make_map(&tb, g.dtype, g.w, g.kd, static_cast<uint64_t>(g.num_experts) * g.n, g.kd, 128);
+    else
+        ok = tc::make_map(&tb, g.dtype, g.w, g.n, static_cast<uint64_t>(g.num_experts) * g.kd, g.n, 64);
+    if (!ok) return XMA_ERR_TENSOR_MAP;
+    if (g.dtype == XMA_BF16) return tc2::rows_dispatch2<__nv_bfloat16>(g, ta, tb);
+    return tc2::rows_dispatch2<__half>(g, ta, tb);
+}
+
+int dw_gemm_tc2(const DwGemmArgs& g) {
+    if (!dw_gemm_tc_supported(g)) return XMA_ERR_UNSUPPORTED;
+    if (g.num_experts == 0) return XMA_OK;
+    CUtensorMap tx, ty;
+    if (!tc::make_map(&tx, g.dtype, g.x, g.m, g.rows_cap, g.x_stride, 64)) return XMA_ERR_TENSOR_MAP;
+    if (!tc::make_map(&ty, g.dtype, g.y, g.n, g.rows_cap, g.y_stride, 64)) return XMA_ERR_TENSOR_MAP;
+    if (g.dtype == XMA_BF16) return tc2::launch_dw2<__nv_bfloat16>(g, tx, ty);
+    return tc2::launch_dw2<__half>(g, tx, ty);
+}
+
+}  // namespace xma

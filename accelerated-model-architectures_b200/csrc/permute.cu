@@ -12,6 +12,10 @@ namespace xma {
 constexpr int ROW_THREADS = 256;
 
 // out[p, :] = src[row_src[p] / fan_out, :] * coeff[row_src[p]]   (zeros where row_src[p] < 0)
+// A CTA moves GATHER_ROWS rows per iteration so that every thread has that many independent
+// 128-bit loads in flight (one row alone does not cover the HBM latency-bandwidth product).
+constexpr int GATHER_ROWS = 4;
+
 template <typename T, bool HAS_COEFF>
 __global__ void __launch_bounds__(ROW_THREADS)
 gather_rows_kernel(const T* __restrict__ src, int64_t src_stride, const int* __restrict__ row_src,
@@ -20,35 +24,47 @@ gather_rows_kernel(const T* __restrict__ src, int64_t src_stride, const int* __r
     constexpr int V = Vec16<T>::N;
     const int64_t limit = rows_in_use ? min(rows, static_cast<int64_t>(*rows_in_use)) : rows;
     const int64_t nvec = width / V;
-    for (int64_t p = blockIdx.x; p < limit; p += gridDim.x) {
-        const int f = row_src[p];
-        T* dst = out + p * out_stride;
-        if (f < 0) {
-            Vec16<T> z;
+    for (int64_t p0 = static_cast<int64_t>(blockIdx.x) * GATHER_ROWS; p0 < limit;
+         p0 += static_cast<int64_t>(gridDim.x) * GATHER_ROWS) {
+        int f[GATHER_ROWS];
+        float cf[GATHER_ROWS];
 #pragma unroll
-            for (int j = 0; j < V; ++j) z.v[j] = from_f32<T>(0.0f);
-            for (int64_t c = threadIdx.x; c < nvec; c += ROW_THREADS) store16(dst + c * V, z);
-            continue;
+        for (int j = 0; j < GATHER_ROWS; ++j) {
+            f[j] = (p0 + j < limit) ? row_src[p0 + j] : -2;  // -2: row does not exist, -1: pad row
+            cf[j] = 1.0f;
+            if (HAS_COEFF && f[j] >= 0) cf[j] = to_f32(coeff[f[j]]);
         }
-        const T* s = src + static_cast<int64_t>(f / fan_out) * src_stride;
-        float cf = 1.0f;
-        if (HAS_COEFF) cf = to_f32(coeff[f]);
         for (int64_t c = threadIdx.x; c < nvec; c += ROW_THREADS) {
-            Vec16<T> x = load16(s + c * V);
-            if (HAS_COEFF) {
+            Vec16<T> x[GATHER_ROWS];
 #pragma unroll
-                for (int j = 0; j < V; ++j) x.v[j] = from_f32<T>(to_f32(x.v[j]) * cf);
+            for (int j = 0; j < GATHER_ROWS; ++j) {
+                if (f[j] >= 0) {
+                    x[j] = load16(src + static_cast<int64_t>(f[j] / fan_out) * src_stride + c * V);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) x[j].v[i] = from_f32<T>(0.0f);
+                }
             }
-            store16_stream(dst + c * V, x);
+#pragma unroll
+            for (int j = 0; j < GATHER_ROWS; ++j) {
+                if (f[j] == -2) continue;
+                if (HAS_COEFF && f[j] >= 0) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) x[j].v[i] = from_f32<T>(to_f32(x[j].v[i]) * cf[j]);
+                }
+                store16_stream(out + (p0 + j) * out_stride + c * V, x[j]);
+            }
         }
     }
 }
 
-// y[t, :] = sum_k w[t,k] * ys[t*K + k, :]; w == nullptr means plain sum.
+// y[t, :] = sum_k w[t,k] * ys[row(t*K + k), :]; w == nullptr means plain sum; row(f) = row_index[f]
+// when an index is given (rows kept in another order), f otherwise.
 template <typename T, bool HAS_W>
 __global__ void __launch_bounds__(ROW_THREADS)
-combine_rows_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restrict__ w, int K, int64_t tokens,
-                    int64_t width, T* __restrict__ y, int64_t y_stride) {
+combine_rows_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restrict__ w,
+                    const int* __restrict__ row_index, int K, int64_t tokens, int64_t width, T* __restrict__ y,
+                    int64_t y_stride) {
     constexpr int V = Vec16<T>::N;
     const int64_t nvec = width / V;
     for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
@@ -58,7 +74,8 @@ combine_rows_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __rest
             for (int j = 0; j < V; ++j) acc[j] = 0.0f;
             for (int k = 0; k < K; ++k) {
                 const float wk = HAS_W ? to_f32(w[t * K + k]) : 1.0f;
-                Vec16<T> x = load16_stream(ys + (t * K + k) * ys_stride + c * V);
+                const int64_t r = row_index ? row_index[t * K + k] : t * K + k;
+                Vec16<T> x = load16_stream(ys + r * ys_stride + c * V);
 #pragma unroll
                 for (int j = 0; j < V; ++j) acc[j] = fmaf(wk, to_f32(x.v[j]), acc[j]);
             }
@@ -70,11 +87,11 @@ combine_rows_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __rest
     }
 }
 
-// dw[t, k] = sum_h ys[t*K+k, h] * dy[t, h]
+// dw[t, k] = sum_h ys[row(t*K+k), h] * dy[t, h]
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
-combine_bwd_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restrict__ dy, int64_t dy_stride, int K,
-                   int64_t tokens, int64_t width, T* __restrict__ dw) {
+combine_bwd_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restrict__ dy, int64_t dy_stride,
+                   const int* __restrict__ row_index, int K, int64_t tokens, int64_t width, T* __restrict__ dw) {
     constexpr int V = Vec16<T>::N;
     __shared__ float s_part[ROW_THREADS / 32];
     const int64_t nvec = width / V;
@@ -83,7 +100,8 @@ combine_bwd_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restr
         for (int k = 0; k < K; ++k) {
             float acc = 0.0f;
             for (int64_t c = threadIdx.x; c < nvec; c += ROW_THREADS) {
-                Vec16<T> a = load16_stream(ys + (t * K + k) * ys_stride + c * V);
+                const int64_t r = row_index ? row_index[t * K + k] : t * K + k;
+                Vec16<T> a = load16_stream(ys + r * ys_stride + c * V);
                 Vec16<T> b = load16(dy + t * dy_stride + c * V);
 #pragma unroll
                 for (int j = 0; j < V; ++j) acc = fmaf(to_f32(a.v[j]), to_f32(b.v[j]), acc);
@@ -103,9 +121,10 @@ combine_bwd_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restr
     }
 }
 
-static int row_grid(int64_t rows) {
+static int row_grid(int64_t rows, int rows_per_cta = 1) {
+    int64_t want = ceil_div(rows, rows_per_cta);
     int64_t cap = static_cast<int64_t>(num_sms()) * 8;
-    return static_cast<int>(rows < 1 ? 1 : (rows > cap ? cap : rows));
+    return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
 }
 
 template <typename T>
@@ -115,7 +134,7 @@ static int gather_impl(const void* src, int64_t src_stride, const int* row_src, 
     constexpr int V = Vec16<T>::N;
     if (width % V || src_stride % V || out_stride % V || !is_aligned16(src) || !is_aligned16(out))
         return XMA_ERR_MISALIGNED;
-    const int grid = row_grid(rows);
+    const int grid = row_grid(rows, GATHER_ROWS);
     if (coeff)
         gather_rows_kernel<T, true><<<grid, ROW_THREADS, 0, stream>>>(
             static_cast<const T*>(src), src_stride, row_src, static_cast<const T*>(coeff), fan_out, rows,
@@ -128,30 +147,31 @@ static int gather_impl(const void* src, int64_t src_stride, const int* row_src, 
 }
 
 template <typename T>
-static int combine_impl(const void* ys, int64_t ys_stride, const void* w, int K, int64_t tokens, int64_t width,
-                        void* y, int64_t y_stride, cudaStream_t stream) {
+static int combine_impl(const void* ys, int64_t ys_stride, const void* w, const int* row_index, int K,
+                        int64_t tokens, int64_t width, void* y, int64_t y_stride, cudaStream_t stream) {
     constexpr int V = Vec16<T>::N;
     if (width % V || ys_stride % V || y_stride % V || !is_aligned16(ys) || !is_aligned16(y))
         return XMA_ERR_MISALIGNED;
     const int grid = row_grid(tokens);
     if (w)
         combine_rows_kernel<T, true><<<grid, ROW_THREADS, 0, stream>>>(
-            static_cast<const T*>(ys), ys_stride, static_cast<const T*>(w), K, tokens, width, static_cast<T*>(y),
-            y_stride);
+            static_cast<const T*>(ys), ys_stride, static_cast<const T*>(w), row_index, K, tokens, width,
+            static_cast<T*>(y), y_stride);
     else
         combine_rows_kernel<T, false><<<grid, ROW_THREADS, 0, stream>>>(
-            static_cast<const T*>(ys), ys_stride, nullptr, K, tokens, width, static_cast<T*>(y), y_stride);
+            static_cast<const T*>(ys), ys_stride, nullptr, row_index, K, tokens, width, static_cast<T*>(y), y_stride);
     return static_cast<int>(cudaGetLastError());
 }
 
 template <typename T>
-static int combine_bwd_impl(const void* ys, int64_t ys_stride, const void* dy, int64_t dy_stride, int K,
-                            int64_t tokens, int64_t width, void* dw, cudaStream_t stream) {
+static int combine_bwd_impl(const void* ys, int64_t ys_stride, const void* dy, int64_t dy_stride,
+                            const int* row_index, int K, int64_t tokens, int64_t width, void* dw,
+                            cudaStream_t stream) {
     constexpr int V = Vec16<T>::N;
     if (width % V || ys_stride % V || dy_stride % V || !is_aligned16(ys) || !is_aligned16(dy))
         return XMA_ERR_MISALIGNED;
     combine_bwd_kernel<T><<<row_grid(tokens), ROW_THREADS, 0, stream>>>(
-        static_cast<const T*>(ys), ys_stride, static_cast<const T*>(dy), dy_stride, K, tokens, width,
+        static_cast<const T*>(ys), ys_stride, static_cast<const T*>(dy), dy_stride, row_index, K, tokens, width,
         static_cast<T*>(dw));
     return static_cast<int>(cudaGetLastError());
 }
@@ -180,40 +200,42 @@ int xma_b200_gather_rows(const void* src, int dtype, int64_t src_row_stride, con
     return XMA_ERR_BAD_DTYPE;
 }
 
-int xma_b200_combine_rows(const void* ys, int dtype, int64_t ys_row_stride, const void* weights, int top_k,
-                          int64_t tokens, int64_t width, void* y, int64_t y_row_stride, cudaStream_t stream) {
+int xma_b200_combine_rows(const void* ys, int dtype, int64_t ys_row_stride, const void* weights,
+                          const int32_t* row_index, int top_k, int64_t tokens, int64_t width, void* y,
+                          int64_t y_row_stride, cudaStream_t stream) {
     if (tokens > 0 && (!ys || !y)) return XMA_ERR_NULL_POINTER;
     if (tokens < 0 || width <= 0 || top_k <= 0) return XMA_ERR_BAD_SHAPE;
     if (tokens == 0) return XMA_OK;
     switch (dtype) {
         case XMA_F32:
-            return xma::combine_impl<float>(ys, ys_row_stride, weights, top_k, tokens, width, y, y_row_stride,
-                                            stream);
+            return xma::combine_impl<float>(ys, ys_row_stride, weights, row_index, top_k, tokens, width, y,
+                                            y_row_stride, stream);
         case XMA_F16:
-            return xma::combine_impl<__half>(ys, ys_row_stride, weights, top_k, tokens, width, y, y_row_stride,
-                                             stream);
+            return xma::combine_impl<__half>(ys, ys_row_stride, weights, row_index, top_k, tokens, width, y,
+                                             y_row_stride, stream);
         case XMA_BF16:
-            return xma::combine_impl<__nv_bfloat16>(ys, ys_row_stride, weights, top_k, tokens, width, y,
+            return xma::combine_impl<__nv_bfloat16>(ys, ys_row_stride, weights, row_index, top_k, tokens, width, y,
                                                     y_row_stride, stream);
     }
     return XMA_ERR_BAD_DTYPE;
 }
 
 int xma_b200_combine_bwd(const void* ys, int dtype, int64_t ys_row_stride, const void* dy, int64_t dy_row_stride,
-                         int top_k, int64_t tokens, int64_t width, void* d_weights, cudaStream_t stream) {
+                         const int32_t* row_index, int top_k, int64_t tokens, int64_t width, void* d_weights,
+                         cudaStream_t stream) {
     if (tokens > 0 && (!ys || !dy || !d_weights)) return XMA_ERR_NULL_POINTER;
     if (tokens < 0 || width <= 0 || top_k <= 0) return XMA_ERR_BAD_SHAPE;
     if (tokens == 0) return XMA_OK;
     switch (dtype) {
         case XMA_F32:
-            return xma::combine_bwd_impl<float>(ys, ys_row_stride, dy, dy_row_stride, top_k, tokens, width,
-                                                d_weights, stream);
+            return xma::combine_bwd_impl<float>(ys, ys_row_stride, dy, dy_row_stride, row_index, top_k, tokens,
+                                                width, d_weights, stream);
         case XMA_F16:
-            return xma::combine_bwd_impl<__half>(ys, ys_row_stride, dy, dy_row_stride, top_k, tokens, width,
-                                                 d_weights, stream);
+            return xma::combine_bwd_impl<__half>(ys, ys_row_stride, dy, dy_row_stride, row_index, top_k, tokens,
+                                                 width, d_weights, stream);
         case XMA_BF16:
-            return xma::combine_bwd_impl<__nv_bfloat16>(ys, ys_row_stride, dy, dy_row_stride, top_k, tokens, width,
-                                                        d_weights, stream);
+            return xma::combine_bwd_impl<__nv_bfloat16>(ys, ys_row_stride, dy, dy_row_stride, row_index, top_k,
+                                                        tokens, width, d_weights, stream);
     }
     return XMA_ERR_BAD_DTYPE;
 }

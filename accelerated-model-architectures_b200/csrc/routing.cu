@@ -126,7 +126,8 @@ static int launch_histogram(const IdT* ids, int64_t n, int bins, unsigned* out, 
 // ------------------------------------------------------------------------------------------------
 __global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __restrict__ offsets_incl,
                             int* __restrict__ pad_offsets, int* __restrict__ tile_prefix,
-                            int* __restrict__ tile_expert, int tile_cap, int* __restrict__ status) {
+                            int* __restrict__ tile_expert, int tile_cap, int* __restrict__ row_src,
+                            int* __restrict__ status) {
     __shared__ int s_tiles_total;
     if (threadIdx.x == 0) {
         int run = 0, pad = 0, tiles = 0;
@@ -155,16 +156,22 @@ __global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __r
         int t1 = t0 + (static_cast<int>(counts[e]) + XMA_ROW_PAD - 1) / XMA_ROW_PAD;
         if (t1 > total) t1 = total;
         for (int t = t0; t < t1; ++t) tile_expert[t] = e;
+        if (row_src) {  // pad rows at the end of the expert's block
+            const int c = static_cast<int>(counts[e]);
+            const int r1 = min(pad_offsets[e] + (t1 - t0) * XMA_ROW_PAD, tile_cap * XMA_ROW_PAD);
+            for (int r = pad_offsets[e] + c; r < r1; ++r) row_src[r] = -1;
+        }
     }
 }
 
 // ------------------------------------------------------------------------------------------------
 // Stable scatter with a decoupled look-back scan
 // ------------------------------------------------------------------------------------------------
-constexpr int SORT_THREADS = 256;
+constexpr int SORT_THREADS = 512;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 constexpr int SORT_ITEMS = 16;
-constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 4096 ids per CTA
+constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 8192 ids per CTA
+constexpr int LB_BATCH = 8;                           // predecessors fetched per look-back round
 constexpr int SORT_MAX_BINS = 1024;
 
 // Look-back status word: [63:62] state, [31:0] value. One 64-bit store/load moves both at once,
@@ -175,13 +182,10 @@ constexpr unsigned long long LB_STATE_MASK = 3ull << 62;
 constexpr unsigned LB_MAX_POLLS = 1u << 22;  // bounded wait; on expiry the status word gets the timeout bit
 
 __host__ __device__ inline size_t sort_smem_bytes(int E) {
-    // s_bin[TILE] u16, s_loc[TILE] u16, s_sbin[TILE] u16, warp_cnt[WARPS][E+1] u32,
-    // bin_start[E+1] u32, goff[E] u32, pad_goff[E] u32, scan scratch[32] u32, tile id
-    size_t b = 3 * static_cast<size_t>(SORT_TILE) * sizeof(uint16_t);
-    b += static_cast<size_t>(SORT_WARPS) * (E + 1) * sizeof(unsigned);
-    b += static_cast<size_t>(E + 1) * sizeof(unsigned);
-    b += 2 * static_cast<size_t>(E) * sizeof(unsigned);
-    b += 40 * sizeof(unsigned);
+    // warp_cnt[WARPS][E+1] u32, pad_delta[E] i32, tile id
+    size_t b = static_cast<size_t>(SORT_WARPS) * (E + 1) * sizeof(unsigned);
+    b += static_cast<size_t>(E) * sizeof(int);
+    b += 16;
     return (b + 15) & ~static_cast<size_t>(15);
 }
 
@@ -193,21 +197,23 @@ __host__ __device__ inline size_t sort_scratch_bytes(int64_t n, int E) {
 
 // The scratch area starts with the dynamic tile counter (256 bytes reserved), followed by
 // status[tile][bin]. The whole area must be zero when the kernel starts.
+//
+// Per tile of SORT_TILE ids: every warp loads its 512 contiguous ids row by row (coalesced), ranks
+// them with match_any against its own per-bin counters (stable: rows in order, lanes in order),
+// then one thread per bin scans the warps, publishes the tile's count and looks back over the
+// earlier tiles for the bin's running total; the result is folded into the warp counters, so an id's
+// destination is `counter[warp][bin] + rank` and every thread scatters straight from registers
+// (ids of one bin held by neighbouring lanes go to neighbouring addresses).
 template <typename IdT>
-__global__ void __launch_bounds__(SORT_THREADS)
+__global__ void __launch_bounds__(SORT_THREADS, 2)
 sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __restrict__ offsets_incl,
                     const int* __restrict__ pad_offsets, int* __restrict__ sorted_expert,
                     int* __restrict__ sorted_scattered, int* __restrict__ row_src,
                     unsigned char* __restrict__ scratch, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char s_raw[];
-    uint16_t* s_bin = reinterpret_cast<uint16_t*>(s_raw);
-    uint16_t* s_loc = s_bin + SORT_TILE;
-    uint16_t* s_sbin = s_loc + SORT_TILE;
-    unsigned* s_warp_cnt = reinterpret_cast<unsigned*>(s_sbin + SORT_TILE);  // [WARPS][E+1]
-    unsigned* s_bin_start = s_warp_cnt + SORT_WARPS * (E + 1);               // [E+1]
-    unsigned* s_goff = s_bin_start + (E + 1);                                // [E]
-    unsigned* s_pad_goff = s_goff + E;                                       // [E]
-    unsigned* s_scan = s_pad_goff + E;                                       // [32] + tile id at [32]
+    unsigned* s_warp_cnt = reinterpret_cast<unsigned*>(s_raw);                 // [WARPS][E+1]
+    int* s_pad_delta = reinterpret_cast<int*>(s_warp_cnt + SORT_WARPS * (E + 1));  // [E]
+    unsigned* s_tile = reinterpret_cast<unsigned*>(s_pad_delta + E);
 
     unsigned* tile_counter = reinterpret_cast<unsigned*>(scratch);
     unsigned long long* lb = reinterpret_cast<unsigned long long*>(scratch + 256);
@@ -217,87 +223,94 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
     const int warp = tid >> 5;
     const int EB = E + 1;  // bin E collects ids that are out of range (dropped)
 
-    if (tid == 0) s_scan[32] = atomicAdd(tile_counter, 1u);
+    if (tid == 0) *s_tile = atomicAdd(tile_counter, 1u);
     for (int i = tid; i < SORT_WARPS * EB; i += SORT_THREADS) s_warp_cnt[i] = 0u;
     __syncthreads();
-    const unsigned tile = s_scan[32];
+    const unsigned tile = *s_tile;
     const int64_t base = static_cast<int64_t>(tile) * SORT_TILE;
     if (base >= n) return;  // uniform for the CTA
     const int cnt = static_cast<int>((n - base) < SORT_TILE ? (n - base) : SORT_TILE);
 
-    // 1. stage the tile's bins in shared memory (coalesced, SORT_ITEMS independent loads per thread)
+    // 1. load (16 independent coalesced loads per thread) and rank
+    unsigned my_bin[SORT_ITEMS];
+    unsigned peers[SORT_ITEMS];
     bool bad = false;
 #pragma unroll
-    for (int j = 0; j < SORT_ITEMS; ++j) {
-        int i = j * SORT_THREADS + tid;
-        uint16_t b = static_cast<uint16_t>(E);
+    for (int r = 0; r < SORT_ITEMS; ++r) {
+        const int i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
+        unsigned b = static_cast<unsigned>(E);
         if (i < cnt) {
-            IdT id = __ldcs(ids + base + i);
-            if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(E)) {
-                b = static_cast<uint16_t>(id);
-            } else {
-                bad = true;
-            }
+            const IdT id = __ldcs(ids + base + i);
+            if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(E)) b = static_cast<unsigned>(id);
+            else bad = true;
         }
-        s_bin[i] = b;
+        my_bin[r] = b;
     }
-    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; ++r) peers[r] = __match_any_sync(0xffffffffu, my_bin[r]);
 
-    // 2. each warp ranks its contiguous 512 ids row by row; equal bins inside a row are ordered
-    //    by lane, rows are processed in order, so the rank is stable.
-    uint16_t my_bin[SORT_ITEMS];
-    uint16_t my_rank[SORT_ITEMS];
+    unsigned my_rank[SORT_ITEMS];
     unsigned* wc = s_warp_cnt + warp * EB;
     const unsigned lt_mask = (1u << lane) - 1u;
 #pragma unroll
     for (int r = 0; r < SORT_ITEMS; ++r) {
-        const int i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
-        const unsigned b = s_bin[i];
-        const unsigned peers = __match_any_sync(0xffffffffu, b);
+        const unsigned b = my_bin[r];
         const unsigned before = wc[b];
         __syncwarp();
-        if ((peers & lt_mask) == 0u) wc[b] = before + __popc(peers);
+        if ((peers[r] & lt_mask) == 0u) wc[b] = before + __popc(peers[r]);
         __syncwarp();
-        my_bin[r] = static_cast<uint16_t>(b);
-        my_rank[r] = static_cast<uint16_t>(before + __popc(peers & lt_mask));
+        my_rank[r] = before + __popc(peers[r] & lt_mask);
     }
     __syncthreads();
 
-    // 3. per bin: exclusive scan over warps, publish the tile aggregate, look back for the prefix
+    // 2. per bin: exclusive scan over warps, publish the tile aggregate, look back for the prefix,
+    //    fold the bin's global base into the warp counters
     for (int b = tid; b < E; b += SORT_THREADS) {
         unsigned run = 0;
 #pragma unroll
         for (int w = 0; w < SORT_WARPS; ++w) {
-            unsigned t = s_warp_cnt[w * EB + b];
+            const unsigned t = s_warp_cnt[w * EB + b];
             s_warp_cnt[w * EB + b] = run;
             run += t;
         }
-        s_bin_start[b] = run;  // tile count for now, scanned below
-
         unsigned long long* mine = lb + static_cast<size_t>(tile) * E + b;
         unsigned excl = 0;
         if (tile == 0) {
             atomicExch(mine, LB_PREFIX | run);
         } else {
             atomicExch(mine, LB_AGGREGATE | run);
+            // Walk back over the predecessors, LB_BATCH status words per round (independent loads),
+            // adding aggregates until a tile that already knows its inclusive prefix is met.
             int64_t prev = static_cast<int64_t>(tile) - 1;
             unsigned polls = 0;
-            bool gave_up = false;
-            while (true) {
-                unsigned long long v =
-                    *reinterpret_cast<volatile unsigned long long*>(lb + static_cast<size_t>(prev) * E + b);
-                unsigned long long st = v & LB_STATE_MASK;
-                if (st == 0ull) {
+            bool gave_up = false, done = false;
+            while (!done) {
+                unsigned long long v[LB_BATCH];
+#pragma unroll
+                for (int j = 0; j < LB_BATCH; ++j) {
+                    const int64_t t = prev - j;
+                    unsigned long long word = 2ull << 62;  // beyond tile 0: an empty prefix
+                    if (t >= 0) word = *reinterpret_cast<volatile unsigned long long*>(lb + static_cast<size_t>(t) * E + b);
+                    v[j] = word;
+                }
+                int used = 0;
+#pragma unroll
+                for (int j = 0; j < LB_BATCH; ++j) {
+                    if (done || used < j) continue;  // stop at the first unpublished entry
+                    const unsigned long long st = v[j] & LB_STATE_MASK;
+                    if (st == 0ull) continue;
+                    excl += static_cast<unsigned>(v[j] & 0xffffffffull);
+                    used = j + 1;
+                    if (st == LB_PREFIX) done = true;
+                }
+                prev -= used;
+                if (!done && used < LB_BATCH) {  // ran into a tile that has not published yet
                     if (++polls > LB_MAX_POLLS) {
                         gave_up = true;
                         break;
                     }
-                    __nanosleep(32);
-                    continue;
+                    if (used == 0) __nanosleep(32);
                 }
-                excl += static_cast<unsigned>(v & 0xffffffffull);
-                if (st == LB_PREFIX) break;
-                --prev;  // an aggregate: keep walking (tile 0 always publishes a prefix)
             }
             if (gave_up) {
                 if (status) atomicOr(status, XMA_DEV_WAIT_TIMEOUT);
@@ -306,67 +319,24 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
             atomicExch(mine, LB_PREFIX | static_cast<unsigned long long>(excl + run));
         }
         const unsigned gbase = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
-        s_goff[b] = gbase + excl;
-        s_pad_goff[b] = static_cast<unsigned>(pad_offsets[b]) + excl;
+        const unsigned first = gbase + excl;  // global sorted position of this tile's first id of bin b
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; ++w) s_warp_cnt[w * EB + b] += first;
+        s_pad_delta[b] = pad_offsets[b] - static_cast<int>(gbase);
     }
     __syncthreads();
 
-    // 4. exclusive scan of the tile's bin counts -> start of each bin inside the tile
-    {
-        constexpr int PER = SORT_MAX_BINS / SORT_THREADS;  // 4 bins per thread
-        unsigned v[PER];
-        unsigned sum = 0;
-#pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            int b = tid * PER + j;
-            v[j] = (b < E) ? s_bin_start[b] : 0u;
-            sum += v[j];
-        }
-        unsigned incl = sum;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += t;
-        }
-        if (lane == 31) s_scan[warp] = incl;
-        __syncthreads();
-        unsigned warp_base = 0;
-        for (int w = 0; w < warp; ++w) warp_base += s_scan[w];
-        unsigned run = warp_base + incl - sum;
-#pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            int b = tid * PER + j;
-            if (b < E) s_bin_start[b] = run;
-            run += v[j];
-            if (b == E - 1) s_bin_start[E] = run;  // number of in-range ids in the tile
-        }
-    }
-    __syncthreads();
-
-    // 5. local stable sort into shared memory
+    // 3. scatter from registers
 #pragma unroll
     for (int r = 0; r < SORT_ITEMS; ++r) {
         const unsigned b = my_bin[r];
         if (b < static_cast<unsigned>(E)) {
-            const int i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
-            const unsigned lp = s_bin_start[b] + s_warp_cnt[warp * EB + b] + my_rank[r];
-            s_loc[lp] = static_cast<uint16_t>(i);
-            s_sbin[lp] = static_cast<uint16_t>(b);
+            const int f = static_cast<int>(base) + warp * (32 * SORT_ITEMS) + r * 32 + lane;
+            const unsigned g = wc[b] + my_rank[r];
+            sorted_scattered[g] = f;
+            sorted_expert[g] = static_cast<int>(b);
+            if (row_src) row_src[static_cast<int>(g) + s_pad_delta[b]] = f;
         }
-    }
-    __syncthreads();
-
-    // 6. write runs of equal bins to their global positions (consecutive threads, consecutive
-    //    addresses inside a run)
-    const int valid = static_cast<int>(s_bin_start[E]);
-    for (int j = tid; j < valid; j += SORT_THREADS) {
-        const unsigned b = s_sbin[j];
-        const unsigned off = static_cast<unsigned>(j) - s_bin_start[b];
-        const int f = static_cast<int>(base + s_loc[j]);
-        const unsigned g = s_goff[b] + off;
-        sorted_scattered[g] = f;
-        sorted_expert[g] = static_cast<int>(b);
-        if (row_src) row_src[s_pad_goff[b] + off] = f;
     }
     if (bad && status) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
 }
@@ -550,9 +520,9 @@ int count_sort_impl(const IdT* ids, int64_t n, int E, uint32_t* counts, int* off
     int rc = xma::launch_histogram(ids, n, E, counts, device_status, stream);
     if (rc) return rc;
     xma::plan_kernel<<<1, 256, 0, stream>>>(counts, E, offsets_incl, pad_offsets, tile_prefix, tile_expert,
-                                            static_cast<int>(tile_cap), device_status);
+                                            static_cast<int>(tile_cap), row_src, device_status);
     XMA_CUDA_TRY(cudaGetLastError());
-    if (row_src) XMA_CUDA_TRY(cudaMemsetAsync(row_src, 0xff, sizeof(int) * row_cap, stream));
+    (void)row_cap;
     if (n == 0) return XMA_OK;
     const size_t need = xma::sort_scratch_bytes(n, E);
     XMA_CUDA_TRY(cudaMemsetAsync(scratch, 0, need, stream));

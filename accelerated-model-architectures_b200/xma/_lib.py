@@ -48,10 +48,10 @@ _SIGNATURES = {
                                    c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     "xma_b200_gather_rows": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int64,
                              c_void_p, c_int64, c_void_p],
-    "xma_b200_combine_rows": [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64,
-                              c_void_p],
-    "xma_b200_combine_bwd": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p,
-                             c_void_p],
+    "xma_b200_combine_rows": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,
+                              c_int64, c_void_p],
+    "xma_b200_combine_bwd": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64,
+                             c_void_p, c_void_p],
     "xma_b200_grouped_gemm_rows": [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int,
                                    c_int, c_void_p, c_void_p],

@@ -71,10 +71,9 @@ class _DispatchRows(torch.autograd.Function):
     def backward(ctx, grad: torch.Tensor):
         (inv_perm,) = ctx.saved_tensors
         grad = grad.contiguous()
-        flat = grad.new_empty(grad.shape)
-        ops.gather_rows_(grad, inv_perm, None, 1, None, flat)  # back to flat (token, slot) order
         dx = grad.new_empty((ctx.tokens, grad.size(1)))
-        ops.combine_rows_(flat, None, ctx.top_k, dx)
+        # sum of a token's K slots, read in place from the expert-sorted rows
+        ops.combine_rows_(grad, None, ctx.top_k, dx, inv_perm)
         return dx, None, None, None
 
 
@@ -85,24 +84,22 @@ class _CombineRows(torch.autograd.Function):
     def forward(ctx, rows: torch.Tensor, router_weights: torch.Tensor, perm: torch.Tensor, inv_perm: torch.Tensor):
         T, K = router_weights.shape
         rows = rows.contiguous()
-        flat = rows.new_empty(rows.shape)
-        ops.gather_rows_(rows, inv_perm, None, 1, None, flat)
         router_weights = router_weights.contiguous()
         y = rows.new_empty((T, rows.size(1)))
-        ops.combine_rows_(flat, router_weights, K, y)
-        ctx.save_for_backward(flat, router_weights, perm)
+        ops.combine_rows_(rows, router_weights, K, y, inv_perm)
+        ctx.save_for_backward(rows, router_weights, perm, inv_perm)
         return y
 
     @staticmethod
     def backward(ctx, dy: torch.Tensor):
-        flat, router_weights, perm = ctx.saved_tensors
+        rows, router_weights, perm, inv_perm = ctx.saved_tensors
         T, K = router_weights.shape
         dy = dy.contiguous()
         d_rw = None
         if ctx.needs_input_grad[1]:
             d_rw = torch.empty_like(router_weights)
-            ops.combine_bwd_(flat, dy, K, d_rw)
-        d_rows = flat.new_empty(flat.shape)
+            ops.combine_bwd_(rows, dy, K, d_rw, inv_perm)
+        d_rows = rows.new_empty(rows.shape)
         ops.gather_rows_(dy, perm, router_weights.view(-1), K, None, d_rows)
         return d_rows, d_rw, None, None
 

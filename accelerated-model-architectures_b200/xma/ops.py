@@ -8,6 +8,7 @@ the current CUDA stream to one `extern "C"` function of libxma_b200.so.
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -113,24 +114,26 @@ def _gather_rows_op(
 
 
 @torch.library.custom_op(f"{_NS}::combine_rows", mutates_args={"y"}, device_types="cuda")
-def _combine_rows_op(ys: Tensor, weights: Optional[Tensor], top_k: int, y: Tensor) -> None:
+def _combine_rows_op(ys: Tensor, weights: Optional[Tensor], top_k: int, y: Tensor,
+                     row_index: Optional[Tensor] = None) -> None:
     require_cuda(ys, y)
     check(
         lib.xma_b200_combine_rows(
-            ptr(ys), dtype_code(ys.dtype), _row_stride(ys), ptr(weights), top_k, y.size(0), y.size(1), ptr(y),
-            _row_stride(y), current_stream(ys.device)
+            ptr(ys), dtype_code(ys.dtype), _row_stride(ys), ptr(weights), ptr(row_index), top_k, y.size(0),
+            y.size(1), ptr(y), _row_stride(y), current_stream(ys.device)
         ),
         "xma_b200_combine_rows",
     )
 
 
 @torch.library.custom_op(f"{_NS}::combine_bwd", mutates_args={"d_weights"}, device_types="cuda")
-def _combine_bwd_op(ys: Tensor, dy: Tensor, top_k: int, d_weights: Tensor) -> None:
+def _combine_bwd_op(ys: Tensor, dy: Tensor, top_k: int, d_weights: Tensor,
+                    row_index: Optional[Tensor] = None) -> None:
     require_cuda(ys, dy, d_weights)
     check(
         lib.xma_b200_combine_bwd(
-            ptr(ys), dtype_code(ys.dtype), _row_stride(ys), ptr(dy), _row_stride(dy), top_k, dy.size(0),
-            dy.size(1), ptr(d_weights), current_stream(ys.device)
+            ptr(ys), dtype_code(ys.dtype), _row_stride(ys), ptr(dy), _row_stride(dy), ptr(row_index), top_k,
+            dy.size(0), dy.size(1), ptr(d_weights), current_stream(ys.device)
         ),
         "xma_b200_combine_bwd",
     )
@@ -281,8 +284,9 @@ swiglu_packed_fwd_ = _wrap(_swiglu_packed_fwd_op, "swiglu_packed_fwd", 1)
 swiglu_packed_bwd_ = _wrap(_swiglu_packed_bwd_op, "swiglu_packed_bwd", 1)
 
 
-# Kernel-family override for the grouped GEMMs, used by tests: 0 automatic, 1 CUDA cores, 2 tcgen05.
-GEMM_IMPL = _lib.IMPL_AUTO
+# Kernel-family override for the grouped GEMMs (tests, tuning): 0 automatic, 1 CUDA cores,
+# 2 tcgen05 one CTA per tile, 3 tcgen05 CTA pairs. XMA_B200_GEMM_IMPL sets the initial value.
+GEMM_IMPL = int(os.environ.get("XMA_B200_GEMM_IMPL", _lib.IMPL_AUTO))
 
 
 def set_gemm_impl(impl: int) -> int:

@@ -92,7 +92,7 @@ int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_expert
  * exit) instead of a caller buffer, and nothing is allocated or freed. Outputs are identical to
  * xma_b200_count_sort. Limits: the scratch the problem needs
  * (xma_b200_count_sort_scratch_bytes) must not exceed
- * xma_b200_count_sort_static_scratch_limit() = 524544 bytes, e.g. up to 1 Mi ids with 256
+ * xma_b200_count_sort_static_scratch_limit() = 524544 bytes, e.g. up to 2 Mi ids with 256
  * experts, else XMA_ERR_TOO_LARGE (-8). The first call on a device resolves the array's device
  * address; issue it before any stream capture. Calls on one device share the array (cleared at
  * the start of each call); calls that overlap on the GPU race.
@@ -114,17 +114,20 @@ int xma_b200_gather_rows(const void* src, int dtype, int64_t src_row_stride, con
                          const void* coeff, int fan_out, int64_t rows, const int32_t* rows_in_use, int64_t width,
                          void* out, int64_t out_row_stride, cudaStream_t stream);
 
-/* y[t, :] = sum_k weights[t, k] * ys[t * top_k + k, :], fp32 accumulate, one rounding
- * (weights NULL: plain sum over the top_k slots).
+/* y[t, :] = sum_k weights[t, k] * ys[row(t * top_k + k), :], fp32 accumulate, one rounding
+ * (weights NULL: plain sum over the top_k slots). row(f) = row_index[f] when row_index is given
+ * (ys kept in another row order, e.g. expert-sorted), f otherwise.
  * Replaces the bmm combine and the K-slot sum:
  *   xma/layers/moe/triton_implementation/__init__.py:100-101 and :70. */
-int xma_b200_combine_rows(const void* ys, int dtype, int64_t ys_row_stride, const void* weights, int top_k,
-                          int64_t tokens, int64_t width, void* y, int64_t y_row_stride, cudaStream_t stream);
+int xma_b200_combine_rows(const void* ys, int dtype, int64_t ys_row_stride, const void* weights,
+                          const int32_t* row_index, int top_k, int64_t tokens, int64_t width, void* y,
+                          int64_t y_row_stride, cudaStream_t stream);
 
-/* d_weights[t, k] = <ys[t * top_k + k, :], dy[t, :]>.
+/* d_weights[t, k] = <ys[row(t * top_k + k), :], dy[t, :]>.
  * Replaces the bmm of xma/layers/moe/triton_implementation/__init__.py:130-131. */
 int xma_b200_combine_bwd(const void* ys, int dtype, int64_t ys_row_stride, const void* dy, int64_t dy_row_stride,
-                         int top_k, int64_t tokens, int64_t width, void* d_weights, cudaStream_t stream);
+                         const int32_t* row_index, int top_k, int64_t tokens, int64_t width, void* d_weights,
+                         cudaStream_t stream);
 
 /* ---- expert grouped GEMMs ------------------------------------------------------------------- */
 

@@ -45,7 +45,7 @@ def test_host_side_argument_errors_need_no_gpu():
     assert lib.xma_b200_tile_capacity(1024, 8) == 16
     assert lib.xma_b200_tile_capacity(-1, 8) < 0
     assert lib.xma_b200_count_sort_scratch_bytes(10, 2000) < 0  # more than 1024 experts
-    assert lib.xma_b200_count_sort_scratch_bytes(4097, 8) == 256 + 2 * 8 * 8
+    assert lib.xma_b200_count_sort_scratch_bytes(8193, 8) == 256 + 2 * 8 * 8
     # null pointers and bad dtypes are refused before anything is launched
     assert lib.xma_b200_continuous_count(None, _lib.I32, 10, 4, None, None, None) == -1
     assert lib.xma_b200_swiglu_fwd(None, 0, None, 0, None, 0, _lib.BF16, 4, 4, None) == -1

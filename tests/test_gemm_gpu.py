@@ -11,9 +11,10 @@ from oracle import moe_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
-SIMT, TC = 1, 2
+SIMT, TC, TC_PAIR = 1, 2, 3
 IMPLS = [pytest.param(SIMT, torch.float32, id="cudacore-f32"), pytest.param(SIMT, torch.bfloat16, id="cudacore-bf16"),
-         pytest.param(TC, torch.bfloat16, id="tcgen05-bf16"), pytest.param(TC, torch.float16, id="tcgen05-f16")]
+         pytest.param(TC, torch.bfloat16, id="tcgen05-bf16"), pytest.param(TC, torch.float16, id="tcgen05-f16"),
+         pytest.param(TC_PAIR, torch.bfloat16, id="pair-bf16"), pytest.param(TC_PAIR, torch.float16, id="pair-f16")]
 
 
 def _plan(counts, E):

@@ -133,6 +133,12 @@ def test_moe_16bit_tensor_cores(name, dtype):
     _run_and_compare(name, dtype, impl=2)
 
 
+@pytest.mark.parametrize("name", list(gi.MOE_CASES))
+def test_moe_bf16_tensor_core_pairs(name):
+    """tcgen05 cta_group::2 kernels (one 256 x 256 tile per CTA pair)."""
+    _run_and_compare(name, torch.bfloat16, impl=3)
+
+
 def test_moe_3d_input_and_backend_argument():
     from xma import KernelBackend
     from xma.layers import MoE, SwiGLU

@@ -59,3 +59,16 @@ def test_gather_combine(dtype, T, K, H):
     ops.combine_bwd_(ys, dy, K, dw)
     dw_ref = (ys.double().view(T, K, H) * dy.double().unsqueeze(1)).sum(-1)
     assert_close_rel(dw, dw_ref, 1e-5 if dtype == torch.float32 else tol, "combine backward")
+
+    # rows kept in another order and addressed through an index (the expert-parallel layer combines
+    # straight from expert-sorted rows)
+    order = torch.from_numpy(rng.permutation(R).astype(np.int32)).cuda()  # flat index f lives in row order[f]
+    shuffled = torch.empty_like(ys)
+    shuffled[order.long()] = ys
+    y2 = torch.empty(T, H, dtype=dtype, device="cuda")
+    ops.combine_rows_(shuffled, w, K, y2, order)
+    ops.combine_rows_(ys, w, K, y)
+    assert torch.equal(y2, y)
+    dw2 = torch.empty(T, K, dtype=dtype, device="cuda")
+    ops.combine_bwd_(shuffled, dy, K, dw2, order)
+    assert torch.equal(dw2, dw)
