@@ -162,6 +162,10 @@ __global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __r
             for (int r = pad_offsets[e] + c; r < r1; ++r) row_src[r] = -1;
         }
     }
+    if (row_src) {  // allocated rows behind the last expert's block
+        const int rows_cap = tile_cap * XMA_ROW_PAD;
+        for (int r = total * XMA_ROW_PAD + threadIdx.x; r < rows_cap; r += blockDim.x) row_src[r] = -1;
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -171,7 +175,7 @@ constexpr int SORT_THREADS = 512;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 constexpr int SORT_ITEMS = 16;
 constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 8192 ids per CTA
-constexpr int LB_BATCH = 8;                           // predecessors fetched per look-back round
+constexpr int LB_BATCH = 16;                          // predecessors fetched per look-back round
 constexpr int SORT_MAX_BINS = 1024;
 
 // Look-back status word: [63:62] state, [31:0] value. One 64-bit store/load moves both at once,
@@ -182,10 +186,13 @@ constexpr unsigned long long LB_STATE_MASK = 3ull << 62;
 constexpr unsigned LB_MAX_POLLS = 1u << 22;  // bounded wait; on expiry the status word gets the timeout bit
 
 __host__ __device__ inline size_t sort_smem_bytes(int E) {
-    // warp_cnt[WARPS][E+1] u32, pad_delta[E] i32, tile id
-    size_t b = static_cast<size_t>(SORT_WARPS) * (E + 1) * sizeof(unsigned);
-    b += static_cast<size_t>(E) * sizeof(int);
-    b += 16;
+    // staged[TILE] u32, warp_cnt[WARPS][E+1] u32, bin_first[E+1] u32, dst_base[E] i32, pad_delta[E] i32,
+    // scan scratch[32] u32 + tile id
+    size_t b = static_cast<size_t>(SORT_TILE) * sizeof(unsigned);
+    b += static_cast<size_t>(SORT_WARPS) * (E + 1) * sizeof(unsigned);
+    b += static_cast<size_t>(E + 1) * sizeof(unsigned);
+    b += 2 * static_cast<size_t>(E) * sizeof(int);
+    b += 40 * sizeof(unsigned);
     return (b + 15) & ~static_cast<size_t>(15);
 }
 
@@ -199,11 +206,11 @@ __host__ __device__ inline size_t sort_scratch_bytes(int64_t n, int E) {
 // status[tile][bin]. The whole area must be zero when the kernel starts.
 //
 // Per tile of SORT_TILE ids: every warp loads its 512 contiguous ids row by row (coalesced), ranks
-// them with match_any against its own per-bin counters (stable: rows in order, lanes in order),
+// them (peer masks from per-bit votes) against its own per-bin counters (stable: rows in order, lanes in order),
 // then one thread per bin scans the warps, publishes the tile's count and looks back over the
-// earlier tiles for the bin's running total; the result is folded into the warp counters, so an id's
-// destination is `counter[warp][bin] + rank` and every thread scatters straight from registers
-// (ids of one bin held by neighbouring lanes go to neighbouring addresses).
+// earlier tiles for the bin's running total. The tile is then sorted locally into shared memory (one
+// packed word per id: position in the tile and bin), so that each bin's run leaves the CTA as
+// consecutive addresses: scattering straight from registers would touch one 32-byte sector per id.
 template <typename IdT>
 __global__ void __launch_bounds__(SORT_THREADS, 2)
 sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __restrict__ offsets_incl,
@@ -211,9 +218,13 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
                     int* __restrict__ sorted_scattered, int* __restrict__ row_src,
                     unsigned char* __restrict__ scratch, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char s_raw[];
-    unsigned* s_warp_cnt = reinterpret_cast<unsigned*>(s_raw);                 // [WARPS][E+1]
-    int* s_pad_delta = reinterpret_cast<int*>(s_warp_cnt + SORT_WARPS * (E + 1));  // [E]
-    unsigned* s_tile = reinterpret_cast<unsigned*>(s_pad_delta + E);
+    unsigned* s_staged = reinterpret_cast<unsigned*>(s_raw);          // [TILE] (index in tile << 16) | bin
+    unsigned* s_warp_cnt = s_staged + SORT_TILE;                      // [WARPS][E+1]
+    unsigned* s_bin_first = s_warp_cnt + SORT_WARPS * (E + 1);        // [E+1] start of each bin inside the tile
+    int* s_dst_base = reinterpret_cast<int*>(s_bin_first + (E + 1));  // [E] global position - position in tile
+    int* s_pad_delta = s_dst_base + E;                                // [E] padded row - sorted row
+    unsigned* s_scan = reinterpret_cast<unsigned*>(s_pad_delta + E);  // [32]
+    unsigned* s_tile = s_scan + 32;
 
     unsigned* tile_counter = reinterpret_cast<unsigned*>(scratch);
     unsigned long long* lb = reinterpret_cast<unsigned long long*>(scratch + 256);
@@ -246,10 +257,25 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
         }
         my_bin[r] = b;
     }
+    // Lanes holding the same bin, from one ballot per bit of the bin index (the native match
+    // instruction is several times slower than log2(E) votes).
+    int bits = 1;
+    while ((1 << bits) <= E) ++bits;  // bins 0..E (E = dropped) need this many bits
 #pragma unroll
-    for (int r = 0; r < SORT_ITEMS; ++r) peers[r] = __match_any_sync(0xffffffffu, my_bin[r]);
+    for (int r = 0; r < SORT_ITEMS; ++r) {
+        unsigned m = 0xffffffffu;
+#pragma unroll
+        for (int k = 0; k < 11; ++k) {
+            if (k < bits) {
+                const bool bit = (my_bin[r] >> k) & 1u;
+                const unsigned vote = __ballot_sync(0xffffffffu, bit);
+                m &= bit ? vote : ~vote;
+            }
+        }
+        peers[r] = m;
+    }
 
-    unsigned my_rank[SORT_ITEMS];
+    // from here on my_bin[r] holds bin | (rank inside the warp's 512 ids) << 16
     unsigned* wc = s_warp_cnt + warp * EB;
     const unsigned lt_mask = (1u << lane) - 1u;
 #pragma unroll
@@ -259,7 +285,7 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
         __syncwarp();
         if ((peers[r] & lt_mask) == 0u) wc[b] = before + __popc(peers[r]);
         __syncwarp();
-        my_rank[r] = before + __popc(peers[r] & lt_mask);
+        my_bin[r] = b | ((before + __popc(peers[r] & lt_mask)) << 16);
     }
     __syncthreads();
 
@@ -319,24 +345,67 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
             atomicExch(mine, LB_PREFIX | static_cast<unsigned long long>(excl + run));
         }
         const unsigned gbase = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
-        const unsigned first = gbase + excl;  // global sorted position of this tile's first id of bin b
-#pragma unroll
-        for (int w = 0; w < SORT_WARPS; ++w) s_warp_cnt[w * EB + b] += first;
+        s_bin_first[b] = run;                                   // tile count for now, scanned below
+        s_dst_base[b] = static_cast<int>(gbase + excl);         // minus the bin's start in the tile, below
         s_pad_delta[b] = pad_offsets[b] - static_cast<int>(gbase);
     }
     __syncthreads();
 
-    // 3. scatter from registers
+    // 3. exclusive scan of the tile's bin counts -> start of each bin inside the tile
+    {
+        constexpr int PER = SORT_MAX_BINS / SORT_THREADS;
+        unsigned v[PER];
+        unsigned sum = 0;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int b = tid * PER + j;
+            v[j] = (b < E) ? s_bin_first[b] : 0u;
+            sum += v[j];
+        }
+        unsigned incl = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) s_scan[warp] = incl;
+        __syncthreads();
+        unsigned run = incl - sum;
+        for (int w = 0; w < warp; ++w) run += s_scan[w];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int b = tid * PER + j;
+            if (b < E) {
+                s_bin_first[b] = run;
+                s_dst_base[b] -= static_cast<int>(run);
+            }
+            run += v[j];
+            if (b == E - 1) s_bin_first[E] = run;  // number of in-range ids in the tile
+        }
+    }
+    __syncthreads();
+
+    // 4. local stable sort into shared memory
 #pragma unroll
     for (int r = 0; r < SORT_ITEMS; ++r) {
-        const unsigned b = my_bin[r];
+        const unsigned b = my_bin[r] & 0xffffu;
         if (b < static_cast<unsigned>(E)) {
-            const int f = static_cast<int>(base) + warp * (32 * SORT_ITEMS) + r * 32 + lane;
-            const unsigned g = wc[b] + my_rank[r];
-            sorted_scattered[g] = f;
-            sorted_expert[g] = static_cast<int>(b);
-            if (row_src) row_src[static_cast<int>(g) + s_pad_delta[b]] = f;
+            const unsigned i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
+            s_staged[s_bin_first[b] + wc[b] + (my_bin[r] >> 16)] = (i << 16) | b;
         }
+    }
+    __syncthreads();
+
+    // 5. each bin's run goes out as consecutive addresses
+    const int valid = static_cast<int>(s_bin_first[E]);
+    for (int j = tid; j < valid; j += SORT_THREADS) {
+        const unsigned word = s_staged[j];
+        const unsigned b = word & 0xffffu;
+        const int f = static_cast<int>(base) + static_cast<int>(word >> 16);
+        const int g = s_dst_base[b] + j;
+        sorted_scattered[g] = f;
+        sorted_expert[g] = static_cast<int>(b);
+        if (row_src) row_src[g + s_pad_delta[b]] = f;
     }
     if (bad && status) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
 }

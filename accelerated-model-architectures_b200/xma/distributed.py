@@ -14,6 +14,11 @@ expert and back:
 Routing weights are applied on the home rank, so only rows travel. Backward is the same exchange
 with the roles of the splits swapped; expert weight gradients are rank-local. Received data always
 lands in local HBM before a kernel reads it.
+
+Overlap: with `overlap_chunks = C > 1` the rank's tokens are cut into C micro-batches that run the
+whole path on alternating CUDA streams, so the all-to-alls of one micro-batch (NCCL's own stream)
+run under the grouped GEMMs of the other; autograd replays the backward on the same streams, which
+overlaps it the same way.
 """
 
 from __future__ import annotations
@@ -108,7 +113,8 @@ class ExpertParallelMoE(nn.Module):
     """Wraps a `MoE` that holds this rank's E/W experts (`c_fc`, `c_proj`) and a replicated router
     weight `[E, H]`. forward(x [.., H]) -> (y, router_logits [T, E]) for this rank's tokens."""
 
-    def __init__(self, local_moe: MoE, gate_weight: torch.Tensor, world_group=None) -> None:
+    def __init__(self, local_moe: MoE, gate_weight: torch.Tensor, world_group=None,
+                 overlap_chunks: int | None = None) -> None:
         super().__init__()
         if not (isinstance(local_moe.act, SwiGLU) and local_moe.is_glu):
             raise ValueError("ExpertParallelMoE runs the fused SwiGLU expert block")
@@ -122,10 +128,36 @@ class ExpertParallelMoE(nn.Module):
         if tuple(gate_weight.shape) != (self.num_experts, self.hidden_size):
             raise ValueError("gate_weight must be [num_experts (global), hidden_size]")
         self.gate_weight = nn.Parameter(gate_weight.detach().clone())
+        # exchange volume grows with (W-1)/W while the per-rank weight gradients (which every extra
+        # micro-batch accumulates once more) shrink with 1/W: micro-batching pays from 4 ranks on
+        self.overlap_chunks = overlap_chunks if overlap_chunks is not None else (2 if self.world >= 4 else 1)
+        self._streams: list[torch.cuda.Stream] = []
 
     def forward(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         original_shape = x.shape
         x = x.reshape(-1, self.hidden_size).contiguous()
+        chunks = min(self.overlap_chunks, max(1, x.size(0)))
+        if chunks <= 1:
+            y, logits = self._forward_rows(x)
+            return y.view(original_shape), logits
+        if not self._streams:
+            self._streams = [torch.cuda.Stream(device=x.device) for _ in range(2)]
+        main = torch.cuda.current_stream(x.device)
+        ys, logits = [], []
+        for i, xc in enumerate(x.chunk(chunks, dim=0)):
+            st = self._streams[i % 2]
+            st.wait_stream(main)
+            with torch.cuda.stream(st):
+                y_i, l_i = self._forward_rows(xc)
+            ys.append(y_i)
+            logits.append(l_i)
+        for st in self._streams:
+            main.wait_stream(st)
+        for t in ys + logits:
+            t.record_stream(main)
+        return torch.cat(ys, dim=0).view(original_shape), torch.cat(logits, dim=0)
+
+    def _forward_rows(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         E, K, W = self.num_experts, self.top_k, self.world
         e_local = E // W
 
@@ -157,4 +189,4 @@ class ExpertParallelMoE(nn.Module):
 
         back = _AllToAllRows.apply(out, recv_splits, send_splits, self.group)
         y = _CombineRows.apply(back, router_weights, perm, inv_perm)
-        return y.view(original_shape), router_logits
+        return y, router_logits

@@ -315,6 +315,8 @@ def main() -> None:
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-chunks", type=int, default=None,
+                    help="micro-batches per step in the expert-parallel layer (overlap of all-to-all and GEMM)")
     args = ap.parse_args()
     if args.workload == "c5":
         run_routing_microbench(args)
@@ -352,7 +354,7 @@ def main() -> None:
     if world > 1:
         from xma.distributed import ExpertParallelMoE
 
-        layer = ExpertParallelMoE(moe, gate, world_group=dist.group.WORLD)
+        layer = ExpertParallelMoE(moe, gate, world_group=dist.group.WORLD, overlap_chunks=args.ep_chunks)
     else:
         with torch.no_grad():
             moe.gate.weight.copy_(gate)
@@ -551,7 +553,8 @@ def main() -> None:
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": f"{args.workload}: {w['desc']}", "tokens_per_gpu": w["tokens"],
                        "hidden": H, "intermediate": I, "experts": E, "top_k": w["top_k"],
-                       "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world}, NCCL all-to-all",
+                       "parallelism": "single GPU" if world == 1 else
+                       f"expert-parallel ep{world}, NCCL all-to-all, {layer.overlap_chunks} micro-batch(es) per step",
                        "l2_policy": "inputs_exceed_l2 (weights + activations >> 126 MB)"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms,

@@ -53,4 +53,8 @@ def test_compiled_moe_matches_eager(fused):
     eager = run(moe)
     compiled = run(torch.compile(moe, fullgraph=True))
     for a, b in zip(eager, compiled):
-        assert torch.equal(a, b)
+        if fused:
+            assert torch.equal(a, b)  # only opaque custom ops between the inputs and the outputs
+        else:
+            # the user activation (nn.GLU) is compiled by inductor, which may round differently from eager
+            torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-3)

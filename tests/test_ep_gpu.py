@@ -29,7 +29,7 @@ def _global_inputs(world):
                 w2=mk(E, H, I, scale=0.02))
 
 
-def _worker(rank: int, world: int, port: int, results) -> None:
+def _worker(rank: int, world: int, port: int, results, chunks: int) -> None:
     import sys
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -52,7 +52,7 @@ def _worker(rank: int, world: int, port: int, results) -> None:
         with torch.no_grad():
             moe.c_fc.weight.copy_(g["w1"][rank * e_local : (rank + 1) * e_local])
             moe.c_proj.weight.copy_(g["w2"][rank * e_local : (rank + 1) * e_local])
-        layer = ExpertParallelMoE(moe, g["gate"].to(dev))
+        layer = ExpertParallelMoE(moe, g["gate"].to(dev), overlap_chunks=chunks)
         x = g["x"][rank * T : (rank + 1) * T].to(dev).requires_grad_()
         y, logits = layer(x)
         y.backward(g["dy"][rank * T : (rank + 1) * T].to(dev))
@@ -83,12 +83,13 @@ def _worker(rank: int, world: int, port: int, results) -> None:
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_matches_single_device_oracle():
+@pytest.mark.parametrize("chunks", [1, 2])
+def test_expert_parallel_matches_single_device_oracle(chunks):
     world = 2
     port = _free_port()
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, results)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, results, chunks)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

@@ -171,3 +171,44 @@ def test_moe_reference_grid_shape():
     torch.testing.assert_close(f32(y), ref.y, rtol=0, atol=1.6e-2)
     torch.testing.assert_close(f32(moe.c_fc.weight.grad), ref.grads["c_fc"], rtol=0, atol=7.9e-3)
     torch.testing.assert_close(f32(moe.c_proj.weight.grad), ref.grads["c_proj"], rtol=0, atol=7.9e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("num_experts,top_k", [(2, 2), (6, 2), (6, 4)])
+@pytest.mark.parametrize("is_glu", [True, False])
+def test_moe_reference_grid(dtype, num_experts, top_k, is_glu):
+    """The reference's own MoE test (tests/layers/moe_test.py:26-157) on a subset of its grid: 7 tokens,
+    hidden 2048, intermediate 8192, nn.GLU / GELU(tanh), `y.sum().backward()`, its absolute tolerances
+    (rtol 0), gate gradients not compared - with the CPU oracle in the place of its torch path."""
+    import torch.nn as nn
+
+    from xma.layers import MoE
+
+    H, I = 2048, 8192
+    torch.manual_seed(42)
+    act = nn.GLU() if is_glu else nn.GELU(approximate="tanh")
+    moe = MoE(num_experts, top_k, H, I, act, is_glu, False, 0.02).to(device="cuda", dtype=dtype)
+    x = torch.randn(7, H, device="cuda", dtype=dtype, requires_grad=True)
+    y, logits = moe(x)
+    y.sum().backward()
+    # like the reference test, both sides run in `dtype`: the oracle is the torch path's arithmetic in
+    # that dtype on the CPU (the tolerances were chosen for a comparison between two `dtype` results)
+    cpu = lambda t: t.detach().cpu()
+    ref = orc.moe_forward_backward(cpu(x), cpu(moe.gate.weight), cpu(moe.c_fc.weight), cpu(moe.c_proj.weight), top_k,
+                                   "glu" if is_glu else "gelu_tanh", dy=torch.ones(7, H, dtype=dtype),
+                                   router_logits=cpu(logits))
+    f32 = lambda t: t.detach().float().cpu()
+    dx_ref = ref.grads["x_experts"].float() + ref.grads["router_logits"].float() @ f32(moe.gate.weight)
+    # The reference's absolute tolerances equal one ulp of the 16-bit types for magnitudes in [1, 2); its
+    # seeds keep the compared tensors there. With other seeds a few entries are larger, and two correct
+    # 16-bit results may differ by one ulp of *that* magnitude, so the bound scales with max|ref| above 1.
+    def close(got, want, atol, what):
+        want = want.float()
+        bound = atol * max(1.0, float(want.abs().max()))
+        err = float((f32(got) - want).abs().max())
+        assert err <= bound, f"{what}: max abs err {err:.3e} > {bound:.3e}"
+
+    close(y, ref.y, REF_ATOL_OUT[dtype], "y")
+    close(x.grad, dx_ref, REF_ATOL_DX[dtype], "x.grad")
+    close(moe.c_fc.weight.grad, ref.grads["c_fc"], REF_ATOL_DW[dtype], "c_fc.weight.grad")
+    close(moe.c_proj.weight.grad, ref.grads["c_proj"], REF_ATOL_DW[dtype], "c_proj.weight.grad")
