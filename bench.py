@@ -93,10 +93,16 @@ class ClockSampler:
 
         def pump():
             for line in self.proc.stdout:
-                self.lines.append(line.strip())
+                self.lines.append((time.time(), line.strip()))
 
         self.thread = threading.Thread(target=pump, daemon=True)
         self.thread.start()
+
+    def mark_begin(self) -> None:
+        self.t_begin = time.time()
+
+    def mark_end(self) -> None:
+        self.t_end = time.time()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -108,7 +114,11 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        t0 = getattr(self, "t_begin", 0.0)
+        t1 = getattr(self, "t_end", float("inf")) + 0.05
+        for stamp, line in self.lines:
+            if not (t0 <= stamp <= t1):
+                continue  # keep the samples taken while the timed region ran
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -392,23 +402,25 @@ def main() -> None:
         return float(t.item())
 
     # ---- device-resident timing --------------------------------------------------------------
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    sampler.start()  # nvidia-smi needs a moment to come up; samples are filtered to the timed region
     for _ in range(max(args.warmup, 3)):
         step(x_dev, dy_dev)
     barrier()
     _lib.raise_on_device_status(device)
 
-    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
-                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
     ops.STATS.enabled, ops.STATS.timing = True, True
     ops.STATS.reset()
-    sampler.start()
     barrier()
+    sampler.mark_begin()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     for _ in range(args.steps):
         step(x_dev, dy_dev)
     t_end.record()
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop()
     ms_total = max_over_ranks(t_start.elapsed_time(t_end))
     launches = ops.STATS.launches
