@@ -204,8 +204,8 @@ def cpu_step_tokens_per_s(w: dict, sample_tokens: int, steps: int, warmup: int) 
 
 
 def cpu_sample_tokens(w: dict) -> int:
-    # about 10-30 s of CPU work in total: the survey measured ~0.26 TFLOP/s bf16 on 8 cores
-    target_flops = 2.0e12
+    # about 10-30 s of CPU work in total (a 16-core host sustains roughly 1.5-2 TFLOP/s bf16 on this path)
+    target_flops = 2.0e13
     per_token = expert_flops(w, 1)
     return int(max(64, min(w["tokens"], 2 ** int(np.log2(max(target_flops / per_token, 64))))))
 
@@ -503,17 +503,17 @@ def main() -> None:
             per_kernel[name]["tflops"] = gemm_flops[name] / (per_kernel[name]["ms_avg"] * 1e-3) / 1e12
     # One entry per kernel function; the dominant one (largest share of the timed region) gets the roofline.
     kernel_functions = {
-        "rows_gemm_tc_kernel<T, W_NK, SwiGLU> (up projection)": ["gemm_up_swiglu"],
+        "rows_gemm_tc2_kernel<T, W_NK, SwiGLU> (up projection, CTA pairs)": ["gemm_up_swiglu"],
         "rows_gemm_tc_kernel<T, W_NK, plain> (down projection)": ["gemm_down"],
-        "rows_gemm_tc_kernel<T, W_KN, dSwiGLU> (d activation)": ["gemm_dact_dswiglu"],
+        "rows_gemm_tc2_kernel<T, W_KN, dSwiGLU> (d activation, CTA pairs)": ["gemm_dact_dswiglu"],
         "rows_gemm_tc_kernel<T, W_KN, plain> (d input)": ["gemm_dx"],
-        "dw_gemm_tc_kernel<T> (dW1 and dW2)": ["gemm_dw1", "gemm_dw2"],
+        "dw_gemm_tc2_kernel<T> (dW1 and dW2, CTA pairs)": ["gemm_dw1", "gemm_dw2"],
     }
     # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures of the
     # 2-expert slice `c2e2` summarised in profiles/ncu_grouped_gemm_tcgen05_c2e2.md; traffic grows in
     # proportion to the number of experts at fixed rows per expert, so configs[1] moves experts/2 times this.
-    ncu_traffic_c2e2 = {"gemm_up_swiglu": 1.491e9, "gemm_down": 1.280e9, "gemm_dact_dswiglu": 1.776e9,
-                        "gemm_dw1": 1.216e9, "gemm_dw2": 1.222e9}
+    ncu_traffic_c2e2 = {"gemm_up_swiglu": 1.435e9, "gemm_down": 1.279e9, "gemm_dact_dswiglu": 1.784e9,
+                        "gemm_dx": 2.500e9, "gemm_dw1": 1.524e9, "gemm_dw2": 0.782e9}
     peak = float(peaks.get("bf16_tflops_sustained", PEAK_FALLBACK["bf16_tflops_sustained"]))
     groups = {}
     for fn, tags in kernel_functions.items():
