@@ -18,9 +18,9 @@ int check_rows(const xma::RowsGemmArgs& g) {
     if (g.num_experts <= 0 || g.tile_cap < 0 || g.kd <= 0 || g.n <= 0) return XMA_ERR_BAD_SHAPE;
     if (g.dtype != XMA_F32 && g.dtype != XMA_F16 && g.dtype != XMA_BF16) return XMA_ERR_BAD_DTYPE;
     if (g.w_layout != xma::W_NK && g.w_layout != xma::W_KN) return XMA_ERR_BAD_SHAPE;
-    if (g.epilogue < xma::EPI_PLAIN || g.epilogue > xma::EPI_DSWIGLU) return XMA_ERR_BAD_SHAPE;
+    if (g.epilogue < xma::EPI_PLAIN || g.epilogue > xma::EPI_DSWIGLU_PACKED) return XMA_ERR_BAD_SHAPE;
     if (g.epilogue != xma::EPI_PLAIN && !g.aux) return XMA_ERR_NULL_POINTER;
-    if (g.epilogue == xma::EPI_SWIGLU && (g.n % 2)) return XMA_ERR_BAD_SHAPE;
+    if ((g.epilogue == xma::EPI_SWIGLU || g.epilogue == xma::EPI_SWIGLU_PACKED) && (g.n % 2)) return XMA_ERR_BAD_SHAPE;
     return XMA_OK;
 }
 

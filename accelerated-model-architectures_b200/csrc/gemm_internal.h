@@ -18,7 +18,9 @@ enum WeightLayout { W_NK = 0, W_KN = 1 };
 //                 out[r, 0:I] = up * gate * sigmoid(gate) computed from the rounded halves.
 //   EPI_DSWIGLU : N = I.  aux holds gate|up [r, 0:2I]; out[r, 0:I] = d gate, out[r, I:2I] = d up,
 //                 where acc is the gradient of the activation output.
-enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2 };
+//   EPI_SWIGLU_PACKED / EPI_DSWIGLU_PACKED : the same with gate/up interleaved along the columns
+//                 (g, u, g, u, ...) in aux and in the weight rows, as swiglu_packed expects.
+enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2, EPI_SWIGLU_PACKED = 3, EPI_DSWIGLU_PACKED = 4 };
 
 struct RowsGemmArgs {
     const void* a;             // [rows_cap, Kd] grouped (padded) rows

@@ -167,6 +167,9 @@ static int dw_gemm_simt_t(const DwGemmArgs& g) {
 }
 
 int rows_gemm_simt(const RowsGemmArgs& g) {
+    // the interleaved SwiGLU epilogues exist on the tensor-core kernels only (the caller composes
+    // a plain GEMM with the stand-alone swiglu_packed kernels instead)
+    if (g.epilogue == EPI_SWIGLU_PACKED || g.epilogue == EPI_DSWIGLU_PACKED) return XMA_ERR_UNSUPPORTED;
     if (g.tile_cap == 0) return XMA_OK;
     switch (g.dtype) {
         case XMA_F32: return rows_gemm_simt_t<float>(g);

@@ -355,7 +355,7 @@ static int launch_rows(const RowsGemmArgs& g, const CUtensorMap& ta, const CUten
     int rc = set_smem(kernel);
     if (rc) return rc;
     const uint32_t idesc = make_idesc(g.dtype, false, WL == W_KN);
-    kernel<<<num_sms(), block_threads(EPI == EPI_DSWIGLU ? 8 : 4), SMEM_BYTES, g.stream>>>(
+    kernel<<<num_sms(), block_threads((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) ? 8 : 4), SMEM_BYTES, g.stream>>>(
         ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
         g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
     return static_cast<int>(cudaGetLastError());
@@ -369,6 +369,8 @@ static int rows_dispatch(const RowsGemmArgs& g, const CUtensorMap& ta, const CUt
     XMA_ROWS_CASE(W_NK, EPI_SWIGLU);
     XMA_ROWS_CASE(W_KN, EPI_PLAIN);
     XMA_ROWS_CASE(W_KN, EPI_DSWIGLU);
+    XMA_ROWS_CASE(W_NK, EPI_SWIGLU_PACKED);
+    XMA_ROWS_CASE(W_KN, EPI_DSWIGLU_PACKED);
 #undef XMA_ROWS_CASE
     return XMA_ERR_UNSUPPORTED;
 }
@@ -381,12 +383,14 @@ bool rows_gemm_tc_supported(const RowsGemmArgs& g) {
     if (g.num_experts > tc::MAX_EXPERTS || g.kd <= 0 || g.n <= 0) return false;
     if (g.kd % 8 || g.n % 8 || g.a_stride % 8 || g.out_stride % 8) return false;
     if (!is_aligned16(g.a) || !is_aligned16(g.w) || !is_aligned16(g.out)) return false;
-    const bool combo = (g.w_layout == W_NK && (g.epilogue == EPI_PLAIN || g.epilogue == EPI_SWIGLU)) ||
-                       (g.w_layout == W_KN && (g.epilogue == EPI_PLAIN || g.epilogue == EPI_DSWIGLU));
+    const bool combo = (g.w_layout == W_NK && (g.epilogue == EPI_PLAIN || g.epilogue == EPI_SWIGLU ||
+                                               g.epilogue == EPI_SWIGLU_PACKED)) ||
+                       (g.w_layout == W_KN && (g.epilogue == EPI_PLAIN || g.epilogue == EPI_DSWIGLU ||
+                                               g.epilogue == EPI_DSWIGLU_PACKED));
     if (!combo) return false;
     if (g.epilogue != EPI_PLAIN) {
         if (!g.aux || g.aux_stride % 8 || !is_aligned16(g.aux) || g.row_map) return false;
-        if (g.epilogue == EPI_SWIGLU && (g.n % 16)) return false;
+        if ((g.epilogue == EPI_SWIGLU || g.epilogue == EPI_SWIGLU_PACKED) && (g.n % 16)) return false;
     }
     if (static_cast<int64_t>(g.num_experts) * g.n > 0x7fffffffLL || static_cast<int64_t>(g.num_experts) * g.kd > 0x7fffffffLL ||
         g.tile_cap * XMA_ROW_PAD > 0x7fffffffLL)

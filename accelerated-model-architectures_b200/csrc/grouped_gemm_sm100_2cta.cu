@@ -455,7 +455,7 @@ static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUte
     int rc = set_smem2(kernel);
     if (rc) return rc;
     const uint32_t idesc = make_idesc_mn(g.dtype, false, WL == W_KN, 2 * BM, BN);
-    kernel<<<pair_grid(), block_threads(EPI == EPI_DSWIGLU ? 8 : 4), SMEM2_BYTES, g.stream>>>(
+    kernel<<<pair_grid(), block_threads((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) ? 8 : 4), SMEM2_BYTES, g.stream>>>(
         ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
         g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
     return static_cast<int>(cudaGetLastError());
@@ -469,6 +469,8 @@ static int rows_dispatch2(const RowsGemmArgs& g, const CUtensorMap& ta, const CU
     XMA_ROWS2_CASE(W_NK, EPI_SWIGLU);
     XMA_ROWS2_CASE(W_KN, EPI_PLAIN);
     XMA_ROWS2_CASE(W_KN, EPI_DSWIGLU);
+    XMA_ROWS2_CASE(W_NK, EPI_SWIGLU_PACKED);
+    XMA_ROWS2_CASE(W_KN, EPI_DSWIGLU_PACKED);
 #undef XMA_ROWS2_CASE
     return XMA_ERR_UNSUPPORTED;
 }

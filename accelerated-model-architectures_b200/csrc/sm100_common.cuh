@@ -291,6 +291,77 @@ __device__ __forceinline__ bool rows_epilogue_tile(uint64_t* acc_full_bar, uint3
                 }
             }
         }
+    } else if (EPI == EPI_SWIGLU_PACKED) {
+        // gate/up interleaved along the columns (g, u, g, u, ...): one thread holds whole pairs.
+        // aux[r, 0:n] = rounded contraction, out[r, 0:n/2] = activation.
+        const int n0 = n_tile * BN;
+        if (!mbar_wait(acc_full_bar, parity, abort_flag)) return false;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = part * chunks; c < (part + 1) * chunks; ++c) {
+            uint32_t v[32];
+            tmem_ld32(taddr + c * 32, v);
+            tmem_ld_wait();
+            const int col = n0 + c * 32;
+            if (col < n) {
+                T* pa = aux + r * aux_stride + col;
+                T* po = out + r * out_stride + col / 2;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {  // 16 interleaved columns -> 8 outputs
+                    if (col + 16 * i < n) {
+                        float gu[16], ac[8];
+#pragma unroll
+                        for (int t = 0; t < 16; ++t) gu[t] = round_to<T>(__uint_as_float(v[16 * i + t]));
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) ac[t] = gu[2 * t + 1] * gu[2 * t] * fast_sigmoid(gu[2 * t]);
+                        *reinterpret_cast<uint4*>(pa + 16 * i) = pack8<T>(gu);
+                        *reinterpret_cast<uint4*>(pa + 16 * i + 8) = pack8<T>(gu + 8);
+                        *reinterpret_cast<uint4*>(po + 8 * i) = pack8<T>(ac);
+                    }
+                }
+            }
+        }
+    } else if (EPI == EPI_DSWIGLU_PACKED) {
+        // n = activation width; aux[r, 0:2n] holds gate/up interleaved; out[r, 0:2n] = d gate/d up interleaved
+        const int n0 = n_tile * BN;
+        const T* pg_row = aux + r * aux_stride;
+        T* pd_row = out + r * out_stride;
+        uint4 q[2][8];
+        auto fetch = [&](int c, int b) {
+            const int col = n0 + c * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (col + 4 * i < n) q[b][i] = *reinterpret_cast<const uint4*>(pg_row + 2 * col + 8 * i);
+        };
+        fetch(part * chunks, 0);
+        if (!mbar_wait(acc_full_bar, parity, abort_flag)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < BN / 32; ++cc) {
+            if (cc >= chunks) break;
+            const int c = part * chunks + cc;
+            if (cc + 1 < chunks) fetch(c + 1, (cc + 1) & 1);
+            uint32_t v[32];
+            tmem_ld32(taddr + c * 32, v);
+            tmem_ld_wait();
+            const int col = n0 + c * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {  // 4 activation columns = 8 interleaved values
+                if (col + 4 * i < n) {
+                    float gu[8], dd[8];
+                    unpack8<T>(q[cc & 1][i], gu);
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const float d = __uint_as_float(v[4 * i + t]);
+                        const float g = gu[2 * t], u = gu[2 * t + 1];
+                        const float sg = fast_sigmoid(g);
+                        dd[2 * t] = d * u * sg * (1.0f + g * (1.0f - sg));
+                        dd[2 * t + 1] = d * g * sg;
+                    }
+                    *reinterpret_cast<uint4*>(pd_row + 2 * col + 8 * i) = pack8<T>(dd);
+                }
+            }
+        }
     } else {  // EPI_DSWIGLU: n is the activation width
         const int n0 = n_tile * BN;
         const T* pg_row = aux + r * aux_stride;

@@ -17,8 +17,8 @@ _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "lib
 F32, F16, BF16, I32, I64 = 0, 1, 2, 3, 4
 ROW_PAD = 128
 W_NK, W_KN = 0, 1
-EPI_PLAIN, EPI_SWIGLU, EPI_DSWIGLU = 0, 1, 2
-IMPL_AUTO, IMPL_SIMT, IMPL_TC = 0, 1, 2
+EPI_PLAIN, EPI_SWIGLU, EPI_DSWIGLU, EPI_SWIGLU_PACKED, EPI_DSWIGLU_PACKED = 0, 1, 2, 3, 4
+IMPL_AUTO, IMPL_SIMT, IMPL_TC, IMPL_TC_PAIR = 0, 1, 2, 3
 
 DEV_ID_OUT_OF_RANGE, DEV_WAIT_TIMEOUT, DEV_BAD_TILE = 1, 2, 4
 

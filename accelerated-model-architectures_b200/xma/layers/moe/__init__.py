@@ -19,7 +19,8 @@ import torch
 import torch.nn as nn
 
 from ... import ops
-from ..._lib import EPI_DSWIGLU, EPI_PLAIN, EPI_SWIGLU, ROW_PAD, W_KN, W_NK
+from ..._lib import (EPI_DSWIGLU, EPI_DSWIGLU_PACKED, EPI_PLAIN, EPI_SWIGLU, EPI_SWIGLU_PACKED, IMPL_SIMT, ROW_PAD,
+                     W_KN, W_NK, dtype_code, lib)
 from ...accelerator import KernelBackend, resolve_kernel_backend
 from ...functional import swiglu, swiglu_packed
 
@@ -213,9 +214,11 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
     output is returned in the order of x (the expert-parallel layer combines on the home rank)."""
 
     @staticmethod
-    def forward(ctx, x, w1, w2, router_weights, counts, pad_offsets, tile_prefix, tile_expert, row_src):
+    def forward(ctx, x, w1, w2, router_weights, counts, pad_offsets, tile_prefix, tile_expert, row_src,
+                packed=False):
         E, two_i, H = w1.shape
         I = two_i // 2
+        ctx.packed = packed
         weighted = router_weights is not None
         T, K = router_weights.shape if weighted else (x.size(0), 1)
         row_cap = row_src.numel()
@@ -226,8 +229,8 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         ops.gather_rows_(x, row_src, None, K, pad_offsets[E:], xs)
         gu = torch.empty(row_cap, two_i, **opts)
         act = torch.empty(row_cap, I, **opts)
-        ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, tile_expert, tile_prefix, H, two_i, EPI_SWIGLU, impl,
-                               tag="gemm_up_swiglu")
+        ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, tile_expert, tile_prefix, H, two_i,
+                               EPI_SWIGLU_PACKED if packed else EPI_SWIGLU, impl, tag="gemm_up_swiglu")
         ys = torch.empty(T * K, H, **opts)
         ops.grouped_gemm_rows_(act, w2, W_NK, ys, None, row_src, tile_expert, tile_prefix, I, H, EPI_PLAIN, impl,
                                tag="gemm_down")
@@ -278,8 +281,8 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         d_x = d_w1 = None
         if need_x or need_w1:
             dgu = torch.empty(row_cap, two_i, **opts)
-            ops.grouped_gemm_rows_(dys, w2, W_KN, dgu, gu, None, tile_expert, tile_prefix, H, I, EPI_DSWIGLU, impl,
-                                   tag="gemm_dact_dswiglu")
+            ops.grouped_gemm_rows_(dys, w2, W_KN, dgu, gu, None, tile_expert, tile_prefix, H, I,
+                                   EPI_DSWIGLU_PACKED if ctx.packed else EPI_DSWIGLU, impl, tag="gemm_dact_dswiglu")
             if need_w1:
                 d_w1 = torch.empty_like(w1)
                 ops.grouped_gemm_dw_(dgu, xs, counts, pad_offsets, d_w1, impl, tag="gemm_dw1")
@@ -292,7 +295,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
                 else:
                     d_x = torch.empty(T, H, **opts)
                     ops.combine_rows_(dxs, None, K, d_x)
-        return d_x, d_w1, d_w2, d_rw, None, None, None, None, None
+        return d_x, d_w1, d_w2, d_rw, None, None, None, None, None, None
 
 
 class Experts(nn.Module):
@@ -385,6 +388,14 @@ class MoE(nn.Module):
         # router_weights -> (total_q, top_k) in x.dtype, selected_experts -> (total_q, top_k) int32
         return router_logits, router_weights, selected_experts
 
+    def _tensor_cores(self, x: torch.Tensor) -> bool:
+        """True when the grouped GEMMs of this layer run on the tcgen05 kernels."""
+        if ops.GEMM_IMPL == IMPL_SIMT:
+            return False
+        code = dtype_code(x.dtype)
+        return bool(lib.xma_b200_grouped_gemm_uses_tensor_cores(code, self.hidden_size, self.intermediate_size)) \
+            and self.intermediate_size % 8 == 0
+
     def _compute_experts(
         self, x: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor
     ) -> torch.Tensor:
@@ -396,6 +407,9 @@ class MoE(nn.Module):
 
         if isinstance(self.act, SwiGLU) and self.is_glu:
             return _FusedSwiGLUExperts.apply(x, self.c_fc.weight, self.c_proj.weight, router_weights, *tensors)
+        if isinstance(self.act, SwiGLUPacked) and self.is_glu and self._tensor_cores(x):
+            # the interleaved epilogues exist on the tensor-core kernels only
+            return _FusedSwiGLUExperts.apply(x, self.c_fc.weight, self.c_proj.weight, router_weights, *tensors, True)
 
         h = _UpProjectionExperts.apply(x, self.c_fc.weight, self.top_k, *tensors)
         h = self.act(h)

@@ -136,7 +136,10 @@ int xma_b200_combine_bwd(const void* ys, int dtype, int64_t ys_row_stride, const
  *           1 = SwiGLU forward, n = 2I: aux[r, 0:2I] = gate|up (rounded), out[r, 0:I] = up*gate*sigmoid(gate);
  *           2 = SwiGLU backward, n = I: aux holds gate|up, the contraction is d(activation),
  *               out[r, 0:I] = d gate, out[r, I:2I] = d up.
- * impl: 0 = automatic, 1 = CUDA cores, 2 = tcgen05 tensor cores (bf16/fp16, widths multiple of 8).
+ *           3 / 4 = the same two with gate and up interleaved along the columns (g,u,g,u,...: the layout of
+ *               swiglu_packed); tensor-core kernels only (XMA_ERR_UNSUPPORTED otherwise).
+ * impl: 0 = automatic, 1 = CUDA cores, 2 = tcgen05 tensor cores with one CTA per 128x256 tile, 3 = tcgen05
+ *       with CTA pairs (cta_group::2, 256x256 tiles); 2 and 3 need bf16/fp16 and widths that are multiples of 8.
  * a is grouped [128 * tile_cap, kd]. fp32 accumulation everywhere.
  * Replaces scatter2scatter: xma/layers/moe/triton_implementation/scatter_kernel.py:137-183,
  * with swiglu fused as in xma/functional/swiglu/__init__.py:39. */

@@ -163,3 +163,55 @@ def test_dw_gemm(impl, dtype, counts, m, n):
         if counts[e] == 0:
             assert bool((dw[e] == 0).all()), "experts without rows must get exactly zero"
     assert _lib.read_and_clear_device_status() == 0
+
+
+@pytest.mark.parametrize("impl,dtype", [pytest.param(TC, torch.bfloat16, id="tcgen05-bf16"),
+                                        pytest.param(TC_PAIR, torch.bfloat16, id="pair-bf16"),
+                                        pytest.param(TC_PAIR, torch.float16, id="pair-f16")])
+@pytest.mark.parametrize("counts,kd,inter", [([5, 0, 130, 1], 64, 128), ([300, 7, 0, 129], 192, 200),
+                                             ([700, 100], 512, 1024)])
+def test_rows_gemm_packed_swiglu_epilogues(impl, dtype, counts, kd, inter):
+    """Epilogues 3 / 4: gate and up interleaved along the columns (the swiglu_packed layout)."""
+    from xma import _lib, ops
+
+    E, R = len(counts), int(sum(counts))
+    plan, _ = _plan(counts, E)
+    used = int(plan.pad_offsets[-1])
+    a, _ = _grouped(plan, R, kd, dtype, seed=8)
+    rng = np.random.RandomState(9)
+    w1 = torch.from_numpy((rng.standard_normal((E, 2 * inter, kd)) * 0.05).astype(np.float32)).to(dtype).cuda()
+    gu = torch.full((plan.row_cap, 2 * inter), float("nan"), dtype=dtype, device="cuda")
+    act = torch.full((plan.row_cap, inter), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(a, w1, _lib.W_NK, act, gu, None, plan.tile_expert, plan.tile_prefix, kd, 2 * inter,
+                           _lib.EPI_SWIGLU_PACKED, impl)
+    pad = plan.pad_offsets.cpu().tolist()
+    exp_gu = torch.zeros(plan.row_cap, 2 * inter, dtype=torch.float64)
+    for e in range(E):
+        r0, c = pad[e], counts[e]
+        if c:
+            exp_gu[r0 : r0 + c] = a[r0 : r0 + c].double().cpu() @ w1[e].double().cpu().t()
+    tol = REL_TOL[dtype]
+    assert_close_rel(gu[:used].cpu(), exp_gu[:used], tol, "gate/up interleaved")
+    stored = gu[:used].cpu().double()
+    g, u = stored[:, 0::2], stored[:, 1::2]
+    assert_close_rel(act[:used].cpu(), u * g * torch.sigmoid(g), tol / 2, "activation")
+
+    H = kd
+    dys, _ = _grouped(plan, R, H, dtype, seed=10)
+    w2 = torch.from_numpy((rng.standard_normal((E, H, inter)) * 0.05).astype(np.float32)).to(dtype).cuda()
+    dgu = torch.full((plan.row_cap, 2 * inter), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(dys, w2, _lib.W_KN, dgu, gu, None, plan.tile_expert, plan.tile_prefix, H, inter,
+                           _lib.EPI_DSWIGLU_PACKED, impl)
+    d_act = torch.zeros(plan.row_cap, inter, dtype=torch.float64)
+    for e in range(E):
+        r0, c = pad[e], counts[e]
+        if c:
+            d_act[r0 : r0 + c] = dys[r0 : r0 + c].double().cpu() @ w2[e].double().cpu()
+    s = torch.sigmoid(g)
+    assert_close_rel(dgu[:used, 0::2].cpu(), d_act[:used] * u * s * (1 + g * (1 - s)), 2 * tol, "d gate")
+    assert_close_rel(dgu[:used, 1::2].cpu(), d_act[:used] * g * s, 2 * tol, "d up")
+    assert _lib.read_and_clear_device_status() == 0
+    # the CUDA-core kernels do not have these epilogues
+    with pytest.raises(RuntimeError):
+        ops.grouped_gemm_rows_(a, w1, _lib.W_NK, act, gu, None, plan.tile_expert, plan.tile_prefix, kd, 2 * inter,
+                               _lib.EPI_SWIGLU_PACKED, SIMT)
