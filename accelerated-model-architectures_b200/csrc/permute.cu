@@ -88,35 +88,43 @@ combine_rows_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __rest
 }
 
 // dw[t, k] = sum_h ys[row(t*K+k), h] * dy[t, h]
+// Each warp owns whole (token, slot) rows, so a dot product is one warp reduction and the CTA never
+// synchronises (dy[t] is re-read from L1/L2 by the warps that share a token).
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
 combine_bwd_kernel(const T* __restrict__ ys, int64_t ys_stride, const T* __restrict__ dy, int64_t dy_stride,
                    const int* __restrict__ row_index, int K, int64_t tokens, int64_t width, T* __restrict__ dw) {
     constexpr int V = Vec16<T>::N;
-    __shared__ float s_part[ROW_THREADS / 32];
+    constexpr int WARPS = ROW_THREADS / 32;
     const int64_t nvec = width / V;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
-        for (int k = 0; k < K; ++k) {
+    const int64_t pairs = tokens * K;
+    for (int64_t q = static_cast<int64_t>(blockIdx.x) * WARPS + warp; q < pairs;
+         q += static_cast<int64_t>(gridDim.x) * WARPS) {
+        {
+            const int64_t t = q / K;
+            const T* dy_row = dy + t * dy_stride;
+            const int64_t r = row_index ? row_index[q] : q;
+            const T* ys_row = ys + r * ys_stride;
             float acc = 0.0f;
-            for (int64_t c = threadIdx.x; c < nvec; c += ROW_THREADS) {
-                const int64_t r = row_index ? row_index[t * K + k] : t * K + k;
-                Vec16<T> a = load16_stream(ys + r * ys_stride + c * V);
-                Vec16<T> b = load16(dy + t * dy_stride + c * V);
+            int64_t c = lane;
+            for (; c + 32 < nvec; c += 64) {  // two packets of each operand in flight
+                Vec16<T> a0 = load16_stream(ys_row + c * V), a1 = load16_stream(ys_row + (c + 32) * V);
+                Vec16<T> b0 = load16(dy_row + c * V), b1 = load16(dy_row + (c + 32) * V);
 #pragma unroll
-                for (int j = 0; j < V; ++j) acc = fmaf(to_f32(a.v[j]), to_f32(b.v[j]), acc);
+                for (int j = 0; j < V; ++j) acc = fmaf(to_f32(a0.v[j]), to_f32(b0.v[j]), acc);
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc = fmaf(to_f32(a1.v[j]), to_f32(b1.v[j]), acc);
+            }
+            for (; c < nvec; c += 32) {
+                Vec16<T> a0 = load16_stream(ys_row + c * V);
+                Vec16<T> b0 = load16(dy_row + c * V);
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc = fmaf(to_f32(a0.v[j]), to_f32(b0.v[j]), acc);
             }
 #pragma unroll
             for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (lane == 0) s_part[warp] = acc;
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                float s = 0.0f;
-#pragma unroll
-                for (int i = 0; i < ROW_THREADS / 32; ++i) s += s_part[i];
-                dw[t * K + k] = from_f32<T>(s);
-            }
-            __syncthreads();
+            if (lane == 0) dw[q] = from_f32<T>(acc);
         }
     }
 }
@@ -170,7 +178,7 @@ static int combine_bwd_impl(const void* ys, int64_t ys_stride, const void* dy, i
     constexpr int V = Vec16<T>::N;
     if (width % V || ys_stride % V || dy_stride % V || !is_aligned16(ys) || !is_aligned16(dy))
         return XMA_ERR_MISALIGNED;
-    combine_bwd_kernel<T><<<row_grid(tokens), ROW_THREADS, 0, stream>>>(
+    combine_bwd_kernel<T><<<row_grid(tokens * K, ROW_THREADS / 32), ROW_THREADS, 0, stream>>>(
         static_cast<const T*>(ys), ys_stride, static_cast<const T*>(dy), dy_stride, row_index, K, tokens, width,
         static_cast<T*>(dw));
     return static_cast<int>(cudaGetLastError());

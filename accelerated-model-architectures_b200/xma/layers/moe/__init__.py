@@ -401,6 +401,10 @@ class MoE(nn.Module):
     ) -> torch.Tensor:
         # the kernel path of the reference has no bias support either (xma/layers/moe/__init__.py:53,75)
         assert self.c_fc.bias is None and self.c_proj.bias is None, "expert biases are not supported"
+        if x.size(0) == 0:
+            # nothing is routed: an empty result that still hands exact zero gradients to every parameter
+            zero = (self.c_fc.weight.sum() + self.c_proj.weight.sum() + router_weights.sum()) * 0
+            return x + zero.to(x.dtype)
         x = x.contiguous()
         plan = build_route_plan(selected_experts, self.num_experts)
         tensors = _plan_tensors(plan)

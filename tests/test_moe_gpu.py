@@ -212,3 +212,16 @@ def test_moe_reference_grid(dtype, num_experts, top_k, is_glu):
     close(x.grad, dx_ref, REF_ATOL_DX[dtype], "x.grad")
     close(moe.c_fc.weight.grad, ref.grads["c_fc"], REF_ATOL_DW[dtype], "c_fc.weight.grad")
     close(moe.c_proj.weight.grad, ref.grads["c_proj"], REF_ATOL_DW[dtype], "c_proj.weight.grad")
+
+
+def test_moe_empty_batch():
+    """No tokens at all: every kernel gets a zero-sized problem and the gradients are exact zeros."""
+    from xma.layers import MoE, SwiGLU
+
+    moe = MoE(4, 2, 64, 128, SwiGLU(), True, False, 0.02).to(device="cuda", dtype=torch.bfloat16)
+    x = torch.zeros(0, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y, logits = moe(x)
+    assert y.shape == (0, 64) and logits.shape == (0, 4)
+    y.sum().backward()
+    assert x.grad.shape == (0, 64)
+    assert float(moe.c_fc.weight.grad.abs().max()) == 0.0 and float(moe.c_proj.weight.grad.abs().max()) == 0.0
