@@ -412,7 +412,7 @@ dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 continue;
             }
             const uint32_t buf = lt & 1u;
-            if (!mbar_wait(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
+            if (!mbar_wait_epilogue(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
@@ -445,6 +445,7 @@ static int pair_grid() { return num_sms() & ~1; }
 
 template <typename K>
 static int set_smem2(K kernel) {
+    apply_epilogue_tuning();
     return static_cast<int>(
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM2_BYTES)));
 }
