@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own torch path on CPU.
 
-Usage (in a container that has the reference tree):  python tests/golden/make_golden.py /root/reference
+Usage (in a container that has the reference tree):  python tests/golden/make_golden.py <path-to-reference-checkout>
 The reference package is loaded under the alias `xma_ref` (this repository's package is also called
 `xma`). Two harness-side adjustments, neither touching reference code:
   * `MoE._compute_experts` calls `continuous_count` without forwarding `kernel_backend`
@@ -145,4 +145,6 @@ def main(root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path-to-reference-checkout>")
+    main(sys.argv[1])
