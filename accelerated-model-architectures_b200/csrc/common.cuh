@@ -46,6 +46,11 @@
 
 namespace xma {
 
+// Expert-parallel row maps address a row of another rank's buffer as (rank << 24) | row.
+constexpr int PEER_ROW_BITS = 24;
+constexpr int PEER_ROW_MASK = (1 << PEER_ROW_BITS) - 1;
+constexpr int PEER_MAX_RANKS = 128;
+
 __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 template <typename T>

@@ -28,12 +28,15 @@ int check_rows(const xma::RowsGemmArgs& g) {
 
 extern "C" {
 
-int xma_b200_grouped_gemm_rows(const void* a, int64_t a_row_stride, const void* w, int w_layout, void* out,
-                               int64_t out_row_stride, void* aux, int64_t aux_row_stride, const int32_t* row_map,
-                               const int32_t* tile_expert, const int32_t* tile_prefix, int num_experts,
-                               int64_t tile_cap, int64_t kd, int64_t n, int epilogue, int dtype, int impl,
-                               int* device_status, cudaStream_t stream) {
+int xma_b200_grouped_gemm_rows_peer(const void* a, int64_t a_row_stride, const void* w, int w_layout, void* out,
+                                    int64_t out_row_stride, void* aux, int64_t aux_row_stride,
+                                    const int32_t* row_map, void* const* out_peers, const int32_t* tile_expert,
+                                    const int32_t* tile_prefix, int num_experts, int64_t tile_cap, int64_t kd,
+                                    int64_t n, int epilogue, int dtype, int impl, int* device_status,
+                                    cudaStream_t stream) {
     xma::RowsGemmArgs g;
+    if (out_peers && (!row_map || epilogue != xma::EPI_PLAIN)) return XMA_ERR_BAD_SHAPE;
+    g.out_peers = out_peers;
     g.a = a;
     g.a_stride = a_row_stride;
     g.w = w;
@@ -64,6 +67,16 @@ int xma_b200_grouped_gemm_rows(const void* a, int64_t a_row_stride, const void* 
         return xma::rows_gemm_tc(g);
     }
     return xma::rows_gemm_simt(g);
+}
+
+int xma_b200_grouped_gemm_rows(const void* a, int64_t a_row_stride, const void* w, int w_layout, void* out,
+                               int64_t out_row_stride, void* aux, int64_t aux_row_stride, const int32_t* row_map,
+                               const int32_t* tile_expert, const int32_t* tile_prefix, int num_experts,
+                               int64_t tile_cap, int64_t kd, int64_t n, int epilogue, int dtype, int impl,
+                               int* device_status, cudaStream_t stream) {
+    return xma_b200_grouped_gemm_rows_peer(a, a_row_stride, w, w_layout, out, out_row_stride, aux, aux_row_stride,
+                                           row_map, nullptr, tile_expert, tile_prefix, num_experts, tile_cap, kd, n,
+                                           epilogue, dtype, impl, device_status, stream);
 }
 
 int xma_b200_grouped_gemm_dw(const void* x, int64_t x_row_stride, const void* y, int64_t y_row_stride,

@@ -32,6 +32,9 @@ struct RowsGemmArgs {
     void* aux;                 // gate|up buffer for the SwiGLU epilogues, else null
     int64_t aux_stride;
     const int* row_map;        // null: out row = grouped row; else out row = row_map[r], rows < 0 skipped
+    void* const* out_peers;    // null, or (plain epilogue with a row_map only) a device table of output
+                               // bases, one per rank: row_map[r] = (rank << 24) | row, and the row is
+                               // stored to out_peers[rank] instead of `out` (peer memory over NVLink)
     const int* tile_expert;    // [tile_cap]
     const int* tile_prefix;    // [E+1], tile_prefix[E] = tiles in use
     int num_experts;

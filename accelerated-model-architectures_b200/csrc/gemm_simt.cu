@@ -70,7 +70,7 @@ template <typename T>
 __global__ void __launch_bounds__(ST_THREADS)
 rows_gemm_simt_kernel(const T* __restrict__ a, int64_t a_stride, const T* __restrict__ w, int w_layout,
                       T* __restrict__ out, int64_t out_stride, const int* __restrict__ row_map,
-                      const int* __restrict__ tile_expert, const int* __restrict__ tile_prefix, int E, int64_t kd,
+                      void* const* __restrict__ out_peers, const int* __restrict__ tile_expert, const int* __restrict__ tile_prefix, int E, int64_t kd,
                       int64_t n) {
     const int tile = blockIdx.x >> 1;
     if (tile >= tile_prefix[E]) return;
@@ -91,10 +91,15 @@ rows_gemm_simt_kernel(const T* __restrict__ a, int64_t a_stride, const T* __rest
         int64_t dst = r;
         if (row_map) dst = row_map[r];
         if (dst < 0) continue;
+        T* base = out;
+        if (out_peers) {  // (rank << 24) | row of that rank's buffer
+            base = static_cast<T*>(out_peers[dst >> PEER_ROW_BITS]);
+            dst &= PEER_ROW_MASK;
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int64_t c = n0 + tx * 4 + j;
-            if (c < n) out[dst * out_stride + c] = from_f32<T>(acc[i][j]);
+            if (c < n) base[dst * out_stride + c] = from_f32<T>(acc[i][j]);
         }
     }
 }
@@ -134,11 +139,12 @@ static int rows_gemm_simt_t(const RowsGemmArgs& g) {
     T* raw = static_cast<T*>(g.epilogue == EPI_SWIGLU ? g.aux : g.out);
     const int64_t raw_stride = (g.epilogue == EPI_SWIGLU) ? g.aux_stride : g.out_stride;
     const int* row_map = (g.epilogue == EPI_PLAIN) ? g.row_map : nullptr;
+    void* const* out_peers = (g.epilogue == EPI_PLAIN) ? g.out_peers : nullptr;
     dim3 grid(static_cast<unsigned>(2 * g.tile_cap), static_cast<unsigned>(ceil_div(g.n, ST_BN)));
     if (grid.y > 65535) return XMA_ERR_TOO_LARGE;
     rows_gemm_simt_kernel<T><<<grid, ST_THREADS, 0, g.stream>>>(
         static_cast<const T*>(g.a), g.a_stride, static_cast<const T*>(g.w), g.w_layout, raw, raw_stride, row_map,
-        g.tile_expert, g.tile_prefix, g.num_experts, g.kd, g.n);
+        out_peers, g.tile_expert, g.tile_prefix, g.num_experts, g.kd, g.n);
     XMA_CUDA_TRY(cudaGetLastError());
     const int64_t rows = g.tile_cap * XMA_ROW_PAD;
     if (g.epilogue == EPI_SWIGLU) {

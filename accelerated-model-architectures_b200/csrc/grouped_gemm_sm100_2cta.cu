@@ -213,8 +213,9 @@ template <typename T, int WL, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                      T* __restrict__ out, int64_t out_stride, T* __restrict__ aux, int64_t aux_stride,
-                     const int* __restrict__ row_map, const int* __restrict__ g_tile_prefix, int E, int kd, int n,
-                     uint32_t idesc, int* __restrict__ status) {
+                     const int* __restrict__ row_map, void* const* __restrict__ out_peers,
+                     const int* __restrict__ g_tile_prefix, int E, int kd, int n, uint32_t idesc,
+                     int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const Shared2 s = carve_smem2(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -306,8 +307,8 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
             if (!rows_epilogue_tile<T, EPI>(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag, taddr, r, wk.active,
-                                            wk.n_tile, n, half_n, out, out_stride, aux, aux_stride, row_map, part,
-                                            chunks))
+                                            wk.n_tile, n, half_n, out, out_stride, aux, aux_stride, row_map, out_peers,
+                                            part, chunks))
                 break;
             tc_fence_before();
             __syncwarp();
@@ -458,7 +459,7 @@ static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUte
     const uint32_t idesc = make_idesc_mn(g.dtype, false, WL == W_KN, 2 * BM, BN);
     kernel<<<pair_grid(), block_threads((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) ? 8 : 4), SMEM2_BYTES, g.stream>>>(
         ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
-        g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
+        g.out_peers, g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
     return static_cast<int>(cudaGetLastError());
 }
 

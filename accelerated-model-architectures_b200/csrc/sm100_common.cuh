@@ -262,11 +262,16 @@ __device__ __forceinline__ bool rows_epilogue_tile(uint64_t* acc_full_bar, uint3
                                                    uint32_t taddr, int64_t r, bool active, int n_tile, int n,
                                                    int half_n, T* __restrict__ out, int64_t out_stride,
                                                    T* __restrict__ aux, int64_t aux_stride,
-                                                   const int* __restrict__ row_map, int part, int chunks) {
+                                                   const int* __restrict__ row_map,
+                                                   void* const* __restrict__ out_peers, int part, int chunks) {
     if (!active) return mbar_wait_epilogue(acc_full_bar, parity, abort_flag);
     if (EPI == EPI_PLAIN) {
         int64_t dst = r;
         if (row_map) dst = row_map[r];
+        if (out_peers && dst >= 0) {  // the row belongs to another rank's buffer: (rank << 24) | row
+            out = static_cast<T*>(out_peers[dst >> PEER_ROW_BITS]);
+            dst &= PEER_ROW_MASK;
+        }
         const int n0 = n_tile * BN;
         if (!mbar_wait_epilogue(acc_full_bar, parity, abort_flag)) return false;
         tc_fence_after();

@@ -55,6 +55,9 @@ _SIGNATURES = {
     "xma_b200_grouped_gemm_rows": [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int,
                                    c_int, c_void_p, c_void_p],
+    "xma_b200_grouped_gemm_rows_peer": [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
+                                        c_int, c_int, c_int, c_void_p, c_void_p],
     "xma_b200_grouped_gemm_dw": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int64,
                                  c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "xma_b200_grouped_gemm_uses_tensor_cores": [c_int, c_int64, c_int64],
@@ -65,6 +68,17 @@ _SIGNATURES = {
     "xma_b200_swiglu_packed_fwd": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p],
     "xma_b200_swiglu_packed_bwd": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64,
                                    c_int64, c_void_p],
+    "xma_b200_ep_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                         c_void_p, c_int64, c_void_p, c_void_p],
+    "xma_b200_ep_dispatch": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                             c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
+    "xma_b200_ep_copy_rows": [c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p, c_void_p],
+    "xma_b200_exchange_alloc": [c_int64, c_void_p],
+    "xma_b200_exchange_free": [c_void_p],
+    "xma_b200_exchange_handle_bytes": [],
+    "xma_b200_exchange_export": [c_void_p, c_void_p],
+    "xma_b200_exchange_open": [c_void_p, c_void_p],
+    "xma_b200_exchange_close": [c_void_p],
 }
 _RESTYPES = {
     "xma_b200_error_string": c_char_p,

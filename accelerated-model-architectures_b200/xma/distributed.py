@@ -19,15 +19,34 @@ Overlap: with `overlap_chunks = C > 1` the rank's tokens are cut into C micro-ba
 whole path on alternating CUDA streams, so the all-to-alls of one micro-batch (NCCL's own stream)
 run under the grouped GEMMs of the other; autograd replays the backward on the same streams, which
 overlaps it the same way.
+
+`transport="peer"` replaces the two row all-to-alls by stores into the other ranks' memory (the
+ranks of one node map each other's exchange buffers once, CUDA IPC over NVLink):
+
+    all_gather of the per-expert counts [W, E]  (tiny; one device->host read sizes the buffers)
+    -> DISPATCH kernel: every routed token row is gathered and stored straight into its slot of the
+       owner's padded, expert-major buffer, with a word naming its origin (home rank, token slot)
+    -> barrier -> up projection + SwiGLU -> down projection whose epilogue stores every output row
+       into the home rank's [T*K, H] buffer (GEMM and combine exchange are one kernel)
+    -> barrier -> weighted sum over the k slots on the home rank.
+
+Backward mirrors it (dY rows dispatched with the routing weight applied, dX rows returned by the
+dX GEMM's epilogue). No kernel waits on another GPU: the phases are separated by a stream-ordered
+barrier (a one-element NCCL all-reduce), so a rank that stops costs a collective timeout, never a
+spinning kernel. Tensors kept for backward are private copies; the exchange buffers are reused by
+every call.
 """
 
 from __future__ import annotations
+
+import ctypes
 
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 
 from . import ops
+from ._lib import EPI_DSWIGLU, EPI_PLAIN, EPI_SWIGLU, ROW_PAD, W_KN, W_NK, check, lib
 from .layers.moe import MoE, _FusedSwiGLUExperts, _plan_tensors, _TopKSoftmax, build_route_plan, SwiGLU
 
 
@@ -109,19 +128,258 @@ class _CombineRows(torch.autograd.Function):
         return d_rows, d_rw, None, None
 
 
+# ---- peer-memory transport ---------------------------------------------------------------------------
+class _DeviceBlock:
+    """`cudaMalloc` memory of the current device, outside torch's caching allocator so that it can be
+    exported to the other processes of the node; `tensor` is a uint8 view of it."""
+
+    def __init__(self, nbytes: int, device: torch.device) -> None:
+        out = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            check(lib.xma_b200_exchange_alloc(nbytes, ctypes.byref(out)), "xma_b200_exchange_alloc")
+        self.ptr, self.nbytes = int(out.value), int(nbytes)
+        self.__cuda_array_interface__ = {
+            "shape": (self.nbytes,), "typestr": "|u1", "data": (self.ptr, False), "version": 3, "strides": None,
+        }
+        self.tensor = torch.as_tensor(self, device=device)
+
+    def export(self) -> bytes:
+        handle = ctypes.create_string_buffer(lib.xma_b200_exchange_handle_bytes())
+        check(lib.xma_b200_exchange_export(self.ptr, handle), "xma_b200_exchange_export")
+        return handle.raw
+
+    def free(self) -> None:
+        if self.ptr:
+            self.tensor = None
+            check(lib.xma_b200_exchange_free(self.ptr), "xma_b200_exchange_free")
+            self.ptr = 0
+
+
+class PeerLink:
+    """What the peer transport needs from the fabric, for the ranks of one node (one process per GPU):
+    the count exchange, a barrier that orders the current stream after every rank's earlier work, and
+    memory that every rank can store into."""
+
+    def __init__(self, group) -> None:
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._token: torch.Tensor | None = None
+
+    def all_gather_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(self.world * counts.numel(), dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(out, counts.contiguous(), group=self.group)
+        return out.view(self.world, -1)
+
+    def barrier(self) -> None:
+        if self._token is None:
+            self._token = torch.zeros(1, dtype=torch.int32, device=torch.cuda.current_device())
+        dist.all_reduce(self._token, group=self.group)
+
+    def share(self, nbytes: int, device: torch.device):
+        """Collective. -> (block of this rank, [address of every rank's block in this process], mapped addresses)."""
+        block = _DeviceBlock(nbytes, device)
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, block.export(), group=self.group)
+        addresses, mapped = [], []
+        with torch.cuda.device(device):
+            for r, handle in enumerate(handles):
+                if r == self.rank:
+                    addresses.append(block.ptr)
+                    continue
+                out = ctypes.c_void_p()
+                check(lib.xma_b200_exchange_open(handle, ctypes.byref(out)), "xma_b200_exchange_open")
+                addresses.append(int(out.value))
+                mapped.append(int(out.value))
+        dist.barrier(group=self.group)
+        return block, addresses, mapped
+
+    def release(self, block, mapped: list[int]) -> None:
+        """Collective: nobody may still be storing into a block when its owner frees it."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for address in mapped:
+            check(lib.xma_b200_exchange_close(address), "xma_b200_exchange_close")
+        dist.barrier(group=self.group)
+        block.free()
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return (value + multiple - 1) // multiple * multiple
+
+
+class _Exchange:
+    """Exchange buffers of one micro-batch slot, shared by every call of the layer:
+    `recv_rows` [recv_cap, H] + `recv_meta` [recv_cap]: rows this rank's experts receive and where each
+    came from; `home_rows` [home_cap, H]: expert outputs returned to this rank, one row per token slot.
+    `*_table`: int64 [W] device tensors with every rank's address of the same buffer."""
+
+    def __init__(self, link, device: torch.device, dtype: torch.dtype, hidden: int) -> None:
+        self.link, self.device, self.dtype, self.hidden = link, device, dtype, hidden
+        self.recv_cap = self.home_cap = 0
+        self._held: list = []
+        self.recv_rows = self.recv_meta = self.home_rows = None
+        self.recv_table = self.meta_table = self.home_table = None
+
+    def _shared(self, nbytes: int):
+        block, addresses, mapped = self.link.share(nbytes, self.device)
+        self._held.append((block, mapped))
+        return block.tensor, torch.tensor(addresses, dtype=torch.int64, device=self.device)
+
+    def ensure(self, need_recv: int, need_home: int) -> None:
+        """Collective whenever it reallocates; every rank calls it with the same arguments."""
+        if need_recv <= self.recv_cap and need_home <= self.home_cap:
+            return
+        if max(need_recv, need_home) > (1 << 24):
+            raise ValueError("the peer transport addresses at most 2^24 rows per rank")
+        self.close()
+        item = torch.empty((), dtype=self.dtype).element_size()
+        self.recv_cap = max(self.recv_cap, _round_up(need_recv + need_recv // 4, ROW_PAD), ROW_PAD)
+        self.home_cap = max(self.home_cap, _round_up(need_home + need_home // 4, ROW_PAD), ROW_PAD)
+        raw, self.recv_table = self._shared(self.recv_cap * self.hidden * item)
+        self.recv_rows = raw.view(self.dtype).view(self.recv_cap, self.hidden)
+        raw, self.meta_table = self._shared(self.recv_cap * 4)
+        self.recv_meta = raw.view(torch.int32)
+        raw, self.home_table = self._shared(self.home_cap * self.hidden * item)
+        self.home_rows = raw.view(self.dtype).view(self.home_cap, self.hidden)
+
+    def close(self) -> None:
+        """Collective."""
+        self.recv_rows = self.recv_meta = self.home_rows = None
+        for block, mapped in self._held:
+            self.link.release(block, mapped)
+        self._held = []
+
+
+class _PeerRoute:
+    """Device tables of one routing decision under the peer transport (all from `ep_plan`)."""
+
+    def __init__(self, count_matrix: torch.Tensor, rank: int, rows: int, exchange: _Exchange) -> None:
+        world, num_experts = count_matrix.shape
+        e_local = num_experts // world
+        dev = count_matrix.device
+        self.world, self.rank, self.rows, self.e_local = world, rank, rows, e_local
+        self.send_delta = torch.empty(num_experts, dtype=torch.int32, device=dev)
+        self.counts = torch.empty(e_local, dtype=torch.int32, device=dev)
+        self.pad_offsets = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+        self.tile_prefix = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+        self.tile_expert = torch.empty(rows // ROW_PAD + e_local, dtype=torch.int32, device=dev)
+        ops.ep_plan_(count_matrix, rank, self.send_delta, self.counts, self.pad_offsets, self.tile_prefix,
+                     self.tile_expert, exchange.recv_meta)
+
+
+class _PeerSwiGLUExperts(torch.autograd.Function):
+    """The fused SwiGLU expert block with the experts sharded over the ranks: dispatch and combine are
+    stores into the other ranks' exchange buffers (see the module docstring)."""
+
+    @staticmethod
+    def forward(ctx, x, router_weights, w1, w2, sorted_expert_idxs, sorted_scattered_idxs, route, exchange):
+        T, K = router_weights.shape
+        e_local, two_i, H = w1.shape
+        I = two_i // 2
+        R = T * K
+        link = exchange.link
+        opts = dict(dtype=x.dtype, device=x.device)
+        impl = ops.GEMM_IMPL
+        rows = route.rows                              # padded rows of this rank's experts in use
+        alloc = route.tile_expert.numel() * ROW_PAD    # grouped buffers span the whole tile table
+
+        ops.ep_dispatch_(x, sorted_expert_idxs, sorted_scattered_idxs, None, K, route.send_delta, route.world,
+                         route.rank, exchange.recv_table, exchange.meta_table, exchange.recv_cap)
+        link.barrier()
+
+        xs = torch.empty(alloc, H, **opts)
+        meta = exchange.recv_meta[:alloc].clone()
+        ops.ep_copy_rows_(exchange.recv_rows, meta, xs[:rows])
+        gu = torch.empty(alloc, two_i, **opts)
+        act = torch.empty(alloc, I, **opts)
+        ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, route.tile_expert, route.tile_prefix, H, two_i,
+                               EPI_SWIGLU, impl, tag="gemm_up_swiglu")
+        ops.grouped_gemm_rows_(act, w2, W_NK, exchange.home_rows, None, meta, route.tile_expert, route.tile_prefix,
+                               I, H, EPI_PLAIN, impl, exchange.home_table, tag="gemm_down")
+        link.barrier()
+
+        ys = exchange.home_rows[:R].clone()
+        y = torch.empty(T, H, **opts)
+        router_weights = router_weights.contiguous()
+        if T > 0:
+            ops.combine_rows_(ys, router_weights, K, y)
+        ctx.save_for_backward(xs, gu, act, ys, meta, w1, w2, router_weights, sorted_expert_idxs,
+                              sorted_scattered_idxs)
+        ctx.route, ctx.exchange = route, exchange
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        xs, gu, act, ys, meta, w1, w2, router_weights, sorted_expert_idxs, sorted_scattered_idxs = ctx.saved_tensors
+        route, exchange = ctx.route, ctx.exchange
+        link = exchange.link
+        T, K = router_weights.shape
+        e_local, two_i, H = w1.shape
+        I = two_i // 2
+        R = T * K
+        rows = route.rows
+        alloc = xs.size(0)
+        opts = dict(dtype=xs.dtype, device=xs.device)
+        impl = ops.GEMM_IMPL
+        grad_out = grad_out.contiguous()
+
+        d_rw = None
+        if ctx.needs_input_grad[1]:
+            d_rw = torch.empty_like(router_weights)
+            if T > 0:
+                ops.combine_bwd_(ys, grad_out, K, d_rw)
+
+        # dY rows, scaled by their routing weight, to the owners (same slots as the forward rows)
+        ops.ep_dispatch_(grad_out, sorted_expert_idxs, sorted_scattered_idxs, router_weights.view(-1), K,
+                         route.send_delta, route.world, route.rank, exchange.recv_table, None, exchange.recv_cap)
+        dys = exchange.recv_rows[:alloc]
+        ops.ep_copy_rows_(dys, meta, dys[:rows])  # in place: zero the pad rows (nobody else writes them)
+        link.barrier()
+
+        d_w2 = torch.empty_like(w2)
+        ops.grouped_gemm_dw_(dys, act, route.counts, route.pad_offsets, d_w2, impl, tag="gemm_dw2")
+        dgu = torch.empty(alloc, two_i, **opts)
+        ops.grouped_gemm_rows_(dys, w2, W_KN, dgu, gu, None, route.tile_expert, route.tile_prefix, H, I,
+                               EPI_DSWIGLU, impl, tag="gemm_dact_dswiglu")
+        d_w1 = torch.empty_like(w1)
+        ops.grouped_gemm_dw_(dgu, xs, route.counts, route.pad_offsets, d_w1, impl, tag="gemm_dw1")
+        # dX rows straight back to the token's home rank
+        ops.grouped_gemm_rows_(dgu, w1, W_KN, exchange.home_rows, None, meta, route.tile_expert, route.tile_prefix,
+                               two_i, H, EPI_PLAIN, impl, exchange.home_table, tag="gemm_dx")
+        link.barrier()
+
+        d_x = torch.empty(T, H, **opts)
+        if T > 0:
+            ops.combine_rows_(exchange.home_rows[:R], None, K, d_x)
+        return d_x, d_rw, d_w1, d_w2, None, None, None, None
+
+
 class ExpertParallelMoE(nn.Module):
     """Wraps a `MoE` that holds this rank's E/W experts (`c_fc`, `c_proj`) and a replicated router
     weight `[E, H]`. forward(x [.., H]) -> (y, router_logits [T, E]) for this rank's tokens."""
 
     def __init__(self, local_moe: MoE, gate_weight: torch.Tensor, world_group=None,
-                 overlap_chunks: int | None = None) -> None:
+                 overlap_chunks: int | None = None, transport: str = "nccl", link=None) -> None:
+        """`transport`: "nccl" (all-to-all collectives; any process group) or "peer" (stores into the
+        other ranks' memory; the ranks must be GPUs of one node with peer access). `link` replaces the
+        `PeerLink` built from the process group (tests drive several ranks of one process with it)."""
         super().__init__()
         if not (isinstance(local_moe.act, SwiGLU) and local_moe.is_glu):
             raise ValueError("ExpertParallelMoE runs the fused SwiGLU expert block")
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport must be 'nccl' or 'peer'")
         self.local = local_moe
-        self.group = world_group if world_group is not None else dist.group.WORLD
-        self.world = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
+        self.transport = transport
+        if link is not None:
+            self.link, self.group = link, None
+            self.world, self.rank = link.world, link.rank
+        else:
+            self.group = world_group if world_group is not None else dist.group.WORLD
+            self.world = dist.get_world_size(self.group)
+            self.rank = dist.get_rank(self.group)
+            self.link = PeerLink(self.group) if transport == "peer" else None
+        self._exchanges: dict = {}
         self.num_experts = local_moe.num_experts * self.world
         self.top_k = local_moe.top_k
         self.hidden_size = local_moe.hidden_size
@@ -130,7 +388,10 @@ class ExpertParallelMoE(nn.Module):
         self.gate_weight = nn.Parameter(gate_weight.detach().clone())
         # exchange volume grows with (W-1)/W while the per-rank weight gradients (which every extra
         # micro-batch accumulates once more) shrink with 1/W: micro-batching pays from 4 ranks on
-        self.overlap_chunks = overlap_chunks if overlap_chunks is not None else (2 if self.world >= 4 else 1)
+        # (the peer transport hides the way back inside the GEMMs, so it starts from one micro-batch)
+        if overlap_chunks is None:
+            overlap_chunks = 2 if (self.world >= 4 and transport == "nccl") else 1
+        self.overlap_chunks = overlap_chunks
         self._streams: list[torch.cuda.Stream] = []
 
     def forward(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -138,7 +399,7 @@ class ExpertParallelMoE(nn.Module):
         x = x.reshape(-1, self.hidden_size).contiguous()
         chunks = min(self.overlap_chunks, max(1, x.size(0)))
         if chunks <= 1:
-            y, logits = self._forward_rows(x)
+            y, logits = self._forward_rows(x, 0)
             return y.view(original_shape), logits
         if not self._streams:
             self._streams = [torch.cuda.Stream(device=x.device) for _ in range(2)]
@@ -148,7 +409,7 @@ class ExpertParallelMoE(nn.Module):
             st = self._streams[i % 2]
             st.wait_stream(main)
             with torch.cuda.stream(st):
-                y_i, l_i = self._forward_rows(xc)
+                y_i, l_i = self._forward_rows(xc, i % 2)
             ys.append(y_i)
             logits.append(l_i)
         for st in self._streams:
@@ -157,7 +418,41 @@ class ExpertParallelMoE(nn.Module):
             t.record_stream(main)
         return torch.cat(ys, dim=0).view(original_shape), torch.cat(logits, dim=0)
 
-    def _forward_rows(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    def _exchange(self, slot: int, x: torch.Tensor) -> _Exchange:
+        key = (slot, x.device, x.dtype)
+        if key not in self._exchanges:
+            self._exchanges[key] = _Exchange(self.link, x.device, x.dtype, self.hidden_size)
+        return self._exchanges[key]
+
+    def close(self) -> None:
+        """Collective: unmaps and frees the exchange buffers of the peer transport."""
+        for exchange in self._exchanges.values():
+            exchange.close()
+        self._exchanges = {}
+
+    def _forward_rows_peer(self, x: torch.Tensor, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
+        E, K, W = self.num_experts, self.top_k, self.world
+        e_local = E // W
+        router_logits = torch.nn.functional.linear(x, self.gate_weight)
+        router_weights, selected = _TopKSoftmax.apply(router_logits, K)
+        with torch.no_grad():
+            plan = build_route_plan(selected, E)
+            count_matrix = self.link.all_gather_counts(plan.counts)  # [W, E] int32
+            # one small device->host read per step: every rank sizes every rank's buffers from it,
+            # so all of them take the same (collective) decision to grow the exchange buffers
+            host = count_matrix.cpu().to(torch.int64)
+            padded = ((host.sum(0) + ROW_PAD - 1) // ROW_PAD * ROW_PAD).view(W, e_local).sum(1)
+            exchange = self._exchange(slot, x)
+            # (grouped buffers are allocated for rows // 128 + e_local tiles, the received rows included)
+            exchange.ensure(int(padded.max()) + e_local * ROW_PAD, int(host.sum(1).max()))
+            route = _PeerRoute(count_matrix, self.rank, int(padded[self.rank]), exchange)
+        y = _PeerSwiGLUExperts.apply(x, router_weights, self.local.c_fc.weight, self.local.c_proj.weight,
+                                     plan.sorted_expert_idxs, plan.sorted_scattered_idxs, route, exchange)
+        return y, router_logits
+
+    def _forward_rows(self, x: torch.Tensor, slot: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+        if self.transport == "peer":
+            return self._forward_rows_peer(x, slot)
         E, K, W = self.num_experts, self.top_k, self.world
         e_local = E // W
 

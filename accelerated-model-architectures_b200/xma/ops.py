@@ -153,15 +153,18 @@ def _grouped_gemm_rows_op(
     n: int,
     epilogue: int,
     impl: int,
+    out_peers: Optional[Tensor] = None,
 ) -> None:
+    """`out_peers` (int64 [world], device): base address of every rank's output buffer; rows then go
+    to the rank named by `row_map` (expert parallelism) and `out` is this rank's own buffer."""
     require_cuda(a, w, out)
     if not w.is_contiguous():
         raise ValueError("expert weights must be contiguous [E, out_features, in_features]")
     check(
-        lib.xma_b200_grouped_gemm_rows(
+        lib.xma_b200_grouped_gemm_rows_peer(
             ptr(a), _row_stride(a), ptr(w), w_layout, ptr(out), _row_stride(out), ptr(aux),
-            0 if aux is None else _row_stride(aux), ptr(row_map), ptr(tile_expert), ptr(tile_prefix), w.size(0),
-            tile_expert.numel(), kd, n, epilogue, dtype_code(a.dtype), impl, ptr(status_word(a.device)),
+            0 if aux is None else _row_stride(aux), ptr(row_map), ptr(out_peers), ptr(tile_expert), ptr(tile_prefix),
+            w.size(0), tile_expert.numel(), kd, n, epilogue, dtype_code(a.dtype), impl, ptr(status_word(a.device)),
             current_stream(a.device)
         ),
         "xma_b200_grouped_gemm_rows",
@@ -178,6 +181,57 @@ def _grouped_gemm_dw_op(x: Tensor, y: Tensor, counts: Tensor, pad_offsets: Tenso
             current_stream(x.device)
         ),
         "xma_b200_grouped_gemm_dw",
+    )
+
+
+@torch.library.custom_op(
+    f"{_NS}::ep_plan",
+    mutates_args={"send_delta", "counts", "pad_offsets", "tile_prefix", "tile_expert", "meta"},
+    device_types="cuda",
+)
+def _ep_plan_op(count_matrix: Tensor, rank: int, send_delta: Tensor, counts: Tensor, pad_offsets: Tensor,
+                tile_prefix: Tensor, tile_expert: Tensor, meta: Tensor) -> None:
+    require_cuda(count_matrix, send_delta, meta)
+    if count_matrix.dtype != torch.int32 or not count_matrix.is_contiguous():
+        raise ValueError("count_matrix must be a contiguous int32 [world, num_experts] tensor")
+    check(
+        lib.xma_b200_ep_plan(
+            ptr(count_matrix), count_matrix.size(0), count_matrix.size(1), rank, ptr(send_delta), ptr(counts),
+            ptr(pad_offsets), ptr(tile_prefix), ptr(tile_expert), tile_expert.numel(), ptr(meta), meta.numel(),
+            ptr(status_word(meta.device)), current_stream(meta.device)
+        ),
+        "xma_b200_ep_plan",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::ep_dispatch", mutates_args=(), device_types="cuda")
+def _ep_dispatch_op(src: Tensor, sorted_expert_idxs: Tensor, sorted_scattered_idxs: Tensor, coeff: Optional[Tensor],
+                    fan_out: int, send_delta: Tensor, world: int, rank: int, peer_rows: Tensor,
+                    peer_meta: Optional[Tensor], peer_rows_cap: int) -> None:
+    """Writes into the exchange buffers whose addresses `peer_rows` / `peer_meta` (int64 [world]) hold."""
+    require_cuda(src, sorted_expert_idxs, sorted_scattered_idxs, send_delta, peer_rows)
+    check(
+        lib.xma_b200_ep_dispatch(
+            ptr(src), dtype_code(src.dtype), _row_stride(src), ptr(sorted_expert_idxs), ptr(sorted_scattered_idxs),
+            ptr(coeff), fan_out, ptr(send_delta), send_delta.numel(), world, rank, sorted_expert_idxs.numel(),
+            src.size(1), ptr(peer_rows), ptr(peer_meta), peer_rows_cap, ptr(status_word(src.device)),
+            current_stream(src.device)
+        ),
+        "xma_b200_ep_dispatch",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::ep_copy_rows", mutates_args={"out"}, device_types="cuda")
+def _ep_copy_rows_op(rows: Tensor, meta: Tensor, out: Tensor) -> None:
+    """out[r] = rows[r] where meta[r] >= 0, zeros elsewhere, for the out.size(0) first rows
+    (`out` may be `rows` itself: only the pad rows are then written)."""
+    require_cuda(rows, meta, out)
+    if not (rows.is_contiguous() and out.is_contiguous()):
+        raise ValueError("exchange rows must be dense")
+    check(
+        lib.xma_b200_ep_copy_rows(ptr(rows), dtype_code(rows.dtype), ptr(meta), out.size(0), out.size(1), ptr(out),
+                                  current_stream(rows.device)),
+        "xma_b200_ep_copy_rows",
     )
 
 
@@ -278,6 +332,9 @@ combine_rows_ = _wrap(_combine_rows_op, "combine_rows", 1)
 combine_bwd_ = _wrap(_combine_bwd_op, "combine_bwd", 1)
 grouped_gemm_rows_ = _wrap(_grouped_gemm_rows_op, "grouped_gemm_rows", 1)
 grouped_gemm_dw_ = _wrap(_grouped_gemm_dw_op, "grouped_gemm_dw", 1)
+ep_plan_ = _wrap(_ep_plan_op, "ep_plan", 1)
+ep_dispatch_ = _wrap(_ep_dispatch_op, "ep_dispatch", 1)
+ep_copy_rows_ = _wrap(_ep_copy_rows_op, "ep_copy_rows", 1)
 swiglu_fwd_ = _wrap(_swiglu_fwd_op, "swiglu_fwd", 1)
 swiglu_bwd_ = _wrap(_swiglu_bwd_op, "swiglu_bwd", 1)
 swiglu_packed_fwd_ = _wrap(_swiglu_packed_fwd_op, "swiglu_packed_fwd", 1)

@@ -325,6 +325,8 @@ def main() -> None:
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--transport", choices=["peer", "nccl"], default="peer",
+                    help="row exchange of the expert-parallel layer: stores into peer memory, or NCCL all-to-all")
     ap.add_argument("--ep-chunks", type=int, default=None,
                     help="micro-batches per step in the expert-parallel layer (overlap of all-to-all and GEMM)")
     args = ap.parse_args()
@@ -364,7 +366,8 @@ def main() -> None:
     if world > 1:
         from xma.distributed import ExpertParallelMoE
 
-        layer = ExpertParallelMoE(moe, gate, world_group=dist.group.WORLD, overlap_chunks=args.ep_chunks)
+        layer = ExpertParallelMoE(moe, gate, world_group=dist.group.WORLD, overlap_chunks=args.ep_chunks,
+                                  transport=args.transport)
     else:
         with torch.no_grad():
             moe.gate.weight.copy_(gate)
@@ -566,7 +569,10 @@ def main() -> None:
             "config": {"workload": f"{args.workload}: {w['desc']}", "tokens_per_gpu": w["tokens"],
                        "hidden": H, "intermediate": I, "experts": E, "top_k": w["top_k"],
                        "parallelism": "single GPU" if world == 1 else
-                       f"expert-parallel ep{world}, NCCL all-to-all, {layer.overlap_chunks} micro-batch(es) per step",
+                       f"expert-parallel ep{world}, "
+                       + ("dispatch kernel + GEMM epilogues storing into peer memory over NVLink"
+                          if args.transport == "peer" else "NCCL all-to-all")
+                       + f", {layer.overlap_chunks} micro-batch(es) per step",
                        "l2_policy": "inputs_exceed_l2 (weights + activations >> 126 MB)"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms,

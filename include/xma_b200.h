@@ -149,6 +149,19 @@ int xma_b200_grouped_gemm_rows(const void* a, int64_t a_row_stride, const void* 
                                int64_t tile_cap, int64_t kd, int64_t n, int epilogue, int dtype, int impl,
                                int* device_status, cudaStream_t stream);
 
+/* The same GEMM with its output rows stored into other ranks' memory (expert parallelism): plain
+ * epilogue and row_map required; row_map[r] = (rank << 24) | row (negative: skipped) and the row is
+ * stored to out_peers[rank] + row * out_row_stride, where out_peers is a device table of one base
+ * address per rank (this rank's own buffer included; the others mapped with xma_b200_exchange_open).
+ * out_peers NULL: identical to xma_b200_grouped_gemm_rows. No counterpart in the reference, whose MoE
+ * keeps all experts on one device (xma/layers/moe/__init__.py:144-160). */
+int xma_b200_grouped_gemm_rows_peer(const void* a, int64_t a_row_stride, const void* w, int w_layout, void* out,
+                                    int64_t out_row_stride, void* aux, int64_t aux_row_stride,
+                                    const int32_t* row_map, void* const* out_peers, const int32_t* tile_expert,
+                                    const int32_t* tile_prefix, int num_experts, int64_t tile_cap, int64_t kd,
+                                    int64_t n, int epilogue, int dtype, int impl, int* device_status,
+                                    cudaStream_t stream);
+
 /* dw[e, m, n] = sum over the rows r of expert e of x[r, m] * y[r, n]; x, y grouped (rows_cap rows
  * allocated); experts without rows get zeros, so dw needs no pre-zeroing.
  * Replaces group_bwd_W: xma/layers/moe/triton_implementation/group_backward_kernel.py:102-128. */
@@ -176,6 +189,47 @@ int xma_b200_swiglu_packed_fwd(const void* x, int64_t x_row_stride, void* y, int
 int xma_b200_swiglu_packed_bwd(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
                                void* dx, int64_t dx_row_stride, int dtype, int64_t rows, int64_t out_cols,
                                cudaStream_t stream);
+
+/* ---- expert parallelism over peer memory ------------------------------------------------------ */
+/* None of these has a counterpart in the reference (single-device MoE, xma/layers/moe/__init__.py:144-160).
+ * Rank r of `world` owns experts [r * E / world, (r + 1) * E / world). An owner keeps the rows it receives
+ * expert-major, inside an expert ordered by source rank, every expert padded to 128 rows. No kernel waits
+ * on another GPU: the caller separates the phases with a stream-ordered barrier over all ranks. */
+
+/* count_matrix [world, E] (int32, device): rows rank s routes to global expert e. Writes, for this rank:
+ * send_delta [E] (sorted row p of expert e lands in row p + send_delta[e] of the owner's buffer), and the
+ * grouped layout of its own E / world experts (counts, pad_offsets [E/world + 1], tile_prefix [E/world + 1],
+ * tile_expert [tile_cap]); resets the pad slots of `meta` (this rank's origin words, meta_cap entries) to -1.
+ * Sets device status bit 4 and an empty layout if tile_cap or meta_cap is too small. */
+int xma_b200_ep_plan(const int32_t* count_matrix, int world, int num_experts, int rank, int32_t* send_delta,
+                     uint32_t* counts, int32_t* pad_offsets, int32_t* tile_prefix, int32_t* tile_expert,
+                     int64_t tile_cap, int32_t* meta, int64_t meta_cap, int* device_status, cudaStream_t stream);
+
+/* Dispatch: for every sorted row p (q = sorted_scattered_idxs[p], e = sorted_expert_idxs[p], owner = e / (E/world))
+ *   peer_rows[owner][p + send_delta[e], :] = src[q / fan_out, :] * coeff[q]   (coeff NULL: 1)
+ *   peer_meta[owner][p + send_delta[e]]    = (rank << 24) | q                 (peer_meta NULL: not written)
+ * peer_rows / peer_meta: device tables of one base address per rank; rows of `width` elements, dense.
+ * Rows that would fall outside [0, peer_rows_cap) are not stored and set device status bit 1. */
+int xma_b200_ep_dispatch(const void* src, int dtype, int64_t src_row_stride, const int32_t* sorted_expert_idxs,
+                         const int32_t* sorted_scattered_idxs, const void* coeff, int fan_out,
+                         const int32_t* send_delta, int num_experts, int world, int rank, int64_t rows, int64_t width,
+                         void* const* peer_rows, int32_t* const* peer_meta, int64_t peer_rows_cap,
+                         int* device_status, cudaStream_t stream);
+
+/* out[r, :] = meta[r] >= 0 ? rows[r, :] : 0 for r < n_rows (dense rows of `width` elements);
+ * out == rows zero-fills the pad rows in place. */
+int xma_b200_ep_copy_rows(const void* rows, int dtype, const int32_t* meta, int64_t n_rows, int64_t width, void* out,
+                          cudaStream_t stream);
+
+/* Exchange buffers: zero-filled device memory of the current device that the other processes of the node map
+ * into their address space (CUDA IPC; the devices must be peers). _export writes
+ * xma_b200_exchange_handle_bytes() bytes that another process hands to _open; _close unmaps, _free releases. */
+int xma_b200_exchange_alloc(int64_t bytes, void** out_ptr);
+int xma_b200_exchange_free(void* ptr);
+int xma_b200_exchange_handle_bytes(void);
+int xma_b200_exchange_export(void* ptr, void* handle_out);
+int xma_b200_exchange_open(const void* handle, void** out_ptr);
+int xma_b200_exchange_close(void* ptr);
 
 #ifdef __cplusplus
 }
