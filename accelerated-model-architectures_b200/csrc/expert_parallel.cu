@@ -12,9 +12,14 @@
 //                          origin (home rank << 24 | token slot).
 //   * ep_copy_rows_kernel: owner side, received rows -> private padded buffer (pad rows zero),
 //                          or zero-fill of the pad rows in place.
-// The way back is fused into the grouped GEMM: its plain epilogue stores each output row to the
-// home rank named by that word (`out_peers` of the rows GEMM). No kernel here waits on another
-// GPU; ranks are ordered by the caller's stream-ordered barrier between the phases.
+//   * ep_return_kernel   : owner side, expert output rows -> the home rank named by their origin
+//                          word, whole rows at a time (512 contiguous bytes per warp store).
+// The way back can also be fused into the grouped GEMM (`out_peers` of the rows GEMM: the plain
+// epilogue stores each output row to its home rank), but an epilogue thread owns one row, so a warp
+// store is 32 pieces of 16 bytes in 32 rows; over NVLink those reached about 125 GB/s against about
+// 560 GB/s for the row-contiguous stores of ep_return_kernel, so the separate kernel is the default.
+// No kernel here waits on another GPU; ranks are ordered by the caller's stream-ordered barrier
+// between the phases.
 #include "common.cuh"
 
 #include <cstring>
@@ -183,6 +188,50 @@ ep_copy_rows_kernel(const T* __restrict__ rows, const int* __restrict__ meta, in
     }
 }
 
+// peer_rows[meta[r] >> 24][meta[r] & mask, :] = rows[r, :] for every r < n_rows with meta[r] >= 0.
+template <typename T>
+__global__ void __launch_bounds__(EP_ROW_THREADS)
+ep_return_kernel(const T* __restrict__ rows, int64_t row_stride, const int* __restrict__ meta, int64_t n_rows,
+                 int64_t width, int world, void* const* __restrict__ peer_rows, int64_t peer_rows_cap,
+                 int* __restrict__ status) {
+    constexpr int V = Vec16<T>::N;
+    const int64_t nvec = width / V;
+    for (int64_t p0 = static_cast<int64_t>(blockIdx.x) * EP_ROWS; p0 < n_rows;
+         p0 += static_cast<int64_t>(gridDim.x) * EP_ROWS) {
+        T* dst[EP_ROWS];
+#pragma unroll
+        for (int j = 0; j < EP_ROWS; ++j) {
+            dst[j] = nullptr;
+            if (p0 + j >= n_rows) continue;
+            const int m = meta[p0 + j];
+            if (m < 0) continue;  // pad row
+            const int owner = m >> PEER_ROW_BITS;
+            const int64_t row = m & PEER_ROW_MASK;
+            if (owner >= world || row >= peer_rows_cap) {
+                if (threadIdx.x == 0 && status) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
+                continue;
+            }
+            dst[j] = static_cast<T*>(peer_rows[owner]) + row * width;
+        }
+        for (int64_t c = threadIdx.x; c < nvec; c += EP_ROW_THREADS) {
+            Vec16<T> x[EP_ROWS];
+#pragma unroll
+            for (int j = 0; j < EP_ROWS; ++j)
+                if (dst[j]) x[j] = load16_stream(rows + (p0 + j) * row_stride + c * V);
+#pragma unroll
+            for (int j = 0; j < EP_ROWS; ++j)
+                if (dst[j]) store16(dst[j] + c * V, x[j]);
+        }
+    }
+}
+
+// Device words -> host memory that the device can address (pinned, mapped): a store instead of a
+// copy-engine transfer, so a small read-back never queues behind bulk downloads.
+__global__ void ep_publish_kernel(const int* __restrict__ src, int64_t n, int* __restrict__ host_words) {
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) host_words[i] = src[i];
+    __threadfence_system();
+}
+
 static int ep_grid(int64_t rows) {
     int64_t want = ceil_div(rows, EP_ROWS);
     int64_t cap = static_cast<int64_t>(num_sms()) * 8;
@@ -218,6 +267,15 @@ static int ep_copy_t(const void* rows, const int* meta, int64_t n_rows, int64_t 
     else
         ep_copy_rows_kernel<T, false><<<grid, EP_ROW_THREADS, 0, stream>>>(static_cast<const T*>(rows), meta, n_rows,
                                                                            width, static_cast<T*>(out));
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+static int ep_return_t(const void* rows, int64_t row_stride, const int* meta, int64_t n_rows, int64_t width,
+                       int world, void* const* peer_rows, int64_t peer_rows_cap, int* status, cudaStream_t stream) {
+    if (width % Vec16<T>::N || row_stride % Vec16<T>::N || !is_aligned16(rows)) return XMA_ERR_MISALIGNED;
+    ep_return_kernel<T><<<ep_grid(n_rows), EP_ROW_THREADS, 0, stream>>>(
+        static_cast<const T*>(rows), row_stride, meta, n_rows, width, world, peer_rows, peer_rows_cap, status);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -279,6 +337,35 @@ int xma_b200_ep_copy_rows(const void* rows, int dtype, const int32_t* meta, int6
         case XMA_F32: return xma::ep_copy_t<float>(rows, meta, n_rows, width, out, stream);
         case XMA_F16: return xma::ep_copy_t<__half>(rows, meta, n_rows, width, out, stream);
         case XMA_BF16: return xma::ep_copy_t<__nv_bfloat16>(rows, meta, n_rows, width, out, stream);
+    }
+    return XMA_ERR_BAD_DTYPE;
+}
+
+int xma_b200_ep_publish(const int32_t* src, int64_t n, int32_t* host_words, cudaStream_t stream) {
+    if (n == 0) return XMA_OK;
+    if (!src || !host_words) return XMA_ERR_NULL_POINTER;
+    if (n < 0) return XMA_ERR_BAD_SHAPE;
+    xma::ep_publish_kernel<<<1, 256, 0, stream>>>(src, n, host_words);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int xma_b200_ep_return(const void* rows, int dtype, int64_t row_stride, const int32_t* meta, int64_t n_rows,
+                       int64_t width, int world, void* const* peer_rows, int64_t peer_rows_cap, int* device_status,
+                       cudaStream_t stream) {
+    if (n_rows == 0) return XMA_OK;
+    if (!rows || !meta || !peer_rows) return XMA_ERR_NULL_POINTER;
+    if (n_rows < 0 || width <= 0 || world <= 0 || world > xma::PEER_MAX_RANKS || peer_rows_cap < 0)
+        return XMA_ERR_BAD_SHAPE;
+    switch (dtype) {
+        case XMA_F32:
+            return xma::ep_return_t<float>(rows, row_stride, meta, n_rows, width, world, peer_rows, peer_rows_cap,
+                                           device_status, stream);
+        case XMA_F16:
+            return xma::ep_return_t<__half>(rows, row_stride, meta, n_rows, width, world, peer_rows, peer_rows_cap,
+                                            device_status, stream);
+        case XMA_BF16:
+            return xma::ep_return_t<__nv_bfloat16>(rows, row_stride, meta, n_rows, width, world, peer_rows,
+                                                   peer_rows_cap, device_status, stream);
     }
     return XMA_ERR_BAD_DTYPE;
 }

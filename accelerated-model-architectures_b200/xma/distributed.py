@@ -26,12 +26,13 @@ ranks of one node map each other's exchange buffers once, CUDA IPC over NVLink):
     all_gather of the per-expert counts [W, E]  (tiny; one device->host read sizes the buffers)
     -> DISPATCH kernel: every routed token row is gathered and stored straight into its slot of the
        owner's padded, expert-major buffer, with a word naming its origin (home rank, token slot)
-    -> barrier -> up projection + SwiGLU -> down projection whose epilogue stores every output row
-       into the home rank's [T*K, H] buffer (GEMM and combine exchange are one kernel)
+    -> barrier -> up projection + SwiGLU -> down projection -> RETURN kernel: every output row is
+       stored into its slot of the home rank's [T*K, H] buffer (`fused_return=True`: by the GEMM's
+       own epilogue instead)
     -> barrier -> weighted sum over the k slots on the home rank.
 
-Backward mirrors it (dY rows dispatched with the routing weight applied, dX rows returned by the
-dX GEMM's epilogue). No kernel waits on another GPU: the phases are separated by a stream-ordered
+Backward mirrors it (dY rows dispatched with the routing weight applied, dX rows returned the same
+way). No kernel waits on another GPU: the phases are separated by a stream-ordered
 barrier (a one-element NCCL all-reduce), so a rank that stops costs a collective timeout, never a
 spinning kernel. Tensors kept for backward are private copies; the exchange buffers are reused by
 every call.
@@ -41,6 +42,7 @@ from __future__ import annotations
 
 import ctypes
 
+import numpy as np
 import torch
 import torch.distributed as dist
 import torch.nn as nn
@@ -165,11 +167,26 @@ class PeerLink:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self._token: torch.Tensor | None = None
+        self._pinned: torch.Tensor | None = None
 
     def all_gather_counts(self, counts: torch.Tensor) -> torch.Tensor:
         out = torch.empty(self.world * counts.numel(), dtype=counts.dtype, device=counts.device)
         dist.all_gather_into_tensor(out, counts.contiguous(), group=self.group)
         return out.view(self.world, -1)
+
+    def host_counts(self, count_matrix: torch.Tensor):
+        """The count matrix as a host numpy array: a kernel stores it into pinned host memory (no
+        copy-engine transfer that would queue behind bulk downloads) and the host waits on an event."""
+        n = count_matrix.numel()
+        if self._pinned is None or self._pinned.numel() < n:
+            self._pinned = torch.empty(n, dtype=torch.int32).pin_memory()
+        stream = torch.cuda.current_stream(count_matrix.device)
+        check(lib.xma_b200_ep_publish(count_matrix.data_ptr(), n, self._pinned.data_ptr(), stream.cuda_stream),
+              "xma_b200_ep_publish")
+        done = torch.cuda.Event()
+        done.record(stream)
+        done.synchronize()
+        return self._pinned[:n].numpy().reshape(count_matrix.shape).astype(np.int64)
 
     def barrier(self) -> None:
         if self._token is None:
@@ -214,8 +231,9 @@ class _Exchange:
     came from; `home_rows` [home_cap, H]: expert outputs returned to this rank, one row per token slot.
     `*_table`: int64 [W] device tensors with every rank's address of the same buffer."""
 
-    def __init__(self, link, device: torch.device, dtype: torch.dtype, hidden: int) -> None:
+    def __init__(self, link, device: torch.device, dtype: torch.dtype, hidden: int, fused_return: bool) -> None:
         self.link, self.device, self.dtype, self.hidden = link, device, dtype, hidden
+        self.fused_return = fused_return
         self.recv_cap = self.home_cap = 0
         self._held: list = []
         self.recv_rows = self.recv_meta = self.home_rows = None
@@ -259,11 +277,9 @@ class _PeerRoute:
         e_local = num_experts // world
         dev = count_matrix.device
         self.world, self.rank, self.rows, self.e_local = world, rank, rows, e_local
-        self.send_delta = torch.empty(num_experts, dtype=torch.int32, device=dev)
-        self.counts = torch.empty(e_local, dtype=torch.int32, device=dev)
-        self.pad_offsets = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
-        self.tile_prefix = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
-        self.tile_expert = torch.empty(rows // ROW_PAD + e_local, dtype=torch.int32, device=dev)
+        sizes = (num_experts, e_local, e_local + 1, e_local + 1, rows // ROW_PAD + e_local)
+        (self.send_delta, self.counts, self.pad_offsets, self.tile_prefix,
+         self.tile_expert) = torch.empty(sum(sizes), dtype=torch.int32, device=dev).split(sizes)
         ops.ep_plan_(count_matrix, rank, self.send_delta, self.counts, self.pad_offsets, self.tile_prefix,
                      self.tile_expert, exchange.recv_meta)
 
@@ -295,8 +311,14 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
         act = torch.empty(alloc, I, **opts)
         ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, route.tile_expert, route.tile_prefix, H, two_i,
                                EPI_SWIGLU, impl, tag="gemm_up_swiglu")
-        ops.grouped_gemm_rows_(act, w2, W_NK, exchange.home_rows, None, meta, route.tile_expert, route.tile_prefix,
-                               I, H, EPI_PLAIN, impl, exchange.home_table, tag="gemm_down")
+        if exchange.fused_return:
+            ops.grouped_gemm_rows_(act, w2, W_NK, exchange.home_rows, None, meta, route.tile_expert,
+                                   route.tile_prefix, I, H, EPI_PLAIN, impl, exchange.home_table, tag="gemm_down")
+        else:
+            out = torch.empty(alloc, H, **opts)
+            ops.grouped_gemm_rows_(act, w2, W_NK, out, None, None, route.tile_expert, route.tile_prefix, I, H,
+                                   EPI_PLAIN, impl, tag="gemm_down")
+            ops.ep_return_(out[:rows], meta, route.world, exchange.home_table, exchange.home_cap)
         link.barrier()
 
         ys = exchange.home_rows[:R].clone()
@@ -345,8 +367,14 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
         d_w1 = torch.empty_like(w1)
         ops.grouped_gemm_dw_(dgu, xs, route.counts, route.pad_offsets, d_w1, impl, tag="gemm_dw1")
         # dX rows straight back to the token's home rank
-        ops.grouped_gemm_rows_(dgu, w1, W_KN, exchange.home_rows, None, meta, route.tile_expert, route.tile_prefix,
-                               two_i, H, EPI_PLAIN, impl, exchange.home_table, tag="gemm_dx")
+        if exchange.fused_return:
+            ops.grouped_gemm_rows_(dgu, w1, W_KN, exchange.home_rows, None, meta, route.tile_expert,
+                                   route.tile_prefix, two_i, H, EPI_PLAIN, impl, exchange.home_table, tag="gemm_dx")
+        else:
+            dxs = torch.empty(alloc, H, **opts)
+            ops.grouped_gemm_rows_(dgu, w1, W_KN, dxs, None, None, route.tile_expert, route.tile_prefix, two_i, H,
+                                   EPI_PLAIN, impl, tag="gemm_dx")
+            ops.ep_return_(dxs[:rows], meta, route.world, exchange.home_table, exchange.home_cap)
         link.barrier()
 
         d_x = torch.empty(T, H, **opts)
@@ -360,10 +388,14 @@ class ExpertParallelMoE(nn.Module):
     weight `[E, H]`. forward(x [.., H]) -> (y, router_logits [T, E]) for this rank's tokens."""
 
     def __init__(self, local_moe: MoE, gate_weight: torch.Tensor, world_group=None,
-                 overlap_chunks: int | None = None, transport: str = "nccl", link=None) -> None:
+                 overlap_chunks: int | None = None, transport: str = "nccl", link=None,
+                 fused_return: bool = False) -> None:
         """`transport`: "nccl" (all-to-all collectives; any process group) or "peer" (stores into the
         other ranks' memory; the ranks must be GPUs of one node with peer access). `link` replaces the
-        `PeerLink` built from the process group (tests drive several ranks of one process with it)."""
+        `PeerLink` built from the process group (the tests run several ranks on one GPU with it).
+        `fused_return` (peer transport): the down-projection and dX GEMMs store their rows into the home
+        ranks' memory from their epilogues instead of a separate row kernel; one thread owns one row
+        there, and such 16-byte-per-row stores measured about 4x slower over NVLink than whole rows."""
         super().__init__()
         if not (isinstance(local_moe.act, SwiGLU) and local_moe.is_glu):
             raise ValueError("ExpertParallelMoE runs the fused SwiGLU expert block")
@@ -371,6 +403,7 @@ class ExpertParallelMoE(nn.Module):
             raise ValueError("transport must be 'nccl' or 'peer'")
         self.local = local_moe
         self.transport = transport
+        self.fused_return = fused_return
         if link is not None:
             self.link, self.group = link, None
             self.world, self.rank = link.world, link.rank
@@ -421,7 +454,7 @@ class ExpertParallelMoE(nn.Module):
     def _exchange(self, slot: int, x: torch.Tensor) -> _Exchange:
         key = (slot, x.device, x.dtype)
         if key not in self._exchanges:
-            self._exchanges[key] = _Exchange(self.link, x.device, x.dtype, self.hidden_size)
+            self._exchanges[key] = _Exchange(self.link, x.device, x.dtype, self.hidden_size, self.fused_return)
         return self._exchanges[key]
 
     def close(self) -> None:
@@ -440,8 +473,8 @@ class ExpertParallelMoE(nn.Module):
             count_matrix = self.link.all_gather_counts(plan.counts)  # [W, E] int32
             # one small device->host read per step: every rank sizes every rank's buffers from it,
             # so all of them take the same (collective) decision to grow the exchange buffers
-            host = count_matrix.cpu().to(torch.int64)
-            padded = ((host.sum(0) + ROW_PAD - 1) // ROW_PAD * ROW_PAD).view(W, e_local).sum(1)
+            host = self.link.host_counts(count_matrix)
+            padded = ((host.sum(0) + ROW_PAD - 1) // ROW_PAD * ROW_PAD).reshape(W, e_local).sum(1)
             exchange = self._exchange(slot, x)
             # (grouped buffers are allocated for rows // 128 + e_local tiles, the received rows included)
             exchange.ensure(int(padded.max()) + e_local * ROW_PAD, int(host.sum(1).max()))

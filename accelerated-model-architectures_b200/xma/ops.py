@@ -235,6 +235,18 @@ def _ep_copy_rows_op(rows: Tensor, meta: Tensor, out: Tensor) -> None:
     )
 
 
+@torch.library.custom_op(f"{_NS}::ep_return", mutates_args=(), device_types="cuda")
+def _ep_return_op(rows: Tensor, meta: Tensor, world: int, peer_rows: Tensor, peer_rows_cap: int) -> None:
+    """Stores every row whose origin word is >= 0 into the exchange buffer of its home rank."""
+    require_cuda(rows, meta, peer_rows)
+    check(
+        lib.xma_b200_ep_return(ptr(rows), dtype_code(rows.dtype), _row_stride(rows), ptr(meta), rows.size(0),
+                               rows.size(1), world, ptr(peer_rows), peer_rows_cap, ptr(status_word(rows.device)),
+                               current_stream(rows.device)),
+        "xma_b200_ep_return",
+    )
+
+
 @torch.library.custom_op(f"{_NS}::swiglu_fwd", mutates_args={"y"}, device_types="cuda")
 def _swiglu_fwd_op(g: Tensor, u: Tensor, y: Tensor) -> None:
     require_cuda(g, u, y)
@@ -335,6 +347,7 @@ grouped_gemm_dw_ = _wrap(_grouped_gemm_dw_op, "grouped_gemm_dw", 1)
 ep_plan_ = _wrap(_ep_plan_op, "ep_plan", 1)
 ep_dispatch_ = _wrap(_ep_dispatch_op, "ep_dispatch", 1)
 ep_copy_rows_ = _wrap(_ep_copy_rows_op, "ep_copy_rows", 1)
+ep_return_ = _wrap(_ep_return_op, "ep_return", 1)
 swiglu_fwd_ = _wrap(_swiglu_fwd_op, "swiglu_fwd", 1)
 swiglu_bwd_ = _wrap(_swiglu_bwd_op, "swiglu_bwd", 1)
 swiglu_packed_fwd_ = _wrap(_swiglu_packed_fwd_op, "swiglu_packed_fwd", 1)

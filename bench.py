@@ -327,6 +327,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--transport", choices=["peer", "nccl"], default="peer",
                     help="row exchange of the expert-parallel layer: stores into peer memory, or NCCL all-to-all")
+    ap.add_argument("--fused-return", action="store_true",
+                    help="peer transport: return rows from the GEMM epilogues instead of the row kernel")
     ap.add_argument("--ep-chunks", type=int, default=None,
                     help="micro-batches per step in the expert-parallel layer (overlap of all-to-all and GEMM)")
     args = ap.parse_args()
@@ -367,7 +369,7 @@ def main() -> None:
         from xma.distributed import ExpertParallelMoE
 
         layer = ExpertParallelMoE(moe, gate, world_group=dist.group.WORLD, overlap_chunks=args.ep_chunks,
-                                  transport=args.transport)
+                                  transport=args.transport, fused_return=args.fused_return)
     else:
         with torch.no_grad():
             moe.gate.weight.copy_(gate)
@@ -478,7 +480,7 @@ def main() -> None:
             dx.record_stream(d2h)
         main_stream.wait_stream(d2h)
 
-    e2e_run(2)
+    e2e_run(4)  # the caching allocator settles (tensors held for the downloads change its working set)
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
@@ -570,7 +572,8 @@ def main() -> None:
                        "hidden": H, "intermediate": I, "experts": E, "top_k": w["top_k"],
                        "parallelism": "single GPU" if world == 1 else
                        f"expert-parallel ep{world}, "
-                       + ("dispatch kernel + GEMM epilogues storing into peer memory over NVLink"
+                       + (("dispatch kernel + GEMM epilogues" if args.fused_return else "dispatch and return kernels")
+                          + " storing rows into peer memory over NVLink"
                           if args.transport == "peer" else "NCCL all-to-all")
                        + f", {layer.overlap_chunks} micro-batch(es) per step",
                        "l2_policy": "inputs_exceed_l2 (weights + activations >> 126 MB)"},

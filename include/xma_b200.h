@@ -221,6 +221,18 @@ int xma_b200_ep_dispatch(const void* src, int dtype, int64_t src_row_stride, con
 int xma_b200_ep_copy_rows(const void* rows, int dtype, const int32_t* meta, int64_t n_rows, int64_t width, void* out,
                           cudaStream_t stream);
 
+/* host_words[i] = src[i] for i < n, written by a kernel: host_words is pinned host memory that the device
+ * addresses directly (cudaHostAlloc / cudaHostRegister under unified addressing). The host reads it after
+ * an event recorded behind the call; unlike a device->host copy it does not wait in the copy engine's queue. */
+int xma_b200_ep_publish(const int32_t* src, int64_t n, int32_t* host_words, cudaStream_t stream);
+
+/* Return: peer_rows[meta[r] >> 24][meta[r] & 0xffffff, :] = rows[r, :] for every r < n_rows with meta[r] >= 0
+ * (expert output rows back to the token's home rank, whole rows per warp store). The same movement can be
+ * fused into the GEMM (xma_b200_grouped_gemm_rows_peer), whose row-per-thread stores are slower over NVLink. */
+int xma_b200_ep_return(const void* rows, int dtype, int64_t row_stride, const int32_t* meta, int64_t n_rows,
+                       int64_t width, int world, void* const* peer_rows, int64_t peer_rows_cap, int* device_status,
+                       cudaStream_t stream);
+
 /* Exchange buffers: zero-filled device memory of the current device that the other processes of the node map
  * into their address space (CUDA IPC; the devices must be peers). _export writes
  * xma_b200_exchange_handle_bytes() bytes that another process hands to _open; _close unmaps, _free releases. */

@@ -43,12 +43,16 @@ def _run(world: int, cfg: dict):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("transport,chunks", [("nccl", 1), ("nccl", 2), ("peer", 1), ("peer", 2)])
-def test_expert_parallel_matches_single_device_oracle(transport, chunks):
-    _run(2, dict(shared_gpu=False, transport=transport, chunks=chunks, dtype="bfloat16", tokens=150, steps=2))
+@pytest.mark.parametrize("transport,chunks,fused", [("nccl", 1, False), ("nccl", 2, False), ("peer", 1, False),
+                                                    ("peer", 2, False), ("peer", 1, True)])
+def test_expert_parallel_matches_single_device_oracle(transport, chunks, fused):
+    _run(2, dict(shared_gpu=False, transport=transport, chunks=chunks, dtype="bfloat16", tokens=150, steps=2,
+                 fused_return=fused))
 
 
-@pytest.mark.parametrize("world,dtype,chunks", [(2, "bfloat16", 1), (4, "bfloat16", 1), (2, "float32", 1),
-                                                (2, "bfloat16", 2), (8, "bfloat16", 1)])
-def test_peer_transport_with_ranks_sharing_one_gpu(world, dtype, chunks):
-    _run(world, dict(shared_gpu=True, transport="peer", chunks=chunks, dtype=dtype, tokens=300, steps=2))
+@pytest.mark.parametrize("world,dtype,chunks,fused", [(2, "bfloat16", 1, False), (4, "bfloat16", 1, True),
+                                                      (2, "float32", 1, False), (2, "float32", 1, True),
+                                                      (2, "bfloat16", 2, False), (8, "bfloat16", 1, False)])
+def test_peer_transport_with_ranks_sharing_one_gpu(world, dtype, chunks, fused):
+    _run(world, dict(shared_gpu=True, transport="peer", chunks=chunks, dtype=dtype, tokens=300, steps=2,
+                     fused_return=fused))
