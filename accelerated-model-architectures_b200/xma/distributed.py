@@ -194,21 +194,39 @@ class PeerLink:
         dist.all_reduce(self._token, group=self.group)
 
     def share(self, nbytes: int, device: torch.device):
-        """Collective. -> (block of this rank, [address of every rank's block in this process], mapped addresses)."""
-        block = _DeviceBlock(nbytes, device)
+        """Collective. -> (block of this rank, [address of every rank's block in this process], mapped addresses).
+        A failure on any rank (allocation, export, mapping) raises on every rank, after the collectives."""
+        block, handle, error = None, None, None
+        try:
+            block = _DeviceBlock(nbytes, device)
+            handle = block.export()
+        except Exception as exc:  # noqa: BLE001 - reported to every rank below
+            error = repr(exc)
         handles: list = [None] * self.world
-        dist.all_gather_object(handles, block.export(), group=self.group)
+        dist.all_gather_object(handles, handle, group=self.group)
         addresses, mapped = [], []
-        with torch.cuda.device(device):
-            for r, handle in enumerate(handles):
-                if r == self.rank:
-                    addresses.append(block.ptr)
-                    continue
-                out = ctypes.c_void_p()
-                check(lib.xma_b200_exchange_open(handle, ctypes.byref(out)), "xma_b200_exchange_open")
-                addresses.append(int(out.value))
-                mapped.append(int(out.value))
-        dist.barrier(group=self.group)
+        if error is None and all(h is not None for h in handles):
+            try:
+                with torch.cuda.device(device):
+                    for r, peer_handle in enumerate(handles):
+                        if r == self.rank:
+                            addresses.append(block.ptr)
+                            continue
+                        out = ctypes.c_void_p()
+                        check(lib.xma_b200_exchange_open(peer_handle, ctypes.byref(out)), "xma_b200_exchange_open")
+                        addresses.append(int(out.value))
+                        mapped.append(int(out.value))
+            except Exception as exc:  # noqa: BLE001
+                error = repr(exc)
+        errors: list = [None] * self.world
+        dist.all_gather_object(errors, error, group=self.group)  # also: everyone has mapped before anyone goes on
+        if any(h is None for h in handles) or any(e is not None for e in errors):
+            for address in mapped:
+                lib.xma_b200_exchange_close(address)
+            dist.barrier(group=self.group)
+            if block is not None:
+                block.free()
+            raise RuntimeError(f"the ranks could not map each other's exchange buffers: {errors}")
         return block, addresses, mapped
 
     def release(self, block, mapped: list[int]) -> None:

@@ -366,8 +366,18 @@ def main() -> None:
     local = (rank * E // world, (rank + 1) * E // world)
     moe, gate = make_layer(w, device, dtype, seed=100 + rank, local_experts=local if world > 1 else None)
     if world > 1:
-        from xma.distributed import ExpertParallelMoE
+        from xma.distributed import ExpertParallelMoE, PeerLink
 
+        if args.transport == "peer":
+            # the peer transport needs the ranks to map each other's memory; where the node does not allow
+            # that, every rank learns it here (share() fails collectively) and the run uses NCCL all-to-all
+            try:
+                probe = PeerLink(dist.group.WORLD)
+                probe.release(*probe.share(1 << 20, device)[::2])
+            except RuntimeError as exc:
+                if rank == 0:
+                    print(f"peer transport unavailable ({exc}); using NCCL all-to-all", file=sys.stderr)
+                args.transport = "nccl"
         layer = ExpertParallelMoE(moe, gate, world_group=dist.group.WORLD, overlap_chunks=args.ep_chunks,
                                   transport=args.transport, fused_return=args.fused_return)
     else:
