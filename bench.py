@@ -599,6 +599,8 @@ def main() -> None:
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
+        if world > 1 and args.transport == "peer":
+            layer.close()  # collective: unmap the other ranks' exchange buffers before anyone frees them
         dist.destroy_process_group()
 
 
