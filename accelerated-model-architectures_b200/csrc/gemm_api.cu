@@ -58,12 +58,14 @@ int xma_b200_grouped_gemm_rows_peer(const void* a, int64_t a_row_stride, const v
     g.stream = stream;
     int rc = check_rows(g);
     if (rc) return rc;
+    if (out_peers) g.epilogue = xma::EPI_PLAIN_PEER;  // same contraction, rows stored into the ranks' buffers
     if (impl == 1) return xma::rows_gemm_simt(g);
     if (impl == 2) return xma::rows_gemm_tc(g);
     if (impl == 3) return xma::rows_gemm_tc2(g);
     if (impl != 0) return XMA_ERR_BAD_SHAPE;
     if (xma::rows_gemm_tc_supported(g)) {
-        if (g.epilogue != xma::EPI_PLAIN && large_experts(g.tile_cap, g.num_experts)) return xma::rows_gemm_tc2(g);
+        const bool plain = g.epilogue == xma::EPI_PLAIN || g.epilogue == xma::EPI_PLAIN_PEER;
+        if (!plain && large_experts(g.tile_cap, g.num_experts)) return xma::rows_gemm_tc2(g);
         return xma::rows_gemm_tc(g);
     }
     return xma::rows_gemm_simt(g);

@@ -20,7 +20,11 @@ enum WeightLayout { W_NK = 0, W_KN = 1 };
 //                 where acc is the gradient of the activation output.
 //   EPI_SWIGLU_PACKED / EPI_DSWIGLU_PACKED : the same with gate/up interleaved along the columns
 //                 (g, u, g, u, ...) in aux and in the weight rows, as swiglu_packed expects.
-enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2, EPI_SWIGLU_PACKED = 3, EPI_DSWIGLU_PACKED = 4 };
+//   EPI_PLAIN_PEER : internal (chosen when out_peers is set): plain store of each row into the buffer of
+//                 the rank that row_map names.
+enum Epilogue {
+    EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2, EPI_SWIGLU_PACKED = 3, EPI_DSWIGLU_PACKED = 4, EPI_PLAIN_PEER = 5
+};
 
 struct RowsGemmArgs {
     const void* a;             // [rows_cap, Kd] grouped (padded) rows

@@ -138,8 +138,9 @@ static int rows_gemm_simt_t(const RowsGemmArgs& g) {
     // the output for its backward (rewritten in place afterwards), the output otherwise.
     T* raw = static_cast<T*>(g.epilogue == EPI_SWIGLU ? g.aux : g.out);
     const int64_t raw_stride = (g.epilogue == EPI_SWIGLU) ? g.aux_stride : g.out_stride;
-    const int* row_map = (g.epilogue == EPI_PLAIN) ? g.row_map : nullptr;
-    void* const* out_peers = (g.epilogue == EPI_PLAIN) ? g.out_peers : nullptr;
+    const bool plain = (g.epilogue == EPI_PLAIN || g.epilogue == EPI_PLAIN_PEER);
+    const int* row_map = plain ? g.row_map : nullptr;
+    void* const* out_peers = (g.epilogue == EPI_PLAIN_PEER) ? g.out_peers : nullptr;
     dim3 grid(static_cast<unsigned>(2 * g.tile_cap), static_cast<unsigned>(ceil_div(g.n, ST_BN)));
     if (grid.y > 65535) return XMA_ERR_TOO_LARGE;
     rows_gemm_simt_kernel<T><<<grid, ST_THREADS, 0, g.stream>>>(

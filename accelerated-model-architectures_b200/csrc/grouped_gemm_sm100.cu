@@ -29,6 +29,7 @@ struct Shared {
     uint64_t* acc_empty;  // [2]
     uint32_t* tmem_ptr;
     volatile int* abort_flag;
+    uint8_t* peer_stage;  // [PEER_STAGE_BYTES], 16-byte aligned
 };
 
 __device__ __forceinline__ Shared carve_smem(uint8_t* raw) {
@@ -46,6 +47,7 @@ __device__ __forceinline__ Shared carve_smem(uint8_t* raw) {
     s.acc_empty = s.acc_full + 2;
     s.tmem_ptr = reinterpret_cast<uint32_t*>(s.acc_empty + 2);
     s.abort_flag = reinterpret_cast<volatile int*>(s.tmem_ptr + 1);
+    s.peer_stage = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(s.tmem_ptr + 2) + 15) & ~static_cast<uintptr_t>(15));
     return s;
 }
 
@@ -205,6 +207,8 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int part = (warp - 2) >> 2;                            // which share of the columns this warp stores
         const int chunks = (BN / 32) / parts;                        // 32-column chunks per warp
         const int row_in_tile = quarter * 32 + lane;
+        // one staging region per epilogue warp when there are four of them
+        uint8_t* peer_stage = (parts == 1) ? s.peer_stage + (warp - 2) * PEER_STAGE_WARP_BYTES : nullptr;
         uint32_t lt = 0;
         for (int64_t w = blockIdx.x; w < total; w += gridDim.x, ++lt) {
             const RowsWork wk = decode_rows(s.tile_prefix, E, n_tiles, w);
@@ -213,8 +217,8 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
 
             if (!rows_epilogue_tile<T, EPI>(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag, taddr, r, true, wk.n_tile, n,
-                                            half_n, out, out_stride, aux, aux_stride, row_map, out_peers, part,
-                                            chunks))
+                                            half_n, out, out_stride, aux, aux_stride, row_map, out_peers, peer_stage,
+                                            part, chunks))
                 break;
             tc_fence_before();
             mbar_arrive(&s.acc_empty[buf]);
@@ -358,7 +362,9 @@ static int launch_rows(const RowsGemmArgs& g, const CUtensorMap& ta, const CUten
     int rc = set_smem(kernel);
     if (rc) return rc;
     const uint32_t idesc = make_idesc(g.dtype, false, WL == W_KN);
-    kernel<<<num_sms(), block_threads((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) ? 8 : 4), SMEM_BYTES, g.stream>>>(
+    // (rows bound for other ranks are staged per epilogue warp: always four warps then)
+    const int threads = (EPI == EPI_PLAIN_PEER) ? 64 + 32 * 4 : block_threads((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) ? 8 : 4);
+    kernel<<<num_sms(), threads, SMEM_BYTES, g.stream>>>(
         ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
         g.out_peers, g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
     return static_cast<int>(cudaGetLastError());
@@ -374,6 +380,8 @@ static int rows_dispatch(const RowsGemmArgs& g, const CUtensorMap& ta, const CUt
     XMA_ROWS_CASE(W_KN, EPI_DSWIGLU);
     XMA_ROWS_CASE(W_NK, EPI_SWIGLU_PACKED);
     XMA_ROWS_CASE(W_KN, EPI_DSWIGLU_PACKED);
+    XMA_ROWS_CASE(W_NK, EPI_PLAIN_PEER);
+    XMA_ROWS_CASE(W_KN, EPI_PLAIN_PEER);
 #undef XMA_ROWS_CASE
     return XMA_ERR_UNSUPPORTED;
 }
@@ -386,12 +394,14 @@ bool rows_gemm_tc_supported(const RowsGemmArgs& g) {
     if (g.num_experts > tc::MAX_EXPERTS || g.kd <= 0 || g.n <= 0) return false;
     if (g.kd % 8 || g.n % 8 || g.a_stride % 8 || g.out_stride % 8) return false;
     if (!is_aligned16(g.a) || !is_aligned16(g.w) || !is_aligned16(g.out)) return false;
-    const bool combo = (g.w_layout == W_NK && (g.epilogue == EPI_PLAIN || g.epilogue == EPI_SWIGLU ||
+    const bool plain = (g.epilogue == EPI_PLAIN || g.epilogue == EPI_PLAIN_PEER);
+    const bool combo = (g.w_layout == W_NK && (plain || g.epilogue == EPI_SWIGLU ||
                                                g.epilogue == EPI_SWIGLU_PACKED)) ||
-                       (g.w_layout == W_KN && (g.epilogue == EPI_PLAIN || g.epilogue == EPI_DSWIGLU ||
+                       (g.w_layout == W_KN && (plain || g.epilogue == EPI_DSWIGLU ||
                                                g.epilogue == EPI_DSWIGLU_PACKED));
     if (!combo) return false;
-    if (g.epilogue != EPI_PLAIN) {
+    if (g.epilogue == EPI_PLAIN_PEER && (!g.row_map || !g.out_peers)) return false;
+    if (!plain) {
         if (!g.aux || g.aux_stride % 8 || !is_aligned16(g.aux) || g.row_map) return false;
         if ((g.epilogue == EPI_SWIGLU || g.epilogue == EPI_SWIGLU_PACKED) && (g.n % 16)) return false;
     }

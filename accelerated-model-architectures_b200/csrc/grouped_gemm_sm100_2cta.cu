@@ -308,7 +308,7 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
             if (!rows_epilogue_tile<T, EPI>(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag, taddr, r, wk.active,
                                             wk.n_tile, n, half_n, out, out_stride, aux, aux_stride, row_map, out_peers,
-                                            part, chunks))
+                                            nullptr, part, chunks))
                 break;
             tc_fence_before();
             __syncwarp();

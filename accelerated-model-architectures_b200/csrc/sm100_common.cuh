@@ -27,8 +27,12 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_EXPERTS = 1024;
 constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64 x 64 box of an MN-major operand: 8 KiB
+// Staging of the plain epilogue when its rows go to other ranks' memory: 32 rows x 64 columns of
+// 16-bit values per epilogue warp (4 warps), so that a warp store covers 128 contiguous bytes per row.
+constexpr int PEER_STAGE_WARP_BYTES = 32 * 128;
+constexpr int PEER_STAGE_BYTES = 4 * PEER_STAGE_WARP_BYTES;
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + static_cast<size_t>(STAGES) * STAGE_BYTES +
-                              (MAX_EXPERTS + 1) * sizeof(int) + 256 /*barriers*/;
+                              (MAX_EXPERTS + 1) * sizeof(int) + 256 /*barriers*/ + PEER_STAGE_BYTES;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -263,15 +267,12 @@ __device__ __forceinline__ bool rows_epilogue_tile(uint64_t* acc_full_bar, uint3
                                                    int half_n, T* __restrict__ out, int64_t out_stride,
                                                    T* __restrict__ aux, int64_t aux_stride,
                                                    const int* __restrict__ row_map,
-                                                   void* const* __restrict__ out_peers, int part, int chunks) {
+                                                   void* const* __restrict__ out_peers, uint8_t* peer_stage,
+                                                   int part, int chunks) {
     if (!active) return mbar_wait_epilogue(acc_full_bar, parity, abort_flag);
     if (EPI == EPI_PLAIN) {
         int64_t dst = r;
         if (row_map) dst = row_map[r];
-        if (out_peers && dst >= 0) {  // the row belongs to another rank's buffer: (rank << 24) | row
-            out = static_cast<T*>(out_peers[dst >> PEER_ROW_BITS]);
-            dst &= PEER_ROW_MASK;
-        }
         const int n0 = n_tile * BN;
         if (!mbar_wait_epilogue(acc_full_bar, parity, abort_flag)) return false;
         tc_fence_after();
@@ -288,6 +289,69 @@ __device__ __forceinline__ bool rows_epilogue_tile(uint64_t* acc_full_bar, uint3
                     if (col + 8 * i < n)
                         *reinterpret_cast<uint4*>(p + 8 * i) =
                             pack8<T>(reinterpret_cast<const float*>(&v[8 * i]));
+                }
+            }
+        }
+    } else if (EPI == EPI_PLAIN_PEER) {
+        // Plain store whose rows go to other ranks' memory: row_map[r] = (rank << 24) | row of that rank's
+        // buffer. A thread owns one row, so direct stores would be 32 pieces of 16 bytes in 32 rows per warp
+        // instruction, which NVLink moves poorly. Two chunks (64 columns) are staged in shared memory
+        // (16-byte pieces XOR-swizzled by row: conflict-free both ways) and stored 4 rows x 128 contiguous
+        // bytes at a time; the row addresses travel between lanes by shuffle.
+        int64_t dst = row_map[r];
+        if (dst >= 0) {
+            out = static_cast<T*>(out_peers[dst >> PEER_ROW_BITS]);
+            dst &= PEER_ROW_MASK;
+        }
+        const int n0 = n_tile * BN;
+        if (!mbar_wait_epilogue(acc_full_bar, parity, abort_flag)) return false;
+        tc_fence_after();
+        if (peer_stage && (chunks & 1) == 0) {
+            const int lane = threadIdx.x & 31;
+            const uint64_t row_addr = (dst >= 0) ? reinterpret_cast<uint64_t>(out + dst * out_stride) : 0ull;
+            const uint32_t addr_lo = static_cast<uint32_t>(row_addr), addr_hi = static_cast<uint32_t>(row_addr >> 32);
+            uint4* stage = reinterpret_cast<uint4*>(peer_stage);  // [32 rows][8 pieces]
+#pragma unroll 1
+            for (int c = part * chunks; c < (part + 1) * chunks; c += 2) {
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + (c + h) * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        stage[lane * 8 + ((h * 4 + i) ^ (lane & 7))] =
+                            pack8<T>(reinterpret_cast<const float*>(&v[8 * i]));
+                }
+                __syncwarp();
+                const int col0 = n0 + c * 32;
+                const int k = lane & 7;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rr = i * 4 + (lane >> 3);
+                    const uint4 x = stage[rr * 8 + (k ^ (rr & 7))];
+                    const uint32_t lo = __shfl_sync(0xffffffffu, addr_lo, rr);
+                    const uint32_t hi = __shfl_sync(0xffffffffu, addr_hi, rr);
+                    T* p = reinterpret_cast<T*>((static_cast<uint64_t>(hi) << 32) | lo);
+                    if (p && col0 + k * 8 < n) *reinterpret_cast<uint4*>(p + col0 + k * 8) = x;
+                }
+                __syncwarp();
+            }
+        } else {
+#pragma unroll 1
+            for (int c = part * chunks; c < (part + 1) * chunks; ++c) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c * 32, v);
+                tmem_ld_wait();
+                const int col = n0 + c * 32;
+                if (dst >= 0 && col < n) {
+                    T* p = out + dst * out_stride + col;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (col + 8 * i < n)
+                            *reinterpret_cast<uint4*>(p + 8 * i) =
+                                pack8<T>(reinterpret_cast<const float*>(&v[8 * i]));
+                    }
                 }
             }
         }

@@ -215,3 +215,52 @@ def test_rows_gemm_packed_swiglu_epilogues(impl, dtype, counts, kd, inter):
     with pytest.raises(RuntimeError):
         ops.grouped_gemm_rows_(a, w1, _lib.W_NK, act, gu, None, plan.tile_expert, plan.tile_prefix, kd, 2 * inter,
                                _lib.EPI_SWIGLU_PACKED, SIMT)
+
+
+@pytest.mark.parametrize("impl,dtype", [pytest.param(SIMT, torch.float32, id="cudacore-f32"),
+                                        pytest.param(TC, torch.bfloat16, id="tcgen05-bf16"),
+                                        pytest.param(0, torch.float16, id="auto-f16")])
+@pytest.mark.parametrize("counts,kd,n", [([5, 0, 130, 1], 64, 256), ([300, 7, 0, 0, 129, 64], 576, 264),
+                                         ([1000, 24], 256, 1032)])
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+def test_rows_gemm_peer_output_matches_scattered_output(impl, dtype, counts, kd, n, layout):
+    """out_peers: every output row is stored into the buffer that its row_map word names
+    ((buffer << 24) | row). The buffers here are tensors of the same device; the values must be bit-equal to
+    the same GEMM without the table, whatever the epilogue does to coalesce the stores."""
+    from xma import _lib, ops
+
+    E, R = len(counts), int(sum(counts))
+    plan, _ = _plan(counts, E)
+    a, _ = _grouped(plan, R, kd, dtype, seed=4)
+    rng = np.random.RandomState(6)
+    shape = (E, n, kd) if layout == "nk" else (E, kd, n)
+    w = torch.from_numpy((rng.standard_normal(shape) * 0.05).astype(np.float32)).to(dtype).cuda()
+    wl = _lib.W_NK if layout == "nk" else _lib.W_KN
+
+    ref = torch.full((plan.row_cap, n), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(a, w, wl, ref, None, None, plan.tile_expert, plan.tile_prefix, kd, n, _lib.EPI_PLAIN, impl)
+
+    buffers = 3
+    src = plan.row_src.cpu().numpy()
+    valid = np.nonzero(src >= 0)[0]
+    owner = rng.randint(0, buffers, size=valid.size)
+    slot = np.empty(valid.size, np.int64)
+    for b in range(buffers):
+        idx = np.nonzero(owner == b)[0]
+        slot[idx] = rng.permutation(idx.size)
+    row_map = np.full(src.shape, -1, np.int32)
+    row_map[valid] = (owner << 24) | slot
+    cap = int(max((owner == b).sum() for b in range(buffers))) + 1
+    outs = [torch.full((cap, n), float("nan"), dtype=dtype, device="cuda") for _ in range(buffers)]
+    table = torch.tensor([o.data_ptr() for o in outs], dtype=torch.int64, device="cuda")
+    ops.grouped_gemm_rows_(a, w, wl, outs[0], None, torch.from_numpy(row_map).cuda(), plan.tile_expert,
+                           plan.tile_prefix, kd, n, _lib.EPI_PLAIN, impl, table)
+    torch.cuda.synchronize()
+    assert _lib.read_and_clear_device_status(torch.device("cuda")) == 0
+    for b in range(buffers):
+        idx = np.nonzero(owner == b)[0]
+        got = outs[b][torch.from_numpy(slot[idx]).cuda()]
+        want = ref[torch.from_numpy(valid[idx]).cuda()]
+        assert torch.equal(got, want), (b, layout)
+        untouched = np.setdiff1d(np.arange(cap), slot[idx])
+        assert torch.isnan(outs[b][torch.from_numpy(untouched).cuda()]).all()
