@@ -14,10 +14,12 @@
 //                          or zero-fill of the pad rows in place.
 //   * ep_return_kernel   : owner side, expert output rows -> the home rank named by their origin
 //                          word, whole rows at a time (512 contiguous bytes per warp store).
-// The way back can also be fused into the grouped GEMM (`out_peers` of the rows GEMM: the plain
-// epilogue stores each output row to its home rank), but an epilogue thread owns one row, so a warp
-// store is 32 pieces of 16 bytes in 32 rows; over NVLink those reached about 125 GB/s against about
-// 560 GB/s for the row-contiguous stores of ep_return_kernel, so the separate kernel is the default.
+// By default the way back is fused into the grouped GEMM instead (`out_peers` of the rows GEMM): its
+// epilogue stores each output row to its home rank. An epilogue thread owns one accumulator row, so
+// storing straight from registers would be 32 pieces of 16 bytes in 32 rows per warp instruction,
+// which NVLink moved at about 125 GB/s; the epilogue therefore stages 64 columns in shared memory and
+// stores 128 contiguous bytes per row, which hides the exchange inside the GEMM (8 GPUs, 128 experts
+// top-8: down projection 1.33 ms plain + 1.41 ms return kernel -> 1.54 ms fused).
 // No kernel here waits on another GPU; ranks are ordered by the caller's stream-ordered barrier
 // between the phases.
 #include "common.cuh"

@@ -26,9 +26,9 @@ ranks of one node map each other's exchange buffers once, CUDA IPC over NVLink):
     all_gather of the per-expert counts [W, E]  (tiny; one device->host read sizes the buffers)
     -> DISPATCH kernel: every routed token row is gathered and stored straight into its slot of the
        owner's padded, expert-major buffer, with a word naming its origin (home rank, token slot)
-    -> barrier -> up projection + SwiGLU -> down projection -> RETURN kernel: every output row is
-       stored into its slot of the home rank's [T*K, H] buffer (`fused_return=True`: by the GEMM's
-       own epilogue instead)
+    -> barrier -> up projection + SwiGLU -> down projection whose epilogue stores every output row
+       into its slot of the home rank's [T*K, H] buffer: GEMM and return exchange are one kernel
+       (`fused_return=False`: a separate row kernel after a plain GEMM)
     -> barrier -> weighted sum over the k slots on the home rank.
 
 Backward mirrors it (dY rows dispatched with the routing weight applied, dX rows returned the same
@@ -130,6 +130,28 @@ class _CombineRows(torch.autograd.Function):
         return d_rows, d_rw, None, None
 
 
+_PINNED: dict = {}
+
+
+def _host_words(words: torch.Tensor):
+    """int32 device tensor -> host numpy array (int64, same shape). A kernel stores the words into pinned
+    host memory and the host waits on an event: unlike a device->host copy, the read does not queue in
+    the copy engine behind bulk downloads of earlier steps."""
+    if not words.is_cuda:
+        return words.numpy().astype(np.int64)
+    n = words.numel()
+    words = words.contiguous()
+    pinned = _PINNED.get(words.device)
+    if pinned is None or pinned.numel() < n:
+        pinned = _PINNED[words.device] = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
+    stream = torch.cuda.current_stream(words.device)
+    check(lib.xma_b200_ep_publish(words.data_ptr(), n, pinned.data_ptr(), stream.cuda_stream), "xma_b200_ep_publish")
+    done = torch.cuda.Event()
+    done.record(stream)
+    done.synchronize()
+    return pinned[:n].numpy().reshape(tuple(words.shape)).astype(np.int64)
+
+
 # ---- peer-memory transport ---------------------------------------------------------------------------
 class _DeviceBlock:
     """`cudaMalloc` memory of the current device, outside torch's caching allocator so that it can be
@@ -167,7 +189,6 @@ class PeerLink:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self._token: torch.Tensor | None = None
-        self._pinned: torch.Tensor | None = None
 
     def all_gather_counts(self, counts: torch.Tensor) -> torch.Tensor:
         out = torch.empty(self.world * counts.numel(), dtype=counts.dtype, device=counts.device)
@@ -175,18 +196,8 @@ class PeerLink:
         return out.view(self.world, -1)
 
     def host_counts(self, count_matrix: torch.Tensor):
-        """The count matrix as a host numpy array: a kernel stores it into pinned host memory (no
-        copy-engine transfer that would queue behind bulk downloads) and the host waits on an event."""
-        n = count_matrix.numel()
-        if self._pinned is None or self._pinned.numel() < n:
-            self._pinned = torch.empty(n, dtype=torch.int32).pin_memory()
-        stream = torch.cuda.current_stream(count_matrix.device)
-        check(lib.xma_b200_ep_publish(count_matrix.data_ptr(), n, self._pinned.data_ptr(), stream.cuda_stream),
-              "xma_b200_ep_publish")
-        done = torch.cuda.Event()
-        done.record(stream)
-        done.synchronize()
-        return self._pinned[:n].numpy().reshape(count_matrix.shape).astype(np.int64)
+        """The count matrix as a host numpy array (int64)."""
+        return _host_words(count_matrix)
 
     def barrier(self) -> None:
         if self._token is None:
@@ -407,13 +418,13 @@ class ExpertParallelMoE(nn.Module):
 
     def __init__(self, local_moe: MoE, gate_weight: torch.Tensor, world_group=None,
                  overlap_chunks: int | None = None, transport: str = "nccl", link=None,
-                 fused_return: bool = False) -> None:
+                 fused_return: bool = True) -> None:
         """`transport`: "nccl" (all-to-all collectives; any process group) or "peer" (stores into the
         other ranks' memory; the ranks must be GPUs of one node with peer access). `link` replaces the
         `PeerLink` built from the process group (the tests run several ranks on one GPU with it).
         `fused_return` (peer transport): the down-projection and dX GEMMs store their rows into the home
-        ranks' memory from their epilogues instead of a separate row kernel; one thread owns one row
-        there, and such 16-byte-per-row stores measured about 4x slower over NVLink than whole rows."""
+        ranks' memory from their own epilogues (GEMM and exchange are one kernel; the tile is staged in
+        shared memory so that each row leaves in 128-byte pieces); False runs a separate row kernel."""
         super().__init__()
         if not (isinstance(local_moe.act, SwiGLU) and local_moe.is_glu):
             raise ValueError("ExpertParallelMoE runs the fused SwiGLU expert block")
@@ -517,8 +528,8 @@ class ExpertParallelMoE(nn.Module):
             inv_perm[perm.long()] = torch.arange(perm.numel(), dtype=torch.int32, device=perm.device)
             recv_counts = exchange_counts(plan.counts, self.group)  # [W, e_local]
             # one small device->host read per step: the split sizes NCCL needs on the host
-            host = torch.cat([plan.counts.view(W, e_local).sum(1), recv_counts.sum(1)]).tolist()
-            send_splits, recv_splits = host[:W], host[W:]
+            host = _host_words(torch.cat([plan.counts.view(W, e_local).sum(1), recv_counts.sum(1)]).to(torch.int32))
+            send_splits, recv_splits = host[:W].tolist(), host[W:].tolist()
             # local expert id of every received row: source-major, expert-minor
             local_ids = torch.repeat_interleave(
                 torch.arange(e_local, dtype=torch.int32, device=x.device).repeat(W), recv_counts.reshape(-1).long(),

@@ -327,8 +327,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--transport", choices=["peer", "nccl"], default="peer",
                     help="row exchange of the expert-parallel layer: stores into peer memory, or NCCL all-to-all")
-    ap.add_argument("--fused-return", action="store_true",
-                    help="peer transport: return rows from the GEMM epilogues instead of the row kernel")
+    ap.add_argument("--unfused-return", dest="fused_return", action="store_false",
+                    help="peer transport: return rows with a separate row kernel instead of the GEMM epilogues")
     ap.add_argument("--ep-chunks", type=int, default=None,
                     help="micro-batches per step in the expert-parallel layer (overlap of all-to-all and GEMM)")
     args = ap.parse_args()

@@ -153,8 +153,10 @@ int xma_b200_grouped_gemm_rows(const void* a, int64_t a_row_stride, const void* 
  * epilogue and row_map required; row_map[r] = (rank << 24) | row (negative: skipped) and the row is
  * stored to out_peers[rank] + row * out_row_stride, where out_peers is a device table of one base
  * address per rank (this rank's own buffer included; the others mapped with xma_b200_exchange_open).
- * out_peers NULL: identical to xma_b200_grouped_gemm_rows. No counterpart in the reference, whose MoE
- * keeps all experts on one device (xma/layers/moe/__init__.py:144-160). */
+ * The tensor-core kernel (one CTA per tile; impl 3 is not available here) stages the tile in shared
+ * memory so that every row crosses NVLink in 128-byte pieces. out_peers NULL: identical to
+ * xma_b200_grouped_gemm_rows. No counterpart in the reference, whose MoE keeps all experts on one
+ * device (xma/layers/moe/__init__.py:144-160). */
 int xma_b200_grouped_gemm_rows_peer(const void* a, int64_t a_row_stride, const void* w, int w_layout, void* out,
                                     int64_t out_row_stride, void* aux, int64_t aux_row_stride,
                                     const int32_t* row_map, void* const* out_peers, const int32_t* tile_expert,
@@ -227,8 +229,8 @@ int xma_b200_ep_copy_rows(const void* rows, int dtype, const int32_t* meta, int6
 int xma_b200_ep_publish(const int32_t* src, int64_t n, int32_t* host_words, cudaStream_t stream);
 
 /* Return: peer_rows[meta[r] >> 24][meta[r] & 0xffffff, :] = rows[r, :] for every r < n_rows with meta[r] >= 0
- * (expert output rows back to the token's home rank, whole rows per warp store). The same movement can be
- * fused into the GEMM (xma_b200_grouped_gemm_rows_peer), whose row-per-thread stores are slower over NVLink. */
+ * (expert output rows back to the token's home rank, whole rows per warp store): the unfused form of what
+ * xma_b200_grouped_gemm_rows_peer does in its epilogue. */
 int xma_b200_ep_return(const void* rows, int dtype, int64_t row_stride, const int32_t* meta, int64_t n_rows,
                        int64_t width, int world, void* const* peer_rows, int64_t peer_rows_cap, int* device_status,
                        cudaStream_t stream);
