@@ -98,9 +98,11 @@ __device__ __forceinline__ void issue_stage(uint32_t a_saddr, uint32_t b_saddr, 
 
 // ======================================================================================================
 // Rows GEMM: out[dst(r), :] = epilogue( A[r, :] * W_e ), r over the padded grouped rows.
-// Work order: expert-major, then column tile, then row tile inside the expert, so the CTAs of one
-// wave share weight tiles and the expert's activations stay in L2.
+// Work order: expert-major; inside an expert groups of ROWS_RASTER_GROUP row tiles x all column tiles
+// (raster_tile), so the CTAs of one wave share both a few row blocks and a few weight tiles.
 // ======================================================================================================
+constexpr int ROWS_RASTER_GROUP = 16;  // 148 CTAs: about 16 row tiles x 9 column tiles per wave
+
 struct RowsWork {
     int m_tile, n_tile, e;
 };
@@ -117,8 +119,9 @@ __device__ __forceinline__ RowsWork decode_rows(const int* tile_prefix, int E, i
     r.e = lo;
     const int64_t local = w - static_cast<int64_t>(tile_prefix[lo]) * n_tiles;
     const int mt = tile_prefix[lo + 1] - tile_prefix[lo];
-    r.n_tile = static_cast<int>(local / mt);
-    r.m_tile = tile_prefix[lo] + static_cast<int>(local % mt);
+    int m;
+    raster_tile(local, mt, n_tiles, ROWS_RASTER_GROUP, m, r.n_tile);
+    r.m_tile = tile_prefix[lo] + m;
     return r;
 }
 

@@ -193,13 +193,15 @@ struct PairWork {
     bool active;            // false: this CTA's half lies beyond the expert's rows
 };
 
+constexpr int PAIR_RASTER_GROUP = 8;
+
 __device__ __forceinline__ PairWork decode_pair(const Shared2& s, int E, int n_tiles, int64_t w, int rank) {
     PairWork r;
     r.e = find_expert(s.pair_prefix, E, n_tiles, w);
     const int64_t local = w - static_cast<int64_t>(s.pair_prefix[r.e]) * n_tiles;
     const int pt = s.pair_prefix[r.e + 1] - s.pair_prefix[r.e];
-    r.n_tile = static_cast<int>(local / pt);
-    const int pm = static_cast<int>(local % pt);
+    int pm;
+    raster_tile(local, pt, n_tiles, PAIR_RASTER_GROUP, pm, r.n_tile);  // 74 pairs: about 8 pair rows x 9 column tiles
     const int mt = s.tile_prefix[r.e + 1] - s.tile_prefix[r.e];
     r.m_tile = s.tile_prefix[r.e] + 2 * pm + rank;
     r.active = (2 * pm + rank) < mt;

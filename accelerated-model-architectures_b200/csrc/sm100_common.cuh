@@ -509,6 +509,37 @@ __device__ __forceinline__ bool rows_epilogue_tile(uint64_t* acc_full_bar, uint3
     return true;
 }
 
+// ---- order of the tiles inside one expert (rows GEMMs) ----------------------------------------------------
+// The `local`-th work item of an expert with `mt` row tiles (or row-tile pairs) and `nt` column tiles. Row
+// tiles are cut into balanced groups of at most `group`; inside a group the column tiles are swept with the
+// group's row tiles innermost. CTAs take consecutive items and run in step along the reduction, so one wave
+// reads about `group` row blocks and (CTAs / group) weight tiles once each from HBM and shares them through
+// L2. With the row tiles of a whole expert innermost instead, a wave shares a single weight tile and every
+// column tile streams the expert's rows again: for experts of 16384 rows that was 13.6 GB of DRAM reads in
+// the down projection of the 8-expert configuration against 1.2 GB of operands.
+__device__ __forceinline__ void raster_tile(int64_t local, int mt, int nt, int group, int& m, int& n) {
+    const int ng = (mt + group - 1) / group;
+    const int base = mt / ng, rem = mt - base * ng;  // the first `rem` groups hold base + 1 row tiles
+    const int64_t big = static_cast<int64_t>(base + 1) * nt;
+    int gl, m0;
+    int64_t j;
+    if (local < rem * big) {
+        const int g = static_cast<int>(local / big);
+        gl = base + 1;
+        m0 = g * (base + 1);
+        j = local - g * big;
+    } else {
+        const int64_t l2 = local - rem * big;
+        const int64_t per = static_cast<int64_t>(base) * nt;
+        const int g = static_cast<int>(l2 / per);
+        gl = base;
+        m0 = rem * (base + 1) + g * base;
+        j = l2 - g * per;
+    }
+    n = static_cast<int>(j / gl);
+    m = m0 + static_cast<int>(j % gl);
+}
+
 // ---- work decoding of the weight-gradient GEMM ----------------------------------------------------------
 // Expert-major, then groups of DW_GROUP_M row tiles x all column tiles (row tile fastest).
 constexpr int DW_GROUP_M = 8;

@@ -314,6 +314,104 @@ def run_routing_microbench(args) -> None:
     }), flush=True)
 
 
+def run_ep_microbench(args) -> None:
+    """Kernels of the expert-parallel peer transport on ONE GPU, with the shapes one rank of configs[1] sees
+    at 4 ranks (2 local experts, 32768 received rows of 4096 bf16, I = 14336): the "ranks" are buffers of
+    the same device addressed through the same pointer tables, so the figures are HBM figures (what the
+    kernels cost before NVLink enters) and the kernels can be captured by ncu, which a multi-rank run cannot."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    from xma import _lib, ops
+    from xma.layers.moe import build_route_plan
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks.get("hbm_gbs", PEAK_FALLBACK["hbm_gbs"]))
+    W, E, K, H, I, T = 4, 8, 2, 4096, 14336, 16384
+    el, R, dt = E // W, T * K, torch.bfloat16
+    steps, warm = max(args.steps, 1), max(args.warmup, 1)
+
+    def timed(fn) -> float:
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    sel = torch.stack([torch.randperm(E, generator=gen)[:K] for _ in range(T)]).to(torch.int32).to(device)
+    plan = build_route_plan(sel, E)
+    cm = plan.counts.view(1, E).repeat(W, 1).contiguous()  # every virtual rank routes like this one
+    host = cm.cpu().numpy().astype(np.int64)
+    padded = ((host.sum(0) + 127) // 128 * 128).reshape(W, el).sum(1)
+    cap, rows0 = int(padded.max()) + el * 128, int(padded[0])
+    recv = [torch.zeros(cap, H, dtype=dt, device=device) for _ in range(W)]
+    meta = [torch.full((cap,), -1, dtype=torch.int32, device=device) for _ in range(W)]
+    home = [torch.empty(R, H, dtype=dt, device=device) for _ in range(W)]
+    table = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=device)
+    recv_table, meta_table, home_table = table(recv), table(meta), table(home)
+    x = torch.randn(T, H, device=device, dtype=dt)
+
+    def plan_rank(r: int):
+        t = dict(send_delta=torch.empty(E, dtype=torch.int32, device=device),
+                 counts=torch.empty(el, dtype=torch.int32, device=device),
+                 pad_offsets=torch.empty(el + 1, dtype=torch.int32, device=device),
+                 tile_prefix=torch.empty(el + 1, dtype=torch.int32, device=device),
+                 tile_expert=torch.empty(int(padded[r]) // 128 + el, dtype=torch.int32, device=device))
+        ops.ep_plan_(cm, r, t["send_delta"], t["counts"], t["pad_offsets"], t["tile_prefix"], t["tile_expert"], meta[r])
+        return t
+
+    tables = [plan_rank(r) for r in range(W)]
+    dispatch = lambda r: ops.ep_dispatch_(x, plan.sorted_expert_idxs, plan.sorted_scattered_idxs, None, K,
+                                          tables[r]["send_delta"], W, r, recv_table, meta_table, cap)
+    for r in range(1, W):
+        dispatch(r)
+    out = {}
+    row_bytes = H * 2
+    ms = timed(lambda: plan_rank(0))
+    out["ep_plan"] = {"ms": ms}
+    ms = timed(lambda: dispatch(0))
+    moved = R * (2 * row_bytes + 12)
+    out["ep_dispatch"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / ms / 1e6 / hbm, "bytes": moved}
+    t0 = tables[0]
+    alloc = t0["tile_expert"].numel() * 128
+    xs = torch.empty(alloc, H, dtype=dt, device=device)
+    ms = timed(lambda: ops.ep_copy_rows_(recv[0], meta[0], xs[:rows0]))
+    moved = rows0 * (2 * row_bytes + 4)
+    out["ep_copy_rows"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / ms / 1e6 / hbm, "bytes": moved}
+    ms = timed(lambda: ops.ep_return_(xs[:rows0], meta[0], W, home_table, R))
+    out["ep_return"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / ms / 1e6 / hbm, "bytes": moved}
+
+    act = torch.randn(alloc, I, device=device, dtype=dt)
+    w2 = torch.randn(el, H, I, device=device, dtype=dt) * 0.02
+    ys = torch.empty(alloc, H, dtype=dt, device=device)
+    flops = 2.0 * rows0 * I * H
+    ms = timed(lambda: ops.grouped_gemm_rows_(act, w2, _lib.W_NK, ys, None, None, t0["tile_expert"], t0["tile_prefix"],
+                                              I, H, _lib.EPI_PLAIN, 0))
+    out["gemm_down_plain"] = {"ms": ms, "tflops": flops / ms / 1e9}
+    ms = timed(lambda: ops.grouped_gemm_rows_(act, w2, _lib.W_NK, home[0], None, meta[0], t0["tile_expert"],
+                                              t0["tile_prefix"], I, H, _lib.EPI_PLAIN, 0, home_table))
+    out["gemm_down_rows_to_ranks"] = {"ms": ms, "tflops": flops / ms / 1e9}
+    _lib.raise_on_device_status(device)
+    best = out["ep_dispatch"]
+    print(json.dumps({
+        "metric": "ep_row_exchange_hbm_gb_per_s", "value": best["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
+        "warmup": warm, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"ep: peer-transport kernels of configs[1] at {W} ranks, ranks emulated as buffers of one GPU",
+                   "l2_policy": "inputs_exceed_l2"},
+        "roofline": {"bound": "hbm", "kernel": "ep_dispatch_kernel", "achieved": best["gbs"], "peak": hbm,
+                     "unit": "GB/s", "frac": best["frac"], "peak_source": f"{peak_kind} copy bandwidth", "traffic": None},
+        "kernels": out,
+    }), flush=True)
+
+
 # ---------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
@@ -322,7 +420,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "ep"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--transport", choices=["peer", "nccl"], default="peer",
@@ -334,6 +432,9 @@ def main() -> None:
     args = ap.parse_args()
     if args.workload == "c5":
         run_routing_microbench(args)
+        return
+    if args.workload == "ep":
+        run_ep_microbench(args)
         return
     w = WORKLOADS[args.workload]
 
