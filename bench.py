@@ -627,7 +627,10 @@ def main() -> None:
     }
     # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures of the
     # 2-expert slice `c2e2` summarised in profiles/ncu_grouped_gemm_tcgen05_c2e2.md; traffic grows in
-    # proportion to the number of experts at fixed rows per expert, so configs[1] moves experts/2 times this.
+    # proportion to the number of experts at fixed rows per expert, so configs[1] moves experts/2 times this
+    # on one GPU (expert-parallel ranks see other rows per expert: no figure there). The dominant kernel is the
+    # weight-gradient GEMM; the four rows-GEMM entries were captured with the older tile order (an expert's row
+    # tiles innermost) and are upper bounds for the grouped order.
     ncu_traffic_c2e2 = {"gemm_up_swiglu": 1.435e9, "gemm_down": 1.279e9, "gemm_dact_dswiglu": 1.784e9,
                         "gemm_dx": 2.500e9, "gemm_dw1": 1.524e9, "gemm_dw2": 0.782e9}
     peak = float(peaks.get("bf16_tflops_sustained", PEAK_FALLBACK["bf16_tflops_sustained"]))
@@ -647,8 +650,8 @@ def main() -> None:
         fn = max(groups, key=lambda k: groups[k]["ms_total"])
         g = groups[fn]
         traffic = None
-        if args.workload in ("c2", "c2e2") and all(t in ncu_traffic_c2e2 for t in g["tags"]):
-            scale = (E // world) / 2.0
+        if world == 1 and args.workload in ("c2", "c2e2") and all(t in ncu_traffic_c2e2 for t in g["tags"]):
+            scale = E / 2.0
             traffic = scale * sum(ncu_traffic_c2e2[t] for t in g["tags"]) / len(g["tags"])
         roofline = {
             "bound": "tensor", "kernel": fn, "achieved": g["tflops"], "peak": peak, "unit": "TFLOP/s",
