@@ -53,6 +53,43 @@ def test_host_side_argument_errors_need_no_gpu():
     assert "dtype" in _lib.error_string(-2)
 
 
+def test_expert_parallel_entry_points_reject_bad_arguments_without_a_gpu():
+    from xma._lib import lib
+
+    NULL, DTYPE, SHAPE, LARGE = -1, -2, -3, -8  # status codes of the C ABI
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    out = ctypes.c_void_p()
+    # ep_plan: null tables, experts not divisible by the ranks, rank outside the world
+    assert lib.xma_b200_ep_plan(None, 2, 8, 0, p, p, p, p, p, 4, p, 512, None, None) == NULL
+    assert lib.xma_b200_ep_plan(p, 3, 8, 0, p, p, p, p, p, 4, p, 512, None, None) == SHAPE
+    assert lib.xma_b200_ep_plan(p, 2, 8, 2, p, p, p, p, p, 4, p, 512, None, None) == SHAPE
+    # ep_dispatch: nothing to move is fine, null source is not, more rows than an origin word addresses is too large
+    args = lambda src, rows: (src, 2, 64, p, p, None, 2, p, 8, 2, 0, rows, 64, p, p, 1 << 20, None, None)
+    assert lib.xma_b200_ep_dispatch(*args(None, 0)) == 0
+    assert lib.xma_b200_ep_dispatch(*args(None, 16)) == NULL
+    assert lib.xma_b200_ep_dispatch(*args(p, (1 << 24) + 1)) == LARGE
+    assert lib.xma_b200_ep_dispatch(p, 9, 64, p, p, None, 2, p, 8, 2, 0, 16, 64, p, p, 1 << 20, None, None) == DTYPE
+    # ep_copy_rows / ep_return / ep_publish
+    assert lib.xma_b200_ep_copy_rows(p, 2, None, 16, 64, p, None) == NULL
+    assert lib.xma_b200_ep_copy_rows(p, 2, p, 16, 0, p, None) == SHAPE
+    assert lib.xma_b200_ep_return(p, 2, 64, p, 16, 64, 0, p, 128, None, None) == SHAPE
+    assert lib.xma_b200_ep_return(p, 2, 64, p, 0, 64, 2, p, 128, None, None) == 0
+    assert lib.xma_b200_ep_publish(p, 4, None, None) == NULL
+    # a row map is required (and only the plain epilogue allowed) when rows go to other ranks' buffers
+    gemm = lambda row_map, epilogue: lib.xma_b200_grouped_gemm_rows_peer(
+        p, 64, p, 0, p, 64, None, 0, row_map, p, p, p, 2, 4, 64, 64, epilogue, 2, 0, None, None)
+    assert gemm(None, 0) == SHAPE
+    assert gemm(p, 1) == SHAPE
+    # exchange buffers
+    assert lib.xma_b200_exchange_alloc(0, ctypes.byref(out)) == SHAPE
+    assert lib.xma_b200_exchange_alloc(1024, None) == NULL
+    assert lib.xma_b200_exchange_export(None, buf) == NULL
+    assert lib.xma_b200_exchange_open(None, ctypes.byref(out)) == NULL
+    assert lib.xma_b200_exchange_free(None) == 0 and lib.xma_b200_exchange_close(None) == 0
+    assert lib.xma_b200_exchange_handle_bytes() == 64
+
+
 def test_kernel_backend_contract():
     import xma
     from xma.accelerator import resolve_kernel_backend
