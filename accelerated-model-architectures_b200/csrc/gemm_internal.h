@@ -39,6 +39,8 @@ struct RowsGemmArgs {
     void* const* out_peers;    // null, or (plain epilogue with a row_map only) a device table of output
                                // bases, one per rank: row_map[r] = (rank << 24) | row, and the row is
                                // stored to out_peers[rank] instead of `out` (peer memory over NVLink)
+    int peer_world;            // entries of out_peers; words naming a rank >= peer_world are skipped and flagged
+    int64_t peer_rows_cap;     // rows of every rank's buffer; words naming a row >= this are skipped and flagged
     const int* tile_expert;    // [tile_cap]
     const int* tile_prefix;    // [E+1], tile_prefix[E] = tiles in use
     int num_experts;
@@ -67,6 +69,23 @@ struct DwGemmArgs {
     int* device_status;
     cudaStream_t stream;
 };
+
+// Process-wide tuning switches of the tensor-core kernels (xma_b200_tuning_set / XMA_B200_* environment
+// variables read once). Defaults are the measured best on B200.
+struct Tuning {
+    int gu_prefetch = 1;        // SwiGLU-backward epilogue: ask for the next tile's gate|up rows in L2
+    int tma_prefetch_dist = 0;  // reduction blocks the TMA producer prefetches into L2 ahead of its loads
+    int tma_prefetch_mask = 3;  // bit 0: A operand, bit 1: B operand
+    int epi_warps = 0;          // 4 or 8 epilogue warps; 0 = per-kernel default
+    int plain_pairs = 1;        // automatic choice: CTA pairs also for the plain epilogues of large experts
+};
+Tuning& tuning();
+uint32_t tune_word();  // the switches the kernels read, packed (see sm100_common.cuh)
+
+// Which kernel family the automatic choice (impl = 0) takes: 1 CUDA cores, 2 tcgen05 one CTA per tile,
+// 3 tcgen05 CTA pairs.
+int choose_rows_impl(const RowsGemmArgs& a);
+int choose_dw_impl(const struct DwGemmArgs& a);
 
 int rows_gemm_simt(const RowsGemmArgs& a);
 int dw_gemm_simt(const DwGemmArgs& a);

@@ -70,8 +70,9 @@ template <typename T>
 __global__ void __launch_bounds__(ST_THREADS)
 rows_gemm_simt_kernel(const T* __restrict__ a, int64_t a_stride, const T* __restrict__ w, int w_layout,
                       T* __restrict__ out, int64_t out_stride, const int* __restrict__ row_map,
-                      void* const* __restrict__ out_peers, const int* __restrict__ tile_expert, const int* __restrict__ tile_prefix, int E, int64_t kd,
-                      int64_t n) {
+                      void* const* __restrict__ out_peers, int peer_world, int64_t peer_rows_cap,
+                      const int* __restrict__ tile_expert, const int* __restrict__ tile_prefix, int E, int64_t kd,
+                      int64_t n, int* __restrict__ status) {
     const int tile = blockIdx.x >> 1;
     if (tile >= tile_prefix[E]) return;
     const int e = tile_expert[tile];
@@ -92,9 +93,14 @@ rows_gemm_simt_kernel(const T* __restrict__ a, int64_t a_stride, const T* __rest
         if (row_map) dst = row_map[r];
         if (dst < 0) continue;
         T* base = out;
-        if (out_peers) {  // (rank << 24) | row of that rank's buffer
-            base = static_cast<T*>(out_peers[dst >> PEER_ROW_BITS]);
+        if (out_peers) {  // (rank << 24) | row of that rank's buffer; words outside the table are skipped and flagged
+            const int64_t owner = dst >> PEER_ROW_BITS;
             dst &= PEER_ROW_MASK;
+            if (owner >= peer_world || dst >= peer_rows_cap) {
+                if (status && tx == 0) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
+                continue;
+            }
+            base = static_cast<T*>(out_peers[owner]);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -145,7 +151,8 @@ static int rows_gemm_simt_t(const RowsGemmArgs& g) {
     if (grid.y > 65535) return XMA_ERR_TOO_LARGE;
     rows_gemm_simt_kernel<T><<<grid, ST_THREADS, 0, g.stream>>>(
         static_cast<const T*>(g.a), g.a_stride, static_cast<const T*>(g.w), g.w_layout, raw, raw_stride, row_map,
-        out_peers, g.tile_expert, g.tile_prefix, g.num_experts, g.kd, g.n);
+        out_peers, g.peer_world, g.peer_rows_cap, g.tile_expert, g.tile_prefix, g.num_experts, g.kd, g.n,
+        g.device_status);
     XMA_CUDA_TRY(cudaGetLastError());
     const int64_t rows = g.tile_cap * XMA_ROW_PAD;
     if (g.epilogue == EPI_SWIGLU) {

@@ -15,6 +15,7 @@
 //                 and, with 8 warps, half of the tile's columns -> acc_empty[buf]
 // The accumulator is double buffered (2 x 256 columns), so the epilogue of a tile overlaps the
 // main loop of the next one. Every wait is bounded: on expiry the CTA raises a flag, sets the
+// wait-timeout bit of the device status word, leaves its loops and still frees its tensor memory.
 #include "sm100_common.cuh"
 
 namespace xma {
@@ -129,9 +130,9 @@ template <typename T, int WL, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     T* __restrict__ out, int64_t out_stride, T* __restrict__ aux, int64_t aux_stride,
-                    const int* __restrict__ row_map, void* const* __restrict__ out_peers,
-                    const int* __restrict__ g_tile_prefix, int E, int kd, int n, uint32_t idesc,
-                    int* __restrict__ status) {
+                    const int* __restrict__ row_map, void* const* __restrict__ out_peers, int peer_world,
+                    int64_t peer_rows_cap, const int* __restrict__ g_tile_prefix, int E, int kd, int n,
+                    uint32_t idesc, uint32_t tune, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const Shared s = carve_smem(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -218,10 +219,15 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const uint32_t buf = lt & 1u;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
-
+            if ((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) && (tune & TUNE_GU_PREFETCH) &&
+                w + gridDim.x < total) {
+                const RowsWork nx = decode_rows(s.tile_prefix, E, n_tiles, w + gridDim.x);
+                prefetch_gate_up<T, EPI>(aux, aux_stride, static_cast<int64_t>(nx.m_tile) * BM + row_in_tile,
+                                         nx.n_tile, n, part, chunks);
+            }
             if (!rows_epilogue_tile<T, EPI>(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag, taddr, r, true, wk.n_tile, n,
-                                            half_n, out, out_stride, aux, aux_stride, row_map, out_peers, peer_stage,
-                                            part, chunks))
+                                            half_n, out, out_stride, aux, aux_stride, row_map, out_peers, peer_world,
+                                            peer_rows_cap, status, peer_stage, part, chunks))
                 break;
             tc_fence_before();
             mbar_arrive(&s.acc_empty[buf]);
@@ -355,8 +361,7 @@ dw_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 template <typename K>
 static int set_smem(K kernel) {
     apply_epilogue_tuning();
-    return static_cast<int>(
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
+    return set_dynamic_smem_once(kernel, SMEM_BYTES);
 }
 
 template <typename T, int WL, int EPI>
@@ -368,8 +373,9 @@ static int launch_rows(const RowsGemmArgs& g, const CUtensorMap& ta, const CUten
     // (rows bound for other ranks are staged per epilogue warp: always four warps then)
     const int threads = (EPI == EPI_PLAIN_PEER) ? 64 + 32 * 4 : block_threads((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) ? 8 : 4);
     kernel<<<num_sms(), threads, SMEM_BYTES, g.stream>>>(
-        ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
-        g.out_peers, g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
+        ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map, g.out_peers,
+        g.peer_world, g.peer_rows_cap, g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n),
+        idesc, tune_word(), g.device_status);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -403,7 +409,9 @@ bool rows_gemm_tc_supported(const RowsGemmArgs& g) {
                        (g.w_layout == W_KN && (plain || g.epilogue == EPI_DSWIGLU ||
                                                g.epilogue == EPI_DSWIGLU_PACKED));
     if (!combo) return false;
-    if (g.epilogue == EPI_PLAIN_PEER && (!g.row_map || !g.out_peers)) return false;
+    if (g.epilogue == EPI_PLAIN_PEER &&
+        (!g.row_map || !g.out_peers || g.peer_world <= 0 || g.peer_world > PEER_MAX_RANKS || g.peer_rows_cap <= 0))
+        return false;
     if (!plain) {
         if (!g.aux || g.aux_stride % 8 || !is_aligned16(g.aux) || g.row_map) return false;
         if ((g.epilogue == EPI_SWIGLU || g.epilogue == EPI_SWIGLU_PACKED) && (g.n % 16)) return false;
@@ -419,12 +427,12 @@ int rows_gemm_tc(const RowsGemmArgs& g) {
     if (g.tile_cap == 0) return XMA_OK;
     CUtensorMap ta, tb;
     const uint64_t rows_cap = static_cast<uint64_t>(g.tile_cap) * XMA_ROW_PAD;
-    if (!tc::make_map(&ta, g.dtype, g.a, g.kd, rows_cap, g.a_stride, tc::BM)) return XMA_ERR_TENSOR_MAP;
+    if (!tc::cached_map(&ta, g.dtype, g.a, g.kd, rows_cap, g.a_stride, tc::BM)) return XMA_ERR_TENSOR_MAP;
     bool ok;
     if (g.w_layout == W_NK)
-        ok = tc::make_map(&tb, g.dtype, g.w, g.kd, static_cast<uint64_t>(g.num_experts) * g.n, g.kd, 128);
+        ok = tc::cached_map(&tb, g.dtype, g.w, g.kd, static_cast<uint64_t>(g.num_experts) * g.n, g.kd, 128);
     else
-        ok = tc::make_map(&tb, g.dtype, g.w, g.n, static_cast<uint64_t>(g.num_experts) * g.kd, g.n, 64);
+        ok = tc::cached_map(&tb, g.dtype, g.w, g.n, static_cast<uint64_t>(g.num_experts) * g.kd, g.n, 64);
     if (!ok) return XMA_ERR_TENSOR_MAP;
     if (g.dtype == XMA_BF16) return tc::rows_dispatch<__nv_bfloat16>(g, ta, tb);
     return tc::rows_dispatch<__half>(g, ta, tb);
@@ -443,8 +451,8 @@ int dw_gemm_tc(const DwGemmArgs& g) {
     if (!dw_gemm_tc_supported(g)) return XMA_ERR_UNSUPPORTED;
     if (g.num_experts == 0) return XMA_OK;
     CUtensorMap tx, ty;
-    if (!tc::make_map(&tx, g.dtype, g.x, g.m, g.rows_cap, g.x_stride, 64)) return XMA_ERR_TENSOR_MAP;
-    if (!tc::make_map(&ty, g.dtype, g.y, g.n, g.rows_cap, g.y_stride, 64)) return XMA_ERR_TENSOR_MAP;
+    if (!tc::cached_map(&tx, g.dtype, g.x, g.m, g.rows_cap, g.x_stride, 64)) return XMA_ERR_TENSOR_MAP;
+    if (!tc::cached_map(&ty, g.dtype, g.y, g.n, g.rows_cap, g.y_stride, 64)) return XMA_ERR_TENSOR_MAP;
     const uint32_t idesc = tc::make_idesc(g.dtype, true, true);
     if (g.dtype == XMA_BF16) {
         auto kernel = tc::dw_gemm_tc_kernel<__nv_bfloat16>;

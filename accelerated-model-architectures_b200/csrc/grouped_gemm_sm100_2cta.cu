@@ -25,7 +25,7 @@ constexpr int A2_BYTES = BM * BK * 2;         // 128 rows x 64: 16 KiB
 constexpr int B2_BYTES = (BN / 2) * BK * 2;   // this CTA's half of the B tile: 16 KiB
 constexpr int STAGE2_BYTES = A2_BYTES + B2_BYTES;
 constexpr size_t SMEM2_BYTES = 1024 + static_cast<size_t>(STAGES2) * STAGE2_BYTES +
-                               2 * (MAX_EXPERTS + 1) * sizeof(int) + 256;
+                               2 * (MAX_EXPERTS + 1) * sizeof(int) + 256 + PEER_STAGE_BYTES;
 
 // ---- cluster / pair PTX ---------------------------------------------------------------------------------
 
@@ -121,6 +121,7 @@ struct Shared2 {
     uint64_t* acc_empty;
     uint32_t* tmem_ptr;
     volatile int* abort_flag;
+    uint8_t* peer_stage;  // [PEER_STAGE_BYTES], 16-byte aligned
 };
 
 __device__ __forceinline__ Shared2 carve_smem2(uint8_t* raw) {
@@ -140,6 +141,8 @@ __device__ __forceinline__ Shared2 carve_smem2(uint8_t* raw) {
     s.acc_empty = s.acc_full + 2;
     s.tmem_ptr = reinterpret_cast<uint32_t*>(s.acc_empty + 2);
     s.abort_flag = reinterpret_cast<volatile int*>(s.tmem_ptr + 1);
+    s.peer_stage =
+        reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(s.tmem_ptr + 2) + 15) & ~static_cast<uintptr_t>(15));
     return s;
 }
 
@@ -215,9 +218,9 @@ template <typename T, int WL, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                      T* __restrict__ out, int64_t out_stride, T* __restrict__ aux, int64_t aux_stride,
-                     const int* __restrict__ row_map, void* const* __restrict__ out_peers,
-                     const int* __restrict__ g_tile_prefix, int E, int kd, int n, uint32_t idesc,
-                     int* __restrict__ status) {
+                     const int* __restrict__ row_map, void* const* __restrict__ out_peers, int peer_world,
+                     int64_t peer_rows_cap, const int* __restrict__ g_tile_prefix, int E, int kd, int n,
+                     uint32_t idesc, uint32_t tune, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const Shared2 s = carve_smem2(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -244,6 +247,50 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
+            // box coordinates of one reduction block; `load` = false only asks for the boxes in L2
+            auto boxes = [&](const PairWork& wk, int kb, bool load, uint8_t* sa, uint8_t* sb, uint32_t full0) {
+                const bool want_a = load || ((tune & TUNE_PREFETCH_A) && wk.active);
+                const bool want_b = load || (tune & TUNE_PREFETCH_B);
+                if (want_a) {
+                    if (load) tma_load_2d_pair(sa, &tm_a, full0, kb * BK, wk.m_tile * BM);
+                    else tma_prefetch_2d(&tm_a, kb * BK, wk.m_tile * BM);
+                }
+                if (!want_b) return;
+                if (!B_MN) {
+                    // weight stored [E * n, kd]: this CTA's 128 rows of the 256-row B tile
+                    int r0;
+                    if (EPI == EPI_SWIGLU) r0 = wk.e * n + wk.n_tile * 128 + rank * half_n;  // gate | up rows
+                    else r0 = wk.e * n + wk.n_tile * BN + rank * 128;
+                    if (load) tma_load_2d_pair(sb, &tm_b, full0, kb * BK, r0);
+                    else tma_prefetch_2d(&tm_b, kb * BK, r0);
+                } else {
+                    // weight stored [E * kd, n]: two boxes of 64 columns x 64 reduction rows
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int c0 = wk.n_tile * BN + rank * 128 + j * 64, c1 = wk.e * kd + kb * BK;
+                        if (load) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tm_b, full0, c0, c1);
+                        else tma_prefetch_2d(&tm_b, c0, c1);
+                    }
+                }
+            };
+            // L2 prefetch cursor: runs `ahead` reduction blocks in front of the loads, across tiles
+            const int ahead = static_cast<int>(tune_prefetch_distance(tune));
+            int64_t w_pf = pair;
+            int kb_pf = 0;
+            bool pf_on = ahead > 0 && w_pf < total;
+            PairWork wk_pf;
+            if (pf_on) wk_pf = decode_pair(s, E, n_tiles, w_pf, rank);
+            auto prefetch_step = [&]() {
+                if (!pf_on) return;
+                boxes(wk_pf, kb_pf, false, nullptr, nullptr, 0u);
+                if (++kb_pf == k_blocks) {
+                    kb_pf = 0;
+                    w_pf += num_pairs;
+                    pf_on = w_pf < total;
+                    if (pf_on) wk_pf = decode_pair(s, E, n_tiles, w_pf, rank);
+                }
+            };
+            for (int i = 0; i < ahead; ++i) prefetch_step();
             uint32_t it = 0;
             for (int64_t w = pair; w < total; w += num_pairs) {
                 const PairWork wk = decode_pair(s, E, n_tiles, w, rank);
@@ -253,23 +300,10 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     ok = mbar_wait(&s.empty[st], ((it / STAGES2) & 1u) ^ 1u, s.abort_flag);
                     if (!ok) break;
                     uint8_t* sa = s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES;
-                    uint8_t* sb = sa + A2_BYTES;
                     const uint32_t full0 = map_to_cta(smem_u32(&s.full[st]), 0);
                     if (rank == 0) mbar_expect_tx(&s.full[st], 2 * STAGE2_BYTES);
-                    tma_load_2d_pair(sa, &tm_a, full0, kb * BK, wk.m_tile * BM);
-                    if (!B_MN) {
-                        // weight stored [E * n, kd]: this CTA's 128 rows of the 256-row B tile
-                        int r0;
-                        if (EPI == EPI_SWIGLU) r0 = wk.e * n + wk.n_tile * 128 + rank * half_n;  // gate | up rows
-                        else r0 = wk.e * n + wk.n_tile * BN + rank * 128;
-                        tma_load_2d_pair(sb, &tm_b, full0, kb * BK, r0);
-                    } else {
-                        // weight stored [E * kd, n]: two boxes of 64 columns x 64 reduction rows
-#pragma unroll
-                        for (int j = 0; j < 2; ++j)
-                            tma_load_2d_pair(sb + j * CHUNK_BYTES, &tm_b, full0, wk.n_tile * BN + rank * 128 + j * 64,
-                                             wk.e * kd + kb * BK);
-                    }
+                    boxes(wk, kb, true, sa, sa + A2_BYTES, full0);
+                    prefetch_step();
                 }
                 if (!ok) break;
             }
@@ -302,15 +336,24 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         const int part = (warp - 2) >> 2;
         const int chunks = (BN / 32) / parts;
         const int row_in_tile = quarter * 32 + lane;
+        // one staging region per epilogue warp when there are four of them
+        uint8_t* peer_stage = (parts == 1) ? s.peer_stage + (warp - 2) * PEER_STAGE_WARP_BYTES : nullptr;
         uint32_t lt = 0;
         for (int64_t w = pair; w < total; w += num_pairs, ++lt) {
             const PairWork wk = decode_pair(s, E, n_tiles, w, rank);
             const uint32_t buf = lt & 1u;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
+            if ((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) && (tune & TUNE_GU_PREFETCH) &&
+                w + num_pairs < total) {
+                const PairWork nx = decode_pair(s, E, n_tiles, w + num_pairs, rank);
+                if (nx.active)
+                    prefetch_gate_up<T, EPI>(aux, aux_stride, static_cast<int64_t>(nx.m_tile) * BM + row_in_tile,
+                                             nx.n_tile, n, part, chunks);
+            }
             if (!rows_epilogue_tile<T, EPI>(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag, taddr, r, wk.active,
                                             wk.n_tile, n, half_n, out, out_stride, aux, aux_stride, row_map, out_peers,
-                                            nullptr, part, chunks))
+                                            peer_world, peer_rows_cap, status, peer_stage, part, chunks))
                 break;
             tc_fence_before();
             __syncwarp();
@@ -328,7 +371,7 @@ template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                    const uint32_t* __restrict__ counts, const int* __restrict__ pad_offsets, int E, int m, int n,
-                   T* __restrict__ dw, uint32_t idesc, int* __restrict__ status) {
+                   T* __restrict__ dw, uint32_t idesc, uint32_t tune, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const Shared2 s = carve_smem2(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -342,6 +385,46 @@ dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
     if (warp == 0) {
         if (lane == 0) {
+            auto boxes = [&](const DwWork& wk, int row, bool load, uint8_t* sa, uint8_t* sb, uint32_t full0) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int c0 = wk.m_tile * 2 * BM + rank * BM + j * 64;
+                    if (load) tma_load_2d_pair(sa + j * CHUNK_BYTES, &tm_x, full0, c0, row);
+                    else if (tune & TUNE_PREFETCH_A) tma_prefetch_2d(&tm_x, c0, row);
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int c0 = wk.n_tile * BN + rank * 128 + j * 64;
+                    if (load) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tm_y, full0, c0, row);
+                    else if (tune & TUNE_PREFETCH_B) tma_prefetch_2d(&tm_y, c0, row);
+                }
+            };
+            // L2 prefetch cursor, `ahead` reduction blocks in front of the loads (experts without rows have none)
+            const int ahead = static_cast<int>(tune_prefetch_distance(tune));
+            int64_t w_pf = pair;
+            int kb_pf = 0, kbs_pf = 0, row_pf = 0;
+            DwWork wk_pf;
+            bool pf_on = ahead > 0;
+            auto pf_seek = [&]() {  // first work item at or after w_pf that has reduction blocks
+                for (; w_pf < total; w_pf += num_pairs) {
+                    wk_pf = decode_dw(w_pf, m_tiles, n_tiles);
+                    kbs_pf = (static_cast<int>(counts[wk_pf.e]) + BK - 1) / BK;
+                    if (kbs_pf > 0) break;
+                }
+                pf_on = w_pf < total;
+                if (pf_on) row_pf = pad_offsets[wk_pf.e];
+                kb_pf = 0;
+            };
+            if (pf_on) pf_seek();
+            auto prefetch_step = [&]() {
+                if (!pf_on) return;
+                boxes(wk_pf, row_pf + kb_pf * BK, false, nullptr, nullptr, 0u);
+                if (++kb_pf == kbs_pf) {
+                    w_pf += num_pairs;
+                    pf_seek();
+                }
+            };
+            for (int i = 0; i < ahead; ++i) prefetch_step();
             uint32_t it = 0;
             for (int64_t w = pair; w < total; w += num_pairs) {
                 const DwWork wk = decode_dw(w, m_tiles, n_tiles);
@@ -353,17 +436,10 @@ dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     ok = mbar_wait(&s.empty[st], ((it / STAGES2) & 1u) ^ 1u, s.abort_flag);
                     if (!ok) break;
                     uint8_t* sa = s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES;
-                    uint8_t* sb = sa + A2_BYTES;
                     const uint32_t full0 = map_to_cta(smem_u32(&s.full[st]), 0);
                     if (rank == 0) mbar_expect_tx(&s.full[st], 2 * STAGE2_BYTES);
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-                        tma_load_2d_pair(sa + j * CHUNK_BYTES, &tm_x, full0, wk.m_tile * 2 * BM + rank * BM + j * 64,
-                                         row0 + kb * BK);
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-                        tma_load_2d_pair(sb + j * CHUNK_BYTES, &tm_y, full0, wk.n_tile * BN + rank * 128 + j * 64,
-                                         row0 + kb * BK);
+                    boxes(wk, row0 + kb * BK, true, sa, sa + A2_BYTES, full0);
+                    prefetch_step();
                 }
                 if (!ok) break;
             }
@@ -449,8 +525,7 @@ static int pair_grid() { return num_sms() & ~1; }
 template <typename K>
 static int set_smem2(K kernel) {
     apply_epilogue_tuning();
-    return static_cast<int>(
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM2_BYTES)));
+    return set_dynamic_smem_once(kernel, SMEM2_BYTES);
 }
 
 template <typename T, int WL, int EPI>
@@ -459,9 +534,14 @@ static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUte
     int rc = set_smem2(kernel);
     if (rc) return rc;
     const uint32_t idesc = make_idesc_mn(g.dtype, false, WL == W_KN, 2 * BM, BN);
-    kernel<<<pair_grid(), block_threads((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) ? 8 : 4), SMEM2_BYTES, g.stream>>>(
-        ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
-        g.out_peers, g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n), idesc, g.device_status);
+    // (rows bound for other ranks are staged per epilogue warp: always four warps then)
+    const int threads = (EPI == EPI_PLAIN_PEER)
+                            ? 64 + 32 * 4
+                            : block_threads((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) ? 8 : 4);
+    kernel<<<pair_grid(), threads, SMEM2_BYTES, g.stream>>>(
+        ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map, g.out_peers,
+        g.peer_world, g.peer_rows_cap, g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n),
+        idesc, tune_word(), g.device_status);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -475,6 +555,8 @@ static int rows_dispatch2(const RowsGemmArgs& g, const CUtensorMap& ta, const CU
     XMA_ROWS2_CASE(W_KN, EPI_DSWIGLU);
     XMA_ROWS2_CASE(W_NK, EPI_SWIGLU_PACKED);
     XMA_ROWS2_CASE(W_KN, EPI_DSWIGLU_PACKED);
+    XMA_ROWS2_CASE(W_NK, EPI_PLAIN_PEER);
+    XMA_ROWS2_CASE(W_KN, EPI_PLAIN_PEER);
 #undef XMA_ROWS2_CASE
     return XMA_ERR_UNSUPPORTED;
 }
@@ -487,7 +569,7 @@ static int launch_dw2(const DwGemmArgs& g, const CUtensorMap& tx, const CUtensor
     const uint32_t idesc = make_idesc_mn(g.dtype, true, true, 2 * BM, BN);
     kernel<<<pair_grid(), block_threads(4), SMEM2_BYTES, g.stream>>>(
         tx, ty, g.counts, g.pad_offsets, g.num_experts, static_cast<int>(g.m), static_cast<int>(g.n),
-        static_cast<T*>(g.dw), idesc, g.device_status);
+        static_cast<T*>(g.dw), idesc, tune_word(), g.device_status);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -498,12 +580,12 @@ int rows_gemm_tc2(const RowsGemmArgs& g) {
     if (g.tile_cap == 0) return XMA_OK;
     CUtensorMap ta, tb;
     const uint64_t rows_cap = static_cast<uint64_t>(g.tile_cap) * XMA_ROW_PAD;
-    if (!tc::make_map(&ta, g.dtype, g.a, g.kd, rows_cap, g.a_stride, tc::BM)) return XMA_ERR_TENSOR_MAP;
+    if (!tc::cached_map(&ta, g.dtype, g.a, g.kd, rows_cap, g.a_stride, tc::BM)) return XMA_ERR_TENSOR_MAP;
     bool ok;
     if (g.w_layout == W_NK)
-        ok = tc::make_map(&tb, g.dtype, g.w, g.kd, static_cast<uint64_t>(g.num_experts) * g.n, g.kd, 128);
+        ok = tc::cached_map(&tb, g.dtype, g.w, g.kd, static_cast<uint64_t>(g.num_experts) * g.n, g.kd, 128);
     else
-        ok = tc::make_map(&tb, g.dtype, g.w, g.n, static_cast<uint64_t>(g.num_experts) * g.kd, g.n, 64);
+        ok = tc::cached_map(&tb, g.dtype, g.w, g.n, static_cast<uint64_t>(g.num_experts) * g.kd, g.n, 64);
     if (!ok) return XMA_ERR_TENSOR_MAP;
     if (g.dtype == XMA_BF16) return tc2::rows_dispatch2<__nv_bfloat16>(g, ta, tb);
     return tc2::rows_dispatch2<__half>(g, ta, tb);
@@ -513,8 +595,8 @@ int dw_gemm_tc2(const DwGemmArgs& g) {
     if (!dw_gemm_tc_supported(g)) return XMA_ERR_UNSUPPORTED;
     if (g.num_experts == 0) return XMA_OK;
     CUtensorMap tx, ty;
-    if (!tc::make_map(&tx, g.dtype, g.x, g.m, g.rows_cap, g.x_stride, 64)) return XMA_ERR_TENSOR_MAP;
-    if (!tc::make_map(&ty, g.dtype, g.y, g.n, g.rows_cap, g.y_stride, 64)) return XMA_ERR_TENSOR_MAP;
+    if (!tc::cached_map(&tx, g.dtype, g.x, g.m, g.rows_cap, g.x_stride, 64)) return XMA_ERR_TENSOR_MAP;
+    if (!tc::cached_map(&ty, g.dtype, g.y, g.n, g.rows_cap, g.y_stride, 64)) return XMA_ERR_TENSOR_MAP;
     if (g.dtype == XMA_BF16) return tc2::launch_dw2<__nv_bfloat16>(g, tx, ty);
     return tc2::launch_dw2<__half>(g, tx, ty);
 }

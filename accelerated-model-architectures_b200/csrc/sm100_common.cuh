@@ -127,6 +127,19 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// Asks the TMA unit to bring one box of the tensor into L2 (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+                 :
+                 : "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+// One 128-byte line into L2.
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
                  "r"(cols)
@@ -267,8 +280,9 @@ __device__ __forceinline__ bool rows_epilogue_tile(uint64_t* acc_full_bar, uint3
                                                    int half_n, T* __restrict__ out, int64_t out_stride,
                                                    T* __restrict__ aux, int64_t aux_stride,
                                                    const int* __restrict__ row_map,
-                                                   void* const* __restrict__ out_peers, uint8_t* peer_stage,
-                                                   int part, int chunks) {
+                                                   void* const* __restrict__ out_peers, int peer_world,
+                                                   int64_t peer_rows_cap, int* __restrict__ status,
+                                                   uint8_t* peer_stage, int part, int chunks) {
     if (!active) return mbar_wait_epilogue(acc_full_bar, parity, abort_flag);
     if (EPI == EPI_PLAIN) {
         int64_t dst = r;
@@ -298,10 +312,19 @@ __device__ __forceinline__ bool rows_epilogue_tile(uint64_t* acc_full_bar, uint3
         // instruction, which NVLink moves poorly. Two chunks (64 columns) are staged in shared memory
         // (16-byte pieces XOR-swizzled by row: conflict-free both ways) and stored 4 rows x 128 contiguous
         // bytes at a time; the row addresses travel between lanes by shuffle.
+        // A word that names a rank outside the table or a row outside that rank's buffer is treated like a
+        // negative one (nothing is stored) and raises status bit 1: a stale or corrupt word must not
+        // become a store into another GPU's memory.
         int64_t dst = row_map[r];
         if (dst >= 0) {
-            out = static_cast<T*>(out_peers[dst >> PEER_ROW_BITS]);
+            const int64_t owner = dst >> PEER_ROW_BITS;
             dst &= PEER_ROW_MASK;
+            if (owner >= peer_world || dst >= peer_rows_cap) {
+                if (status) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
+                dst = -1;
+            } else {
+                out = static_cast<T*>(out_peers[owner]);
+            }
         }
         const int n0 = n_tile * BN;
         if (!mbar_wait_epilogue(acc_full_bar, parity, abort_flag)) return false;
@@ -509,6 +532,31 @@ __device__ __forceinline__ bool rows_epilogue_tile(uint64_t* acc_full_bar, uint3
     return true;
 }
 
+// The SwiGLU-backward epilogues read the gate|up rows of their tile from global memory; those rows are not
+// in L2 (the buffer is gigabytes and was written a whole GEMM earlier). Called by every epilogue thread for
+// the tile AFTER the one whose accumulator it is about to wait for, this asks for the lines that the thread
+// will read then, so that they arrive while the tensor cores are still working on that tile.
+template <typename T, int EPI>
+__device__ __forceinline__ void prefetch_gate_up(const T* __restrict__ aux, int64_t aux_stride, int64_t r, int n_tile,
+                                                 int n, int part, int chunks) {
+    if (EPI != EPI_DSWIGLU && EPI != EPI_DSWIGLU_PACKED) return;
+    const int col0 = n_tile * BN + part * chunks * 32;
+    if (col0 >= n) return;
+    const int cols = min(chunks * 32, n - col0);
+    const char* row = reinterpret_cast<const char*>(aux + r * aux_stride);
+    if (EPI == EPI_DSWIGLU) {
+        const char* g = row + static_cast<int64_t>(col0) * sizeof(T);
+        const char* u = g + static_cast<int64_t>(n) * sizeof(T);
+        for (int off = 0; off < cols * static_cast<int>(sizeof(T)); off += 128) {
+            prefetch_l2(g + off);
+            prefetch_l2(u + off);
+        }
+    } else {
+        const char* g = row + static_cast<int64_t>(2 * col0) * sizeof(T);
+        for (int off = 0; off < 2 * cols * static_cast<int>(sizeof(T)); off += 128) prefetch_l2(g + off);
+    }
+}
+
 // ---- order of the tiles inside one expert (rows GEMMs) ----------------------------------------------------
 // The `local`-th work item of an expert with `mt` row tiles (or row-tile pairs) and `nt` column tiles. Row
 // tiles are cut into balanced groups of at most `group`; inside a group the column tiles are swept with the
@@ -608,21 +656,90 @@ inline bool make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inn
     return true;
 }
 
+// Whether the CURRENT device is an sm_100 part (answer cached per device ordinal).
 inline bool device_is_sm100() {
-    static int cached = -1;
-    if (cached < 0) {
-        int dev = 0, major = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return false;
-        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
-        cached = (major == 10) ? 1 : 0;
-    }
-    return cached == 1;
+    static signed char cached[64] = {0};  // 0 = unknown, 1 = yes, -1 = no
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    const bool slot = dev >= 0 && dev < 64;
+    if (slot && cached[dev] != 0) return cached[dev] > 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
+    if (slot) cached[dev] = (major == 10) ? 1 : -1;
+    return major == 10;
 }
 
-// Epilogue warps per kernel: 4 (block of 192 threads) or 8 (320). XMA_B200_EPI_WARPS=4|8 overrides
-// the per-kernel default (tuning knob).
-// Copies the tuning switches from the environment into this translation unit's device variables (once;
-// every translation unit that includes this header has its own copy of them).
+// ---- tuning switches (one set per process, defined in gemm_api.cu) ---------------------------------------
+// Packed into one kernel argument: bit 0 = the SwiGLU-backward epilogue asks for the next tile's gate|up
+// rows in L2 while it waits for the accumulator; bits [8,16) = how many reduction blocks ahead of its loads
+// the TMA producer issues L2 prefetches (0 = none); bit 16 / 17 = prefetch the A / B operand.
+constexpr uint32_t TUNE_GU_PREFETCH = 1u;
+__host__ __device__ inline uint32_t tune_prefetch_distance(uint32_t t) { return (t >> 8) & 0xffu; }
+constexpr uint32_t TUNE_PREFETCH_A = 1u << 16;
+constexpr uint32_t TUNE_PREFETCH_B = 1u << 17;
+
+// Tensor-map cache: encoding a map is a driver call per operand per launch; the same (address, shape) pairs
+// come back every step, so the last encodings are kept (mutex-guarded, a few dozen entries, oldest replaced).
+inline bool cached_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_elems, uint32_t box_outer) {
+    struct Key {
+        const void* base;
+        uint64_t inner, outer, stride;
+        uint32_t box;
+        int dtype;
+        bool operator==(const Key& o) const {
+            return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride && box == o.box &&
+                   dtype == o.dtype;
+        }
+    };
+    struct Entry {
+        Key key;
+        CUtensorMap map;
+        bool used;
+    };
+    constexpr int N = 64;
+    static Entry entries[N];
+    static int next = 0;
+    static std::mutex mu;
+    const Key key{base, inner, outer, row_stride_elems, box_outer, dtype};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < N; ++i)
+            if (entries[i].used && entries[i].key == key) {
+                *map = entries[i].map;
+                return true;
+            }
+    }
+    if (!make_map(map, dtype, base, inner, outer, row_stride_elems, box_outer)) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    entries[next] = Entry{key, *map, true};
+    next = (next + 1) % N;
+    return true;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: set it on the first launch
+// of each kernel on each device only.
+template <typename K>
+inline int set_dynamic_smem_once(K kernel, size_t bytes) {
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+    const bool slot = dev >= 0 && dev < 64;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (slot && done[dev]) return 0;
+    }
+    const int rc = static_cast<int>(
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+    if (rc == 0 && slot) {
+        std::lock_guard<std::mutex> lock(mu);
+        done[dev] = true;
+    }
+    return rc;
+}
+
+// Copies the epilogue-wait switch from the environment into this translation unit's device variable (once;
+// every translation unit that includes this header has its own copy of it).
 static inline void apply_epilogue_tuning() {
     static bool done = false;
     if (done) return;
@@ -634,13 +751,11 @@ static inline void apply_epilogue_tuning() {
     }
 }
 
+// Threads per CTA: two control warps + 4 or 8 epilogue warps (per-kernel default unless the tuning switch
+// forces one).
 inline int block_threads(int default_epi_warps) {
-    static int forced = -1;
-    if (forced < 0) {
-        const char* e = getenv("XMA_B200_EPI_WARPS");
-        forced = (e && (e[0] == '4' || e[0] == '8')) ? (e[0] - '0') : 0;
-    }
-    const int warps = forced ? forced : default_epi_warps;
+    const int forced = tuning().epi_warps;
+    const int warps = (forced == 4 || forced == 8) ? forced : default_epi_warps;
     return 64 + 32 * warps;
 }
 

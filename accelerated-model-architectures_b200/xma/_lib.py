@@ -21,6 +21,8 @@ EPI_PLAIN, EPI_SWIGLU, EPI_DSWIGLU, EPI_SWIGLU_PACKED, EPI_DSWIGLU_PACKED = 0, 1
 IMPL_AUTO, IMPL_SIMT, IMPL_TC, IMPL_TC_PAIR = 0, 1, 2, 3
 
 DEV_ID_OUT_OF_RANGE, DEV_WAIT_TIMEOUT, DEV_BAD_TILE = 1, 2, 4
+ABI_VERSION = 2
+TUNE_GU_PREFETCH, TUNE_TMA_PREFETCH, TUNE_TMA_PREFETCH_MASK, TUNE_EPI_WARPS, TUNE_PLAIN_PAIRS = 0, 1, 2, 3, 4
 
 _DTYPE_CODES = {
     torch.float32: F32,
@@ -56,11 +58,13 @@ _SIGNATURES = {
                                    c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int,
                                    c_int, c_void_p, c_void_p],
     "xma_b200_grouped_gemm_rows_peer": [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64,
-                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
-                                        c_int, c_int, c_int, c_void_p, c_void_p],
+                                        c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int64,
+                                        c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p],
     "xma_b200_grouped_gemm_dw": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int64,
                                  c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "xma_b200_grouped_gemm_uses_tensor_cores": [c_int, c_int64, c_int64],
+    "xma_b200_grouped_gemm_choice": [c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int],
+    "xma_b200_tuning_set": [c_int, c_int],
     "xma_b200_swiglu_fwd": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                             c_void_p],
     "xma_b200_swiglu_bwd": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
@@ -102,6 +106,11 @@ def _load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError if the library does not export a declared symbol
         fn.argtypes = argtypes
         fn.restype = _RESTYPES.get(name, c_int)
+    if lib.xma_b200_abi_version() != ABI_VERSION:
+        raise ImportError(
+            f"{_LIB_PATH} has ABI version {lib.xma_b200_abi_version()}, this package binds version {ABI_VERSION}: "
+            "rebuild it with `python accelerated-model-architectures_b200/build.py --force`"
+        )
     return lib
 
 

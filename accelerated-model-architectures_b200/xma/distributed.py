@@ -342,7 +342,8 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
                                EPI_SWIGLU, impl, tag="gemm_up_swiglu")
         if exchange.fused_return:
             ops.grouped_gemm_rows_(act, w2, W_NK, exchange.home_rows, None, meta, route.tile_expert,
-                                   route.tile_prefix, I, H, EPI_PLAIN, impl, exchange.home_table, tag="gemm_down")
+                                   route.tile_prefix, I, H, EPI_PLAIN, impl, exchange.home_table, exchange.home_cap,
+                                   tag="gemm_down")
         else:
             out = torch.empty(alloc, H, **opts)
             ops.grouped_gemm_rows_(act, w2, W_NK, out, None, None, route.tile_expert, route.tile_prefix, I, H,
@@ -398,7 +399,8 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
         # dX rows straight back to the token's home rank
         if exchange.fused_return:
             ops.grouped_gemm_rows_(dgu, w1, W_KN, exchange.home_rows, None, meta, route.tile_expert,
-                                   route.tile_prefix, two_i, H, EPI_PLAIN, impl, exchange.home_table, tag="gemm_dx")
+                                   route.tile_prefix, two_i, H, EPI_PLAIN, impl, exchange.home_table,
+                                   exchange.home_cap, tag="gemm_dx")
         else:
             dxs = torch.empty(alloc, H, **opts)
             ops.grouped_gemm_rows_(dgu, w1, W_KN, dxs, None, None, route.tile_expert, route.tile_prefix, two_i, H,

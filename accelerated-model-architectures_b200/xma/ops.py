@@ -154,16 +154,21 @@ def _grouped_gemm_rows_op(
     epilogue: int,
     impl: int,
     out_peers: Optional[Tensor] = None,
+    peer_rows_cap: int = 0,
 ) -> None:
-    """`out_peers` (int64 [world], device): base address of every rank's output buffer; rows then go
-    to the rank named by `row_map` (expert parallelism) and `out` is this rank's own buffer."""
+    """`out_peers` (int64 [world], device): base address of every rank's output buffer of `peer_rows_cap`
+    rows; rows then go to the rank named by `row_map` (expert parallelism) and `out` is this rank's own
+    buffer. A word of `row_map` that names a rank or a row outside them is skipped and sets status bit 1."""
     require_cuda(a, w, out)
+    if out_peers is not None and peer_rows_cap <= 0:
+        raise ValueError("out_peers needs peer_rows_cap, the number of rows of every rank's buffer")
     if not w.is_contiguous():
         raise ValueError("expert weights must be contiguous [E, out_features, in_features]")
     check(
         lib.xma_b200_grouped_gemm_rows_peer(
             ptr(a), _row_stride(a), ptr(w), w_layout, ptr(out), _row_stride(out), ptr(aux),
-            0 if aux is None else _row_stride(aux), ptr(row_map), ptr(out_peers), ptr(tile_expert), ptr(tile_prefix),
+            0 if aux is None else _row_stride(aux), ptr(row_map), ptr(out_peers),
+            0 if out_peers is None else out_peers.numel(), peer_rows_cap, ptr(tile_expert), ptr(tile_prefix),
             w.size(0), tile_expert.numel(), kd, n, epilogue, dtype_code(a.dtype), impl, ptr(status_word(a.device)),
             current_stream(a.device)
         ),

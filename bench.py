@@ -396,7 +396,7 @@ def run_ep_microbench(args) -> None:
                                               I, H, _lib.EPI_PLAIN, 0))
     out["gemm_down_plain"] = {"ms": ms, "tflops": flops / ms / 1e9}
     ms = timed(lambda: ops.grouped_gemm_rows_(act, w2, _lib.W_NK, home[0], None, meta[0], t0["tile_expert"],
-                                              t0["tile_prefix"], I, H, _lib.EPI_PLAIN, 0, home_table))
+                                              t0["tile_prefix"], I, H, _lib.EPI_PLAIN, 0, home_table, R))
     out["gemm_down_rows_to_ranks"] = {"ms": ms, "tflops": flops / ms / 1e9}
     _lib.raise_on_device_status(device)
     best = out["ep_dispatch"]

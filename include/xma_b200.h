@@ -4,8 +4,9 @@
  *
  * Conventions
  *   - Plain pointers and sizes only; every pointer is a DEVICE pointer unless stated otherwise.
- *   - The caller owns and allocates every buffer (outputs included); nothing here allocates device
- *     memory. All work is enqueued on `stream` and is asynchronous.
+ *   - The caller owns and allocates every buffer (outputs included); no entry point allocates device
+ *     memory except xma_b200_exchange_alloc (memory that other processes map must not come from a
+ *     sub-allocating pool). All work is enqueued on `stream` and is asynchronous.
  *   - Return value: 0 = enqueued; < 0 = argument error found on the host, nothing enqueued
  *     (XMA_ERR_* below); > 0 = cudaError_t of a failed runtime call or launch.
  *     xma_b200_error_string() turns any of them into text.
@@ -153,16 +154,19 @@ int xma_b200_grouped_gemm_rows(const void* a, int64_t a_row_stride, const void* 
  * epilogue and row_map required; row_map[r] = (rank << 24) | row (negative: skipped) and the row is
  * stored to out_peers[rank] + row * out_row_stride, where out_peers is a device table of one base
  * address per rank (this rank's own buffer included; the others mapped with xma_b200_exchange_open).
- * The tensor-core kernel (one CTA per tile; impl 3 is not available here) stages the tile in shared
- * memory so that every row crosses NVLink in 128-byte pieces. out_peers NULL: identical to
- * xma_b200_grouped_gemm_rows. No counterpart in the reference, whose MoE keeps all experts on one
- * device (xma/layers/moe/__init__.py:144-160). */
+ * out_peers has peer_world entries (<= 128) and every rank's buffer peer_rows_cap rows (<= 2^24): a
+ * word that names a rank or a row outside them is skipped like a negative one and sets status bit 1,
+ * so a stale or corrupt word never becomes a store into another GPU's memory.
+ * The tensor-core kernels (one CTA per tile and CTA pairs) stage the tile in shared memory so that
+ * every row crosses NVLink in 128-byte pieces. out_peers NULL: identical to
+ * xma_b200_grouped_gemm_rows (peer_world and peer_rows_cap ignored). No counterpart in the reference,
+ * whose MoE keeps all experts on one device (xma/layers/moe/__init__.py:144-160). */
 int xma_b200_grouped_gemm_rows_peer(const void* a, int64_t a_row_stride, const void* w, int w_layout, void* out,
                                     int64_t out_row_stride, void* aux, int64_t aux_row_stride,
-                                    const int32_t* row_map, void* const* out_peers, const int32_t* tile_expert,
-                                    const int32_t* tile_prefix, int num_experts, int64_t tile_cap, int64_t kd,
-                                    int64_t n, int epilogue, int dtype, int impl, int* device_status,
-                                    cudaStream_t stream);
+                                    const int32_t* row_map, void* const* out_peers, int peer_world,
+                                    int64_t peer_rows_cap, const int32_t* tile_expert, const int32_t* tile_prefix,
+                                    int num_experts, int64_t tile_cap, int64_t kd, int64_t n, int epilogue, int dtype,
+                                    int impl, int* device_status, cudaStream_t stream);
 
 /* dw[e, m, n] = sum over the rows r of expert e of x[r, m] * y[r, n]; x, y grouped (rows_cap rows
  * allocated); experts without rows get zeros, so dw needs no pre-zeroing.
@@ -173,6 +177,24 @@ int xma_b200_grouped_gemm_dw(const void* x, int64_t x_row_stride, const void* y,
                              cudaStream_t stream);
 
 int xma_b200_grouped_gemm_uses_tensor_cores(int dtype, int64_t kd, int64_t n);
+
+/* Host-only query: the kernel family that impl = 0 takes on the current device for a problem of this
+ * shape, assuming 16-byte aligned pointers (1 = CUDA cores, 2 = tcgen05 one CTA per tile, 3 = tcgen05
+ * CTA pairs). kind 0 = xma_b200_grouped_gemm_rows(_peer) with kd, n, w_layout, epilogue and peer
+ * (0/1: out_peers given); kind 1 = xma_b200_grouped_gemm_dw with m = kd, n. No counterpart in the
+ * reference (its Triton autotuner picks tile sizes, xma/layers/moe/triton_implementation/scatter_kernel.py:12-52). */
+int xma_b200_grouped_gemm_choice(int kind, int dtype, int num_experts, int64_t tile_cap, int64_t kd, int64_t n,
+                                 int w_layout, int epilogue, int peer);
+
+/* Process-wide tuning switches of the tensor-core kernels; returns the previous value (< 0: unknown key).
+ * key 0: SwiGLU-backward epilogue asks for the next tile's gate|up rows in L2 (0/1, default 1);
+ * key 1: reduction blocks that the TMA producer prefetches into L2 ahead of its loads (0..255, default 0);
+ * key 2: operands that prefetch covers (bit 0 = A, bit 1 = B); key 3: epilogue warps (0 = per-kernel
+ * default, 4, 8); key 4: CTA pairs also for plain epilogues in the automatic choice (0/1, default 1).
+ * The environment variables XMA_B200_GU_PREFETCH, XMA_B200_TMA_PREFETCH, XMA_B200_TMA_PREFETCH_MASK,
+ * XMA_B200_EPI_WARPS and XMA_B200_PLAIN_PAIRS set the initial values. Stands where the reference has its
+ * autotune configurations (scatter_kernel.py:12-52). */
+int xma_b200_tuning_set(int key, int value);
 
 /* ---- stand-alone SwiGLU --------------------------------------------------------------------- */
 

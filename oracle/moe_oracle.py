@@ -277,3 +277,34 @@ def moe_forward_backward(
         res.grads["gate"] = d_logits.t() @ x
         res.grads["x"] = d_x + d_logits @ gate_w
     return res
+
+
+def expert_weight_grads_slice(
+    xs_e: torch.Tensor,
+    d_o_e: torch.Tensor,
+    w1_e: torch.Tensor,
+    w2_e: torch.Tensor,
+    cols: torch.Tensor,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Weight gradients of ONE SwiGLU expert restricted to the intermediate features `cols`
+    (gate = first half of c_fc's outputs, up = second half), so that the check of a large expert
+    costs a fraction of its full backward. Same arithmetic as the per-expert loop of
+    `moe_forward_backward` (xma/layers/moe/__init__.py:89-105 forward, autograd backward), in fp32:
+
+      xs_e  [rows, H]   the token rows routed to the expert (expert-sorted order)
+      d_o_e [rows, H]   dY of those rows already multiplied by their routing weight
+      w1_e  [2I, H], w2_e [H, I]
+      returns d_w1[cols and I + cols, :]  as [2 * len(cols), H]  and  d_w2[:, cols]  as [H, len(cols)]
+    """
+    inter = w2_e.shape[1]
+    xs, do = xs_e.float(), d_o_e.float()
+    gate = xs @ w1_e[cols].float().t()
+    up = xs @ w1_e[cols + inter].float().t()
+    # the kernels keep gate|up in the storage dtype and apply SwiGLU to the rounded values
+    gate, up = gate.to(xs_e.dtype), up.to(xs_e.dtype)
+    act = swiglu(gate, up)
+    d_w2 = do.t() @ act.float()
+    d_act = do @ w2_e[:, cols].float()
+    dg, du = swiglu_backward(gate.float(), up.float(), d_act)
+    d_w1 = torch.cat([dg.t() @ xs, du.t() @ xs], dim=0)
+    return d_w1, d_w2

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(LIB)
     for name in declared_symbols():
         assert hasattr(lib, name), f"{name} declared in include/xma_b200.h but not exported"
-    assert lib.xma_b200_abi_version() == 1
+    assert lib.xma_b200_abi_version() == 2
 
 
 def test_python_binding_covers_header():
@@ -77,10 +77,20 @@ def test_expert_parallel_entry_points_reject_bad_arguments_without_a_gpu():
     assert lib.xma_b200_ep_return(p, 2, 64, p, 0, 64, 2, p, 128, None, None) == 0
     assert lib.xma_b200_ep_publish(p, 4, None, None) == NULL
     # a row map is required (and only the plain epilogue allowed) when rows go to other ranks' buffers
-    gemm = lambda row_map, epilogue: lib.xma_b200_grouped_gemm_rows_peer(
-        p, 64, p, 0, p, 64, None, 0, row_map, p, p, p, 2, 4, 64, 64, epilogue, 2, 0, None, None)
+    gemm = lambda row_map, epilogue, world=2, cap=512: lib.xma_b200_grouped_gemm_rows_peer(
+        p, 64, p, 0, p, 64, None, 0, row_map, p, world, cap, p, p, 2, 4, 64, 64, epilogue, 2, 0, None, None)
     assert gemm(None, 0) == SHAPE
     assert gemm(p, 1) == SHAPE
+    # ... and the table's size and the buffers' row count bound what a row-map word may name
+    assert gemm(p, 0, world=0) == SHAPE
+    assert gemm(p, 0, world=129) == SHAPE
+    assert gemm(p, 0, cap=0) == SHAPE
+    assert gemm(p, 0, cap=(1 << 24) + 1) == SHAPE
+    # host-only queries and switches
+    assert lib.xma_b200_grouped_gemm_choice(0, 0, 8, 264, 4096, 4096, 0, 0, 0) == 1  # fp32: CUDA cores
+    assert lib.xma_b200_tuning_set(99, 0) == SHAPE
+    previous = lib.xma_b200_tuning_set(1, 7)
+    assert lib.xma_b200_tuning_set(1, previous) == 7
     # exchange buffers
     assert lib.xma_b200_exchange_alloc(0, ctypes.byref(out)) == SHAPE
     assert lib.xma_b200_exchange_alloc(1024, None) == NULL

@@ -219,9 +219,10 @@ def test_rows_gemm_packed_swiglu_epilogues(impl, dtype, counts, kd, inter):
 
 @pytest.mark.parametrize("impl,dtype", [pytest.param(SIMT, torch.float32, id="cudacore-f32"),
                                         pytest.param(TC, torch.bfloat16, id="tcgen05-bf16"),
+                                        pytest.param(TC_PAIR, torch.bfloat16, id="pair-bf16"),
                                         pytest.param(0, torch.float16, id="auto-f16")])
 @pytest.mark.parametrize("counts,kd,n", [([5, 0, 130, 1], 64, 256), ([300, 7, 0, 0, 129, 64], 576, 264),
-                                         ([1000, 24], 256, 1032)])
+                                         ([1000, 24], 256, 1032), ([2300, 1100], 128, 512)])
 @pytest.mark.parametrize("layout", ["nk", "kn"])
 def test_rows_gemm_peer_output_matches_scattered_output(impl, dtype, counts, kd, n, layout):
     """out_peers: every output row is stored into the buffer that its row_map word names
@@ -253,8 +254,23 @@ def test_rows_gemm_peer_output_matches_scattered_output(impl, dtype, counts, kd,
     cap = int(max((owner == b).sum() for b in range(buffers))) + 1
     outs = [torch.full((cap, n), float("nan"), dtype=dtype, device="cuda") for _ in range(buffers)]
     table = torch.tensor([o.data_ptr() for o in outs], dtype=torch.int64, device="cuda")
+    # a few words that name a buffer outside the table or a row outside the buffers: their rows must be
+    # skipped (nothing stored anywhere) and status bit 1 raised
+    bad = rng.choice(valid.size, size=min(5, valid.size), replace=False)
+    bad_words = row_map.copy()
+    bad_words[valid[bad[0::2]]] = (buffers << 24) | 0            # buffer index == number of buffers
+    bad_words[valid[bad[1::2]]] = (owner[bad[1::2]] << 24) | cap  # row == rows of the buffer
+    ops.grouped_gemm_rows_(a, w, wl, outs[0], None, torch.from_numpy(bad_words).cuda(), plan.tile_expert,
+                           plan.tile_prefix, kd, n, _lib.EPI_PLAIN, impl, table, cap)
+    torch.cuda.synchronize()
+    assert _lib.read_and_clear_device_status(torch.device("cuda")) == _lib.DEV_ID_OUT_OF_RANGE
+    for i in bad:
+        assert torch.isnan(outs[int(owner[i])][int(slot[i])]).all(), "a row with a bad word was stored"
+    for o in outs:
+        o.fill_(float("nan"))
+
     ops.grouped_gemm_rows_(a, w, wl, outs[0], None, torch.from_numpy(row_map).cuda(), plan.tile_expert,
-                           plan.tile_prefix, kd, n, _lib.EPI_PLAIN, impl, table)
+                           plan.tile_prefix, kd, n, _lib.EPI_PLAIN, impl, table, cap)
     torch.cuda.synchronize()
     assert _lib.read_and_clear_device_status(torch.device("cuda")) == 0
     for b in range(buffers):
