@@ -2,11 +2,16 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1] [--impl reference]
 
-N = 1 runs the Mixtral-shaped layer of BASELINE.json configs[1] (16384 tokens, hidden 4096,
-intermediate 14336, 8 experts, top-2, bf16) through `xma.layers.MoE`. For N > 1 the script is
+N = 1 runs the Mixtral-shaped layer (16384 tokens, hidden 4096, intermediate 14336, 8 experts,
+top-2, SwiGLU, bf16) through `xma.layers.MoE`. For N > 1 the script is
 launched by torchrun, one rank per GPU, and runs the same per-GPU workload expert-parallel
 (experts sharded over ranks, NCCL all-to-all dispatch/combine): weak scaling.
 A step = one forward + backward of the layer on one batch of seeded synthetic inputs.
+
+After the headline workload the same process times the fine-grained skewed layer (64 experts top-8,
+N = 1 only) and the 128-expert top-8 layer (at the same N) with fewer steps and reports them under
+`configs2` / `configs3`, and checks the headline layer's results against the CPU oracle
+(`parity_check`, outside every timed region).
 
 `value`  : tokens/s with inputs resident in HBM (CUDA events around exactly K steps, max over ranks)
 `e2e`    : the same metric with the step's inputs copied from pinned host memory and its results
@@ -39,15 +44,15 @@ import torch  # noqa: E402
 # name -> tokens per GPU, hidden, intermediate, experts (global), top_k
 WORKLOADS = {
     "c1": dict(tokens=512, hidden=256, inter=512, experts=8, top_k=2, dtype="f32",
-               desc="configs[0] tiny fp32"),
+               desc="tiny fp32 layer"),
     "c2": dict(tokens=16384, hidden=4096, inter=14336, experts=8, top_k=2, dtype="bf16",
-               desc="configs[1] Mixtral-shaped: 4x4096 tokens, 8 experts top-2, SwiGLU"),
+               desc="Mixtral-shaped: 4x4096 tokens, 8 experts top-2, SwiGLU"),
     "c2e2": dict(tokens=4096, hidden=4096, inter=14336, experts=2, top_k=2, dtype="bf16",
-                 desc="profiling slice of configs[1]: same per-expert GEMM shapes (4096 rows/expert), 2 experts"),
+                 desc="profiling slice of c2: same per-expert GEMM shapes (4096 rows/expert), 2 experts"),
     "c3": dict(tokens=32768, hidden=2048, inter=1024, experts=64, top_k=8, dtype="bf16",
-               desc="configs[2] fine-grained: 64 experts top-8, Zipf(1.2)-skewed load"),
+               desc="fine-grained: 64 experts top-8, Zipf(1.2)-skewed load"),
     "c4": dict(tokens=16384, hidden=4096, inter=1536, experts=128, top_k=8, dtype="bf16",
-               desc="configs[3] expert-parallel: 128 experts top-8, uniform random logits"),
+               desc="expert-parallel shape: 128 experts top-8, uniform random logits"),
 }
 PEAK_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 METRIC = "moe_fwd_bwd_tokens_per_s"
@@ -215,12 +220,16 @@ def run_reference_arm(args, w: dict, name: str) -> None:
     if rank != 0:
         return
     sample = cpu_sample_tokens(w)
-    value, sec, threads = cpu_step_tokens_per_s(w, sample, max(1, args.steps), max(0, min(args.warmup, 1)))
+    steps, warm = max(1, args.steps), max(0, min(args.warmup, 1))  # one warm-up step is all a CPU arm needs
+    value, sec, threads = cpu_step_tokens_per_s(w, sample, steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": warm, "warmup_requested": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": f"{name}: {w['desc']}", "tokens_per_step_sample": sample},
+        "config": {"workload": f"{name}: {w['desc']}", "tokens_per_step_sample": sample,
+                   "note": f"each step runs {sample} of the workload's {w['tokens']} tokens through the full expert "
+                           "shapes; tokens/s is per token, so the sample size does not enter it"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": f"{sample} of {w['tokens']} tokens per step, full expert shapes, "
                                    "oracle/moe_oracle.py (CPU restatement of the reference torch path)"},
@@ -231,7 +240,7 @@ def run_reference_arm(args, w: dict, name: str) -> None:
 
 
 # ---------------------------------------------------------------------------------------------------
-# configs[4]: routing microbench (HBM-bound kernels only)
+# routing microbench (HBM-bound kernels only)
 # ---------------------------------------------------------------------------------------------------
 def zipf_ids(n: int, bins: int, s: float, seed: int) -> np.ndarray:
     rng = np.random.RandomState(seed)
@@ -242,9 +251,9 @@ def zipf_ids(n: int, bins: int, s: float, seed: int) -> np.ndarray:
 
 
 def run_routing_microbench(args) -> None:
-    """continuous_count, the counting sort and the row permute of BASELINE configs[4]: 64 Mi int32 ids
-    over 256 bins (uniform and Zipf(1.1)) and rows of 2048 bf16. The 64 Mi x 2048 token buffer of the
-    config is 256 GiB and does not fit a B200, so the permute moves the first `rows` rows (8 Mi =
+    """continuous_count, the counting sort and the row permute of the routing microbench: 64 Mi int32 ids
+    over 256 bins (uniform and Zipf(1.1)) and rows of 2048 bf16. A 64 Mi x 2048 token buffer would be
+    256 GiB and does not fit a B200, so the permute moves the first `rows` rows (8 Mi =
     32 GiB in + 32 GiB out) with the sort permutation of the first `rows` ids; GB/s does not depend on
     the row count at this size."""
     if not torch.cuda.is_available():
@@ -305,7 +314,7 @@ def run_routing_microbench(args) -> None:
         "metric": "routing_hbm_gb_per_s", "value": best["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
         "warmup": warm, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int32/bf16", "data": "synthetic",
-        "config": {"workload": "c5: configs[4] routing microbench, 64 Mi ids over 256 bins; permute of 8 Mi x 2048 bf16 rows",
+        "config": {"workload": "c5: routing microbench, 64 Mi ids over 256 bins; permute of 8 Mi x 2048 bf16 rows",
                    "l2_policy": "inputs_exceed_l2"},
         "roofline": {"bound": "hbm", "kernel": "gather_rows_kernel", "achieved": best["gbs"], "peak": hbm,
                      "unit": "GB/s", "frac": best["frac"], "peak_source": f"{peak_kind} copy bandwidth",
@@ -315,7 +324,7 @@ def run_routing_microbench(args) -> None:
 
 
 def run_ep_microbench(args) -> None:
-    """Kernels of the expert-parallel peer transport on ONE GPU, with the shapes one rank of configs[1] sees
+    """Kernels of the expert-parallel peer transport on ONE GPU, with the shapes one rank of workload c2 sees
     at 4 ranks (2 local experts, 32768 received rows of 4096 bf16, I = 14336): the "ranks" are buffers of
     the same device addressed through the same pointer tables, so the figures are HBM figures (what the
     kernels cost before NVLink enters) and the kernels can be captured by ncu, which a multi-rank run cannot."""
@@ -404,7 +413,7 @@ def run_ep_microbench(args) -> None:
         "metric": "ep_row_exchange_hbm_gb_per_s", "value": best["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
         "warmup": warm, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"ep: peer-transport kernels of configs[1] at {W} ranks, ranks emulated as buffers of one GPU",
+        "config": {"workload": f"ep: peer-transport kernels of workload c2 at {W} ranks, ranks emulated as buffers of one GPU",
                    "l2_policy": "inputs_exceed_l2"},
         "roofline": {"bound": "hbm", "kernel": "ep_dispatch_kernel", "achieved": best["gbs"], "peak": hbm,
                      "unit": "GB/s", "frac": best["frac"], "peak_source": f"{peak_kind} copy bandwidth", "traffic": None},
@@ -413,53 +422,188 @@ def run_ep_microbench(args) -> None:
 
 
 # ---------------------------------------------------------------------------------------------------
+# stand-alone swiglu / swiglu_packed (HBM-bound)
+# ---------------------------------------------------------------------------------------------------
+def run_swiglu_microbench(args) -> None:
+    """`swiglu` and `swiglu_packed`, forward and backward, on the shape of the reference's own throughput
+    scripts (tools/throughput_swiglu.py:31-32,61-75 and tools/throughput_swiglu_packed.py:26-27,48-62):
+    B = 16 * 4096 rows, H = 4096 columns, fp32 / fp16 / bf16, algorithmic bytes 3 * B * H * itemsize forward and
+    5 * B * H * itemsize backward, against the measured copy bandwidth."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    from xma.functional import swiglu, swiglu_packed
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks.get("hbm_gbs", PEAK_FALLBACK["hbm_gbs"]))
+    B, H = 16 * 4096, 4096
+    steps, warm = max(args.steps, 20), max(args.warmup, 5)
+
+    def timed(fn) -> float:
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    out = {}
+    for dtype, tag in ((torch.float32, "f32"), (torch.float16, "f16"), (torch.bfloat16, "bf16")):
+        item = torch.empty((), dtype=dtype).element_size()
+        g = torch.randn(B, H, device=device, dtype=dtype, requires_grad=True)
+        u = torch.randn(B, H, device=device, dtype=dtype, requires_grad=True)
+        dy = torch.randn(B, H, device=device, dtype=dtype)
+        ms = timed(lambda: swiglu(g.detach(), u.detach()))
+        out[f"swiglu_fwd_{tag}"] = {"ms": ms, "gbs": 3 * B * H * item / ms / 1e6}
+        z = swiglu(g, u)
+        ms = timed(lambda: torch.autograd.grad(z, (g, u), grad_outputs=dy, retain_graph=True))
+        out[f"swiglu_bwd_{tag}"] = {"ms": ms, "gbs": 5 * B * H * item / ms / 1e6}
+        del z
+        # gate and up as the two halves of one [B, 2H] buffer (the layout `chunk(2, -1)` hands over)
+        gu = torch.randn(B, 2 * H, device=device, dtype=dtype)
+        ms = timed(lambda: swiglu(*gu.chunk(2, dim=-1)))
+        out[f"swiglu_fwd_chunked_{tag}"] = {"ms": ms, "gbs": 3 * B * H * item / ms / 1e6}
+        xp = gu.requires_grad_()
+        ms = timed(lambda: swiglu_packed(xp.detach()))
+        out[f"swiglu_packed_fwd_{tag}"] = {"ms": ms, "gbs": 3 * B * H * item / ms / 1e6}
+        zp = swiglu_packed(xp)
+        ms = timed(lambda: torch.autograd.grad(zp, (xp,), grad_outputs=dy, retain_graph=True))
+        out[f"swiglu_packed_bwd_{tag}"] = {"ms": ms, "gbs": 5 * B * H * item / ms / 1e6}
+        del zp, xp, gu, g, u, dy
+    for v in out.values():
+        v["frac"] = v["gbs"] / hbm
+    worst = min(out, key=lambda k: out[k]["frac"])
+    head = out["swiglu_bwd_bf16"]
+    print(json.dumps({
+        "metric": "swiglu_hbm_gb_per_s", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
+        "warmup": warm, "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"swiglu: stand-alone swiglu / swiglu_packed, {B} x {H}, fp32/fp16/bf16, forward and backward",
+                   "l2_policy": "inputs_exceed_l2"},
+        "roofline": {"bound": "hbm", "kernel": "swiglu_bwd_kernel<bf16>", "achieved": head["gbs"], "peak": hbm,
+                     "unit": "GB/s", "frac": head["frac"], "peak_source": f"{peak_kind} copy bandwidth",
+                     "traffic": None},
+        "lowest": {"kernel": worst, **out[worst]},
+        "kernels": out,
+    }), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# DRAM traffic table (ncu) and kernel names
+# ---------------------------------------------------------------------------------------------------
+KERNEL_SOURCES = ("grouped_gemm_sm100.cu", "grouped_gemm_sm100_2cta.cu", "sm100_common.cuh", "gemm_api.cu")
+TRAFFIC_TABLE = os.path.join(ROOT, "profiles", "dram_traffic_grouped_gemm_c2e2.md")
+
+
+def kernel_source_digest() -> str:
+    """sha256 over the grouped-GEMM kernel sources: a traffic table names the digest it was captured with."""
+    import hashlib
+
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, "accelerated-model-architectures_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def load_traffic_table() -> tuple[dict | None, str]:
+    """-> ({tag: DRAM bytes per launch on the 2-expert slice}, note). The table is a text summary of an ncu
+    capture (`dram__bytes_read.sum + dram__bytes_write.sum` per launch); it is used only while the kernel
+    sources still have the digest the capture was taken with, otherwise the traffic is reported as null."""
+    if not os.path.exists(TRAFFIC_TABLE):
+        return None, "no ncu traffic table in profiles/"
+    digest, rows = None, {}
+    with open(TRAFFIC_TABLE) as f:
+        for line in f:
+            parts = [c.strip() for c in line.strip().strip("|").split("|")]
+            if line.startswith("kernel-source-digest:"):
+                digest = line.split(":", 1)[1].strip()
+            elif len(parts) >= 2 and parts[0].startswith("gemm_"):
+                try:
+                    rows[parts[0]] = float(parts[1])
+                except ValueError:
+                    pass
+    if digest != kernel_source_digest():
+        return None, f"ncu traffic table is older than the kernel sources (table {digest}, sources {kernel_source_digest()})"
+    return rows, "profiles/dram_traffic_grouped_gemm_c2e2.md (ncu, 2-expert slice, scaled by experts / 2)"
+
+
+_IMPL_NAMES = {1: "CUDA cores", 2: "tcgen05, one CTA per 128x256 tile", 3: "tcgen05, CTA pairs, 256x256 tiles"}
+
+
+def gemm_kernel_names(w: dict, rows_per_rank: int, local_experts: int, peer: bool, dtype: torch.dtype) -> dict:
+    """tag -> the kernel function the automatic choice launches for this workload (asked of the library)."""
+    from xma import _lib
+
+    H, I = w["hidden"], w["inter"]
+    code = _lib.dtype_code(dtype)
+    tile_cap = rows_per_rank // _lib.ROW_PAD + local_experts
+    q = _lib.lib.xma_b200_grouped_gemm_choice
+    rows = lambda kd, n, wl, epi, p=0: q(0, code, local_experts, tile_cap, kd, n, wl, epi, p)
+    dw = lambda m, n: q(1, code, local_experts, tile_cap, m, n, 0, 0, 0)
+    fam = {2: "rows_gemm_tc_kernel", 3: "rows_gemm_tc2_kernel", 1: "rows_gemm_simt_kernel"}
+    famw = {2: "dw_gemm_tc_kernel", 3: "dw_gemm_tc2_kernel", 1: "dw_gemm_simt_kernel"}
+    choice = {
+        "gemm_up_swiglu": (fam, rows(H, 2 * I, _lib.W_NK, _lib.EPI_SWIGLU), "<T, W_NK, SwiGLU>"),
+        "gemm_down": (fam, rows(I, H, _lib.W_NK, _lib.EPI_PLAIN, int(peer)), "<T, W_NK, plain%s>" % (" to peers" if peer else "")),
+        "gemm_dact_dswiglu": (fam, rows(H, I, _lib.W_KN, _lib.EPI_DSWIGLU), "<T, W_KN, dSwiGLU>"),
+        "gemm_dx": (fam, rows(2 * I, H, _lib.W_KN, _lib.EPI_PLAIN, int(peer)), "<T, W_KN, plain%s>" % (" to peers" if peer else "")),
+        "gemm_dw1": (famw, dw(2 * I, H), "<T>"),
+        "gemm_dw2": (famw, dw(H, I), "<T>"),
+    }
+    return {tag: f"{f[impl]}{targs} ({_IMPL_NAMES[impl]})" for tag, (f, impl, targs) in choice.items()}
+
+
+# ---------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "ep"])
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--transport", choices=["peer", "nccl"], default="peer",
-                    help="row exchange of the expert-parallel layer: stores into peer memory, or NCCL all-to-all")
-    ap.add_argument("--unfused-return", dest="fused_return", action="store_false",
-                    help="peer transport: return rows with a separate row kernel instead of the GEMM epilogues")
-    ap.add_argument("--ep-chunks", type=int, default=None,
-                    help="micro-batches per step in the expert-parallel layer (overlap of all-to-all and GEMM)")
-    args = ap.parse_args()
-    if args.workload == "c5":
-        run_routing_microbench(args)
-        return
-    if args.workload == "ep":
-        run_ep_microbench(args)
-        return
-    w = WORKLOADS[args.workload]
+class Bench:
+    """One process of the GPU arm: device, process group, and the helpers every workload shares."""
 
-    if args.impl == "reference":
-        run_reference_arm(args, w, args.workload)
-        return
+    def __init__(self, args) -> None:
+        self.args = args
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={self.world}: launch with torchrun --nproc-per-node {args.gpus}")
+        torch.cuda.set_device(self.local_rank)
+        self.device = torch.device("cuda", self.local_rank)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the B200 kernels are the only implementation (no CPU path)")
+            dist.init_process_group("nccl", device_id=self.device)
+            self.dist = dist
+        self.transport = args.transport
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
+    def barrier(self) -> None:
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
 
-        dist.init_process_group("nccl", device_id=device)
+    def max_over_ranks(self, ms: float) -> float:
+        if self.dist is None:
+            return ms
+        t = torch.tensor([ms], device=self.device, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
 
-    from xma import _lib, ops
+    def gpu_index(self) -> int:
+        if "CUDA_VISIBLE_DEVICES" not in os.environ:
+            return self.local_rank
+        return int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[self.local_rank])
 
+
+def build_workload(b: Bench, name: str):
+    """-> (layer, local MoE, x, dy) on the device, for this rank."""
+    w = WORKLOADS[name]
+    args, rank, world, device = b.args, b.rank, b.world, b.device
     dtype = torch.float32 if w["dtype"] == "f32" else torch.bfloat16
     E = w["experts"]
     if E % world:
@@ -469,18 +613,18 @@ def main() -> None:
     if world > 1:
         from xma.distributed import ExpertParallelMoE, PeerLink
 
-        if args.transport == "peer":
+        if b.transport == "peer":
             # the peer transport needs the ranks to map each other's memory; where the node does not allow
             # that, every rank learns it here (share() fails collectively) and the run uses NCCL all-to-all
             try:
-                probe = PeerLink(dist.group.WORLD)
+                probe = PeerLink(b.dist.group.WORLD)
                 probe.release(*probe.share(1 << 20, device)[::2])
             except RuntimeError as exc:
                 if rank == 0:
                     print(f"peer transport unavailable ({exc}); using NCCL all-to-all", file=sys.stderr)
-                args.transport = "nccl"
-        layer = ExpertParallelMoE(moe, gate, world_group=dist.group.WORLD, overlap_chunks=args.ep_chunks,
-                                  transport=args.transport, fused_return=args.fused_return)
+                b.transport = "nccl"
+        layer = ExpertParallelMoE(moe, gate, world_group=b.dist.group.WORLD, overlap_chunks=args.ep_chunks,
+                                  transport=b.transport, fused_return=args.fused_return)
     else:
         with torch.no_grad():
             moe.gate.weight.copy_(gate)
@@ -494,171 +638,324 @@ def main() -> None:
             g = torch.zeros(E, w["hidden"], device=device, dtype=dtype)
             g[:, :E] = torch.eye(E, device=device, dtype=dtype)
             (layer.gate_weight if world > 1 else moe.gate.weight).copy_(g)
+    return layer, moe, x_dev, dy_dev
 
+
+def make_step(layer):
     params = list(layer.parameters())
 
     def step(x: torch.Tensor, dy: torch.Tensor):
         for p in params:
             p.grad = None
         xin = x.detach().requires_grad_()
-        y, _ = layer(xin)
+        y, logits = layer(xin)
         y.backward(dy)
-        return y, xin.grad
+        return y, xin.grad, logits
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    return step
 
-    def max_over_ranks(ms: float) -> float:
-        if dist is None:
-            return ms
-        t = torch.tensor([ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
 
-    # ---- device-resident timing --------------------------------------------------------------
-    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
-                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
-    sampler.start()  # nvidia-smi needs a moment to come up; samples are filtered to the timed region
-    for _ in range(max(args.warmup, 3)):
+def release_layer(b: Bench, layer) -> None:
+    if b.world > 1 and b.transport == "peer":
+        layer.close()  # collective: unmap the other ranks' exchange buffers before anyone frees them
+
+
+def time_device_resident(b: Bench, name: str, layer, x_dev, dy_dev, steps: int, warmup: int, sampler=None) -> dict:
+    """W warm-up steps, then exactly K steps between CUDA events with a barrier + synchronize on both sides;
+    the time is the maximum over the ranks. Per-op CUDA events on the launching stream give the kernel table."""
+    from xma import _lib, ops
+
+    w = WORKLOADS[name]
+    step = make_step(layer)
+    for _ in range(max(warmup, 3)):
         step(x_dev, dy_dev)
-    barrier()
-    _lib.raise_on_device_status(device)
-
+    b.barrier()
+    _lib.raise_on_device_status(b.device)
     ops.STATS.enabled, ops.STATS.timing = True, True
     ops.STATS.reset()
-    barrier()
-    sampler.mark_begin()
+    b.barrier()
+    if sampler:
+        sampler.mark_begin()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step(x_dev, dy_dev)
     t_end.record()
-    barrier()
-    sampler.mark_end()
-    clocks = sampler.stop()
-    ms_total = max_over_ranks(t_start.elapsed_time(t_end))
+    b.barrier()
+    if sampler:
+        sampler.mark_end()
+    ms_total = b.max_over_ranks(t_start.elapsed_time(t_end))
     launches = ops.STATS.launches
     kernel_ms = ops.STATS.elapsed_ms()
     ops.STATS.enabled = ops.STATS.timing = False
-    _lib.raise_on_device_status(device)
-    ms_per_step = ms_total / args.steps
-    tokens_per_step = w["tokens"] * world
-    value = tokens_per_step / (ms_per_step * 1e-3)
-
-    # ---- end to end: pinned host inputs in, results out, every step ------------------------------
-    x_pin, dy_pin = make_inputs(w, device, dtype, seed=rank, pinned=True)
-    if w is WORKLOADS["c4"]:
-        x_pin.copy_(x_dev.cpu())
-    y_host = torch.empty_like(x_pin).pin_memory()
-    dx_host = torch.empty_like(x_pin).pin_memory()
-
-    # Every step's inputs come from pinned host memory and its results go back to pinned host memory.
-    # The copies run on their own streams so that the upload of step s+1 and the download of step s-1
-    # overlap the kernels of step s (double-buffered device inputs); all of it is inside the timed region.
-    main_stream = torch.cuda.current_stream()
-    h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
-    x_buf = [torch.empty_like(x_dev) for _ in range(2)]
-    dy_buf = [torch.empty_like(dy_dev) for _ in range(2)]
-    uploaded = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
-
-    def upload(s: int) -> None:
-        b = s & 1
-        h2d.wait_event(consumed[b])  # the step that last read this buffer pair has finished
-        with torch.cuda.stream(h2d):
-            x_buf[b].copy_(x_pin, non_blocking=True)
-            dy_buf[b].copy_(dy_pin, non_blocking=True)
-            uploaded[b].record(h2d)
-
-    def e2e_run(steps: int) -> None:
-        for ev in consumed:
-            ev.record(main_stream)
-        upload(0)
-        for s in range(steps):
-            b = s & 1
-            if s + 1 < steps:
-                upload(s + 1)
-            main_stream.wait_event(uploaded[b])
-            y, dx = step(x_buf[b], dy_buf[b])
-            consumed[b].record(main_stream)
-            d2h.wait_event(consumed[b])
-            with torch.cuda.stream(d2h):
-                y_host.copy_(y, non_blocking=True)
-                dx_host.copy_(dx, non_blocking=True)
-            y.record_stream(d2h)
-            dx.record_stream(d2h)
-        main_stream.wait_stream(d2h)
-
-    e2e_run(4)  # the caching allocator settles (tensors held for the downloads change its working set)
-    barrier()
-    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    e2e_run(args.steps)
-    e_end.record()
-    barrier()
-    e2e_ms = max_over_ranks(e_start.elapsed_time(e_end)) / args.steps
-    e2e_value = tokens_per_step / (e2e_ms * 1e-3)
-    bytes_in = (x_pin.numel() + dy_pin.numel()) * x_pin.element_size()
-    bytes_out = (y_host.numel() + dx_host.numel()) * y_host.element_size()
-
-    # ---- roofline of the dominant kernel family ----------------------------------------------------
-    peaks, peak_kind = measured_peaks()
-    T_local = w["tokens"] * (world if world > 1 else 1) // world  # tokens routed through this rank on average
-    R = T_local * w["top_k"]
+    _lib.raise_on_device_status(b.device)
+    ms_per_step = ms_total / steps
+    R = w["tokens"] * w["top_k"]  # routed rows through this rank's experts on average
     H, I = w["hidden"], w["inter"]
     gemm_flops = {  # algorithmic FLOPs per launch
         "gemm_up_swiglu": 2.0 * R * H * 2 * I, "gemm_down": 2.0 * R * I * H, "gemm_dact_dswiglu": 2.0 * R * H * I,
         "gemm_dx": 2.0 * R * 2 * I * H, "gemm_dw1": 2.0 * R * 2 * I * H, "gemm_dw2": 2.0 * R * H * I,
     }
     per_kernel = {}
-    for name, times in kernel_ms.items():
-        per_kernel[name] = {"launches": len(times), "ms_total": sum(times), "ms_avg": sum(times) / len(times)}
-        if name in gemm_flops:
-            per_kernel[name]["tflops"] = gemm_flops[name] / (per_kernel[name]["ms_avg"] * 1e-3) / 1e12
-    # One entry per kernel function; the dominant one (largest share of the timed region) gets the roofline.
-    kernel_functions = {
-        "rows_gemm_tc2_kernel<T, W_NK, SwiGLU> (up projection, CTA pairs)": ["gemm_up_swiglu"],
-        "rows_gemm_tc_kernel<T, W_NK, plain> (down projection)": ["gemm_down"],
-        "rows_gemm_tc2_kernel<T, W_KN, dSwiGLU> (d activation, CTA pairs)": ["gemm_dact_dswiglu"],
-        "rows_gemm_tc_kernel<T, W_KN, plain> (d input)": ["gemm_dx"],
-        "dw_gemm_tc2_kernel<T> (dW1 and dW2, CTA pairs)": ["gemm_dw1", "gemm_dw2"],
-    }
-    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures of the
-    # 2-expert slice `c2e2` summarised in profiles/ncu_grouped_gemm_tcgen05_c2e2.md; traffic grows in
-    # proportion to the number of experts at fixed rows per expert, so configs[1] moves experts/2 times this
-    # on one GPU (expert-parallel ranks see other rows per expert: no figure there). The dominant kernel is the
-    # weight-gradient GEMM; the four rows-GEMM entries were captured with the older tile order (an expert's row
-    # tiles innermost) and are upper bounds for the grouped order.
-    ncu_traffic_c2e2 = {"gemm_up_swiglu": 1.435e9, "gemm_down": 1.279e9, "gemm_dact_dswiglu": 1.784e9,
-                        "gemm_dx": 2.500e9, "gemm_dw1": 1.524e9, "gemm_dw2": 0.782e9}
+    for tag, times in kernel_ms.items():
+        per_kernel[tag] = {"launches": len(times), "ms_total": sum(times), "ms_avg": sum(times) / len(times)}
+        if tag in gemm_flops:
+            per_kernel[tag]["tflops"] = gemm_flops[tag] / (per_kernel[tag]["ms_avg"] * 1e-3) / 1e12
+    gemm_ms = sum(v["ms_total"] for t, v in per_kernel.items() if t in gemm_flops)
+    return {"ms_per_step": ms_per_step, "steps": steps, "launches": launches, "per_kernel": per_kernel,
+            "gemm_flops": gemm_flops, "gemm_ms_per_step": gemm_ms / steps,
+            "tokens_per_s": w["tokens"] * b.world / (ms_per_step * 1e-3),
+            "step_tflops_per_gpu": expert_flops(w, w["tokens"]) / (ms_per_step * 1e-3) / 1e12}
+
+
+def time_end_to_end(b: Bench, name: str, layer, x_dev, dy_dev, steps: int) -> dict:
+    """The same step with its inputs copied from pinned host memory and its results copied back to pinned host
+    memory inside the timed region. The copies run on their own streams so that the upload of step s+1 and the
+    download of step s-1 overlap the kernels of step s (double-buffered device inputs). The copy streams carry
+    their own CUDA events, which give the achieved host->device and device->host rates of this rank."""
+    w = WORKLOADS[name]
+    step = make_step(layer)
+    x_pin, dy_pin = x_dev.cpu().pin_memory(), dy_dev.cpu().pin_memory()
+    y_host = torch.empty_like(x_pin).pin_memory()
+    dx_host = torch.empty_like(x_pin).pin_memory()
+    main_stream = torch.cuda.current_stream()
+    h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
+    x_buf = [torch.empty_like(x_dev) for _ in range(2)]
+    dy_buf = [torch.empty_like(dy_dev) for _ in range(2)]
+    uploaded = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    copy_events: list = []
+
+    def upload(s: int) -> None:
+        k = s & 1
+        h2d.wait_event(consumed[k])  # the step that last read this buffer pair has finished
+        with torch.cuda.stream(h2d):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(h2d)
+            x_buf[k].copy_(x_pin, non_blocking=True)
+            dy_buf[k].copy_(dy_pin, non_blocking=True)
+            e1.record(h2d)
+            uploaded[k].record(h2d)
+            copy_events.append(("h2d", e0, e1))
+
+    def run(n: int) -> None:
+        for ev in consumed:
+            ev.record(main_stream)
+        upload(0)
+        for s in range(n):
+            k = s & 1
+            if s + 1 < n:
+                upload(s + 1)
+            main_stream.wait_event(uploaded[k])
+            y, dx, _ = step(x_buf[k], dy_buf[k])
+            consumed[k].record(main_stream)
+            d2h.wait_event(consumed[k])
+            with torch.cuda.stream(d2h):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(d2h)
+                y_host.copy_(y, non_blocking=True)
+                dx_host.copy_(dx, non_blocking=True)
+                e1.record(d2h)
+                copy_events.append(("d2h", e0, e1))
+            y.record_stream(d2h)
+            dx.record_stream(d2h)
+        main_stream.wait_stream(d2h)
+
+    run(4)  # the caching allocator settles (tensors held for the downloads change its working set)
+    b.barrier()
+    copy_events.clear()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    run(steps)
+    e_end.record()
+    b.barrier()
+    e2e_ms = b.max_over_ranks(e_start.elapsed_time(e_end)) / steps
+    bytes_in = (x_pin.numel() + dy_pin.numel()) * x_pin.element_size()
+    bytes_out = (y_host.numel() + dx_host.numel()) * y_host.element_size()
+    rate = {}
+    for kind, nbytes in (("h2d", bytes_in), ("d2h", bytes_out)):
+        ms = [a.elapsed_time(c) for k, a, c in copy_events if k == kind]
+        # slowest rank decides: report the minimum rate over the ranks
+        gbs = nbytes / (statistics.median(ms) * 1e-3) / 1e9 if ms else 0.0
+        rate[kind] = -b.max_over_ranks(-gbs)
+    return {"value": w["tokens"] * b.world / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+            "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out,
+            "h2d_gb_per_s_per_rank_min": rate["h2d"], "d2h_gb_per_s_per_rank_min": rate["d2h"],
+            "copy_overlap": "upload of step s+1 and download of step s-1 run on their own streams under step s"}
+
+
+def gather_expert_weights(b: Bench, layer, moe):
+    """Every rank's expert weights and the router weight on rank 0's host (the parity check needs all experts)."""
+    w1, w2 = moe.c_fc.weight.detach(), moe.c_proj.weight.detach()
+    gate = (layer.gate_weight if b.world > 1 else moe.gate.weight).detach()
+    if b.world > 1:
+        full1 = torch.empty((b.world,) + tuple(w1.shape), dtype=w1.dtype, device=w1.device)
+        full2 = torch.empty((b.world,) + tuple(w2.shape), dtype=w2.dtype, device=w2.device)
+        b.dist.all_gather_into_tensor(full1, w1.contiguous())
+        b.dist.all_gather_into_tensor(full2, w2.contiguous())
+        w1, w2 = full1.flatten(0, 1), full2.flatten(0, 1)
+    if b.rank != 0:
+        return None
+    return w1.cpu(), w2.cpu(), gate.cpu()
+
+
+def parity_check(results, weights_cpu, x: torch.Tensor, dy: torch.Tensor, top_k: int, sample_tokens: int = 64,
+                 tol: float = 2e-2) -> dict:
+    """`results` = (y, x.grad, router_logits) of one forward + backward of the layer on (x, dy), checked against
+    the CPU oracle (test infrastructure, never on the timed path):
+      routing   : selected experts of EVERY token bit-equal to the oracle's top-k of the layer's own router
+                  logits (ties: lowest expert index first), and the per-expert counts bit-equal to a bincount;
+      y, x.grad : for a seeded sample of tokens, against the fp32 oracle run on those tokens with all expert
+                  weights (a token's output and input gradient depend on its own row only); max |err| / max |ref|.
+    `weights_cpu` = (c_fc [E, 2I, H], c_proj [E, H, I], gate [E, H]) on the host, all experts."""
+    from oracle import moe_oracle as orc
+    from xma.layers.moe import _TopKSoftmax
+
+    w1, w2, gate = weights_cpu
+    E = gate.size(0)
+    y, dx, logits = results
+    torch.cuda.synchronize()
+    with torch.no_grad():
+        _, selected = _TopKSoftmax.apply(logits.detach(), top_k)
+    logits_cpu = logits.detach().cpu()
+    _, ref_selected = orc.route(logits_cpu, top_k)
+    routing_ok = bool(torch.equal(selected.cpu().long(), ref_selected))
+    counts = torch.bincount(selected.flatten().long(), minlength=E).cpu().numpy()
+    counts_ok = bool((counts == orc.continuous_count(ref_selected.numpy(), E)).all())
+
+    T = x.size(0)
+    gen = torch.Generator().manual_seed(4321)
+    pick = torch.unique(torch.cat([torch.tensor([0, T - 1]), torch.randint(0, T, (sample_tokens,), generator=gen)]))
+    f32 = lambda t: t.detach().float().cpu()
+    ref = orc.moe_forward_backward(f32(x[pick.to(x.device)]), gate.float(), w1.float(), w2.float(), top_k, "swiglu",
+                                   dy=f32(dy[pick.to(x.device)]), router_logits=logits_cpu[pick].float())
+    dx_ref = ref.grads["x_experts"] + ref.grads["router_logits"] @ gate.float()
+
+    def rel(got, want):
+        return float((f32(got) - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+    err_y, err_dx = rel(y[pick.to(x.device)], ref.y), rel(dx[pick.to(x.device)], dx_ref)
+    return {"routing_bit_exact": routing_ok, "counts_bit_exact": counts_ok, "tokens_routed": T,
+            "sample_tokens": int(pick.numel()), "y_max_rel_err": err_y, "dx_max_rel_err": err_dx, "tolerance": tol,
+            "ok": routing_ok and counts_ok and err_y <= tol and err_dx <= tol}
+
+
+def secondary_workload(b: Bench, name: str, steps: int) -> dict:
+    """A shorter timed run of another layer shape in the same process, reported as an extra key of the line."""
+    layer, moe, x_dev, dy_dev = build_workload(b, name)
+    r = time_device_resident(b, name, layer, x_dev, dy_dev, steps, 3)
+    w = WORKLOADS[name]
+    peaks, _ = measured_peaks()
     peak = float(peaks.get("bf16_tflops_sustained", PEAK_FALLBACK["bf16_tflops_sustained"]))
+    gemm_tflops = sum(r["gemm_flops"].values()) / (r["gemm_ms_per_step"] * 1e-3) / 1e12 if r["gemm_ms_per_step"] else None
+    out = {"workload": f"{name}: {w['desc']}", "n_gpus": b.world, "steps": steps, "warmup": 3,
+           "ms_per_step": r["ms_per_step"], "tokens_per_s": r["tokens_per_s"],
+           "step_tflops_per_gpu": r["step_tflops_per_gpu"], "step_frac_of_measured_sustained": r["step_tflops_per_gpu"] / peak,
+           "grouped_gemms_tflops": gemm_tflops, "share_outside_gemms": 1.0 - r["gemm_ms_per_step"] / r["ms_per_step"],
+           "efficiency_inputs": {"tokens_per_gpu": w["tokens"], "ms_per_step": r["ms_per_step"], "n_gpus": b.world},
+           "kernels_ms_avg": {k: round(v["ms_avg"], 4) for k, v in r["per_kernel"].items()}}
+    if b.world == 1:
+        out["parity_check"] = parity_check(make_step(layer)(x_dev, dy_dev), gather_expert_weights(b, layer, moe),
+                                           x_dev, dy_dev, w["top_k"], 32)
+    release_layer(b, layer)
+    del layer, moe, x_dev, dy_dev
+    torch.cuda.empty_cache()
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "ep", "swiglu"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the secondary workloads (configs2 / configs3) and the parity check")
+    ap.add_argument("--transport", choices=["peer", "nccl"], default="peer",
+                    help="row exchange of the expert-parallel layer: stores into peer memory, or NCCL all-to-all")
+    ap.add_argument("--unfused-return", dest="fused_return", action="store_false",
+                    help="peer transport: return rows with a separate row kernel instead of the GEMM epilogues")
+    ap.add_argument("--ep-chunks", type=int, default=None,
+                    help="micro-batches per step in the expert-parallel layer (overlap of all-to-all and GEMM)")
+    args = ap.parse_args()
+    if args.workload == "c5":
+        run_routing_microbench(args)
+        return
+    if args.workload == "ep":
+        run_ep_microbench(args)
+        return
+    if args.workload == "swiglu":
+        run_swiglu_microbench(args)
+        return
+    w = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, args.workload)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the B200 kernels are the only implementation (no CPU path)")
+
+    b = Bench(args)
+    rank, world = b.rank, b.world
+    dtype = torch.float32 if w["dtype"] == "f32" else torch.bfloat16
+    E = w["experts"]
+    layer, moe, x_dev, dy_dev = build_workload(b, args.workload)
+
+    # ---- device-resident timing --------------------------------------------------------------
+    sampler = ClockSampler(b.gpu_index())
+    sampler.start()  # nvidia-smi needs a moment to come up; samples are filtered to the timed region
+    r = time_device_resident(b, args.workload, layer, x_dev, dy_dev, args.steps, args.warmup, sampler)
+    clocks = sampler.stop()
+    ms_per_step, per_kernel, gemm_flops = r["ms_per_step"], r["per_kernel"], r["gemm_flops"]
+
+    # ---- end to end: pinned host inputs in, results out, every step ------------------------------
+    e2e = time_end_to_end(b, args.workload, layer, x_dev, dy_dev, args.steps)
+
+    # ---- roofline of the dominant kernel function ----------------------------------------------------
+    peaks, peak_kind = measured_peaks()
+    H, I = w["hidden"], w["inter"]
+    peer = world > 1 and b.transport == "peer" and args.fused_return
+    names = gemm_kernel_names(w, w["tokens"] * w["top_k"], E // world, peer, dtype)
+    # tags launched by the same kernel function are one entry; the one with the largest share gets the roofline
+    functions: dict = {}
+    for tag, fn in names.items():
+        if tag in per_kernel:
+            functions.setdefault(fn, []).append(tag)
+    traffic_rows, traffic_note = load_traffic_table()
+    peak = float(peaks.get("bf16_tflops_sustained", PEAK_FALLBACK["bf16_tflops_sustained"]))
+    sm_mhz = clocks.get("sm_mhz")
     groups = {}
-    for fn, tags in kernel_functions.items():
-        tags = [t for t in tags if t in per_kernel]
-        if not tags:
-            continue
+    for fn, tags in functions.items():
         ms = sum(per_kernel[t]["ms_total"] for t in tags)
         n_launch = sum(per_kernel[t]["launches"] for t in tags)
         flops = sum(gemm_flops[t] * per_kernel[t]["launches"] for t in tags)
         groups[fn] = {"ms_total": ms, "launches": n_launch, "tflops": flops / (ms * 1e-3) / 1e12,
                       "share_of_step": ms / (ms_per_step * args.steps), "tags": tags}
-    roofline = None
-    all_gemms = None
+    roofline = all_gemms = None
     if groups:
         fn = max(groups, key=lambda k: groups[k]["ms_total"])
         g = groups[fn]
         traffic = None
-        if world == 1 and args.workload in ("c2", "c2e2") and all(t in ncu_traffic_c2e2 for t in g["tags"]):
-            scale = E / 2.0
-            traffic = scale * sum(ncu_traffic_c2e2[t] for t in g["tags"]) / len(g["tags"])
+        if traffic_rows is None:
+            traffic_source = traffic_note
+        elif world != 1 or args.workload not in ("c2", "c2e2"):
+            traffic_source = "the ncu table covers the one-GPU c2 / c2e2 shapes only"
+        elif not all(t in traffic_rows for t in g["tags"]):
+            traffic_source = "the ncu table has no row for this kernel"
+        else:
+            traffic = (E / 2.0) * sum(traffic_rows[t] for t in g["tags"]) / len(g["tags"])
+            traffic_source = traffic_note
         roofline = {
             "bound": "tensor", "kernel": fn, "achieved": g["tflops"], "peak": peak, "unit": "TFLOP/s",
             "frac": g["tflops"] / peak, "peak_source": f"{peak_kind} cuBLAS bf16 sustained (kernel timed inside a long step)",
-            "traffic": traffic, "launches_per_step": g["launches"] // args.steps,
+            "traffic": traffic, "traffic_source": traffic_source, "launches_per_step": g["launches"] // args.steps,
             "ms_per_launch": g["ms_total"] / g["launches"], "share_of_step": g["share_of_step"],
             "frac_of_nominal_2250": g["tflops"] / 2250.0,
+            # time x clock compares boxes whose clocks under the power cap differ
+            "ms_per_launch_x_sm_ghz": (g["ms_total"] / g["launches"]) * sm_mhz / 1e3 if sm_mhz else None,
         }
         gemm_ms = sum(g["ms_total"] for g in groups.values())
         achieved = sum(gemm_flops.values()) * args.steps / (gemm_ms * 1e-3) / 1e12
@@ -666,7 +963,15 @@ def main() -> None:
                      "share_of_step": gemm_ms / (ms_per_step * args.steps),
                      "by_kernel": {k: {"tflops": v["tflops"], "share_of_step": v["share_of_step"]}
                                    for k, v in groups.items()}}
-    step_tflops = expert_flops(w, tokens_per_step // world) / (ms_per_step * 1e-3) / 1e12
+
+    # ---- parity of the timed layer against the CPU oracle (outside every timed region) ------------------
+    parity = None
+    if not args.no_extra:
+        results = make_step(layer)(x_dev, dy_dev)  # every rank: the expert-parallel step is collective
+        weights = gather_expert_weights(b, layer, moe)
+        if rank == 0:
+            parity = parity_check(results, weights, x_dev, dy_dev, w["top_k"])
+        del results, weights
 
     # ---- CPU baseline (rank 0, N = 1 only) -----------------------------------------------------------
     cpu = None
@@ -677,35 +982,46 @@ def main() -> None:
                "sample": f"{sample} of {w['tokens']} tokens, full expert shapes, {sec:.1f} s per step, "
                          "oracle/moe_oracle.py on the host cores"}
 
+    parallelism = "single GPU" if world == 1 else (
+        f"expert-parallel ep{world}, "
+        + (("dispatch kernel + GEMM epilogues" if args.fused_return else "dispatch and return kernels")
+           + " storing rows into peer memory over NVLink" if b.transport == "peer" else "NCCL all-to-all")
+        + f", {layer.overlap_chunks} micro-batch(es) per step")
+    release_layer(b, layer)
+    del layer, moe, x_dev, dy_dev
+    torch.cuda.empty_cache()
+
+    # ---- the other layer shapes, shorter runs in the same process ---------------------------------------
+    extra = {}
+    if not args.no_extra and args.workload == "c2":
+        few = max(3, min(args.steps, 5))
+        if world == 1:
+            extra["configs2"] = secondary_workload(b, "c3", few)
+        extra["configs3"] = secondary_workload(b, "c4", few)
+
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC, "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": f"{args.workload}: {w['desc']}", "tokens_per_gpu": w["tokens"],
-                       "hidden": H, "intermediate": I, "experts": E, "top_k": w["top_k"],
-                       "parallelism": "single GPU" if world == 1 else
-                       f"expert-parallel ep{world}, "
-                       + (("dispatch kernel + GEMM epilogues" if args.fused_return else "dispatch and return kernels")
-                          + " storing rows into peer memory over NVLink"
-                          if args.transport == "peer" else "NCCL all-to-all")
-                       + f", {layer.overlap_chunks} micro-batch(es) per step",
+                       "hidden": H, "intermediate": I, "experts": E, "top_k": w["top_k"], "parallelism": parallelism,
                        "l2_policy": "inputs_exceed_l2 (weights + activations >> 126 MB)"},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
-            "gpu_launches": launches,
+            "e2e": e2e,
+            "gpu_launches": r["launches"],
             "roofline": roofline,
             "all_grouped_gemms": all_gemms,
-            "step_tflops_per_gpu": step_tflops,
+            "step_tflops_per_gpu": r["step_tflops_per_gpu"],
+            "step_ms_x_sm_ghz": ms_per_step * sm_mhz / 1e3 if sm_mhz else None,
             "kernels": per_kernel,
+            "parity_check": parity,
             "cpu_baseline": cpu,
         }
+        line.update(extra)
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        if world > 1 and args.transport == "peer":
-            layer.close()  # collective: unmap the other ranks' exchange buffers before anyone frees them
-        dist.destroy_process_group()
+    if b.dist is not None:
+        b.dist.destroy_process_group()
 
 
 if __name__ == "__main__":

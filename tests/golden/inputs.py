@@ -14,7 +14,7 @@ MOE_CASES = {
     "tiny_gelu": (33, 24, 40, 5, 3, "gelu_tanh"),
     "tiny_packed": (37, 32, 16, 4, 2, "swiglu_packed"),
     "empty_experts": (7, 64, 32, 16, 2, "swiglu"),
-    # BASELINE configs[0]: tokens=512, hidden=256, intermediate=512, 8 experts, top-2, fp32, seed 0
+    # the CPU-runnable layer: tokens=512, hidden=256, intermediate=512, 8 experts, top-2, fp32, seed 0
     "config1": (512, 256, 512, 8, 2, "swiglu"),
 }
 

@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
 SIMT, TC, TC_PAIR = 1, 2, 3
 IMPLS = [pytest.param(SIMT, torch.float32, id="cudacore-f32"), pytest.param(SIMT, torch.bfloat16, id="cudacore-bf16"),
          pytest.param(TC, torch.bfloat16, id="tcgen05-bf16"), pytest.param(TC, torch.float16, id="tcgen05-f16"),
-         pytest.param(TC_PAIR, torch.bfloat16, id="pair-bf16"), pytest.param(TC_PAIR, torch.float16, id="pair-f16")]
+         pytest.param(TC_PAIR, torch.bfloat16, id="pair-bf16"), pytest.param(TC_PAIR, torch.float16, id="pair-f16"),
+         pytest.param(0, torch.bfloat16, id="auto-bf16")]
 
 
 def _plan(counts, E):
@@ -42,6 +43,9 @@ CASES = [
     ([128, 256, 3], 192, 512),
     ([300, 7, 0, 0, 129, 64], 576, 264),
     ([1000, 24], 1024, 2048),
+    # experts above 2048 rows: more than one raster group of 16 row tiles (8 tile pairs), odd tile and pair counts
+    ([2049, 300], 128, 512),
+    ([4097, 16384], 192, 768),
 ]
 
 
@@ -93,7 +97,7 @@ def test_rows_gemm_plain_both_layouts(impl, dtype, counts, kd, n):
 
 @pytest.mark.parametrize("impl,dtype", IMPLS)
 @pytest.mark.parametrize("counts,kd,inter", [([5, 0, 130, 1], 64, 128), ([300, 7, 0, 129], 192, 200),
-                                             ([700, 100], 512, 1024)])
+                                             ([700, 100], 512, 1024), ([4097, 2049], 128, 384)])
 def test_rows_gemm_swiglu_epilogues(impl, dtype, counts, kd, inter):
     from xma import _lib, ops
 
@@ -142,7 +146,9 @@ def test_rows_gemm_swiglu_epilogues(impl, dtype, counts, kd, inter):
 
 @pytest.mark.parametrize("impl,dtype", IMPLS)
 @pytest.mark.parametrize("counts,m,n", [([5, 0, 130, 1], 64, 256), ([300, 7, 0, 129], 136, 264),
-                                        ([1000, 24, 64], 512, 384)])
+                                        ([1000, 24, 64], 512, 384),
+                                        # more row tiles than one group of 8 (tiles or tile pairs), ragged last group
+                                        ([300, 0, 70], 2432, 264), ([4097, 2049], 256, 512)])
 def test_dw_gemm(impl, dtype, counts, m, n):
     from xma import _lib, ops
 

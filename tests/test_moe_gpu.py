@@ -103,7 +103,7 @@ def _run_and_compare(name, dtype, impl):
 
 @pytest.mark.parametrize("name", list(gi.MOE_CASES))
 def test_moe_fp32_cuda_cores(name):
-    """fp32 runs on the CUDA-core GEMMs (exact fp32 FMA); configs[0] of the baseline is `config1`."""
+    """fp32 runs on the CUDA-core GEMMs (exact fp32 FMA); `config1` is the CPU-runnable 512-token layer."""
     moe, x, y, logits = _run_and_compare(name, torch.float32, impl=0)
     # against the stored outputs of the reference's torch path
     gold = np.load(os.path.join(GOLDEN, "moe.npz"))

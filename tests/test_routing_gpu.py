@@ -80,7 +80,7 @@ def test_continuous_count_edge_cases():
 
 @pytest.mark.parametrize("dist", ["uniform", "zipf"])
 def test_continuous_count_full_size(dist):
-    """BASELINE configs[4]: 64 Mi int32 ids over 256 bins, uniform and Zipf(1.1)."""
+    """The routing microbench at full size: 64 Mi int32 ids over 256 bins, uniform and Zipf(1.1)."""
     from xma.functional import continuous_count
 
     n = 1 << 26
