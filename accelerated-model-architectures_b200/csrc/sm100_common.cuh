@@ -717,23 +717,31 @@ inline bool cached_map(CUtensorMap* map, int dtype, const void* base, uint64_t i
 }
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: set it on the first launch
-// of each kernel on each device only.
+// of each kernel on each device only. Kernels are told apart by their address (template instances of one
+// signature share a pointer TYPE, so a static per instantiation of this function would not do).
 template <typename K>
 inline int set_dynamic_smem_once(K kernel, size_t bytes) {
+    struct Done {
+        const void* fn;
+        int dev;
+    };
+    constexpr int N = 256;
+    static Done done[N];
+    static int count = 0;
     static std::mutex mu;
-    static bool done[64] = {false};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
-    const bool slot = dev >= 0 && dev < 64;
+    const void* fn = reinterpret_cast<const void*>(kernel);
     {
         std::lock_guard<std::mutex> lock(mu);
-        if (slot && done[dev]) return 0;
+        for (int i = 0; i < count; ++i)
+            if (done[i].fn == fn && done[i].dev == dev) return 0;
     }
     const int rc = static_cast<int>(
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
-    if (rc == 0 && slot) {
+    if (rc == 0 && dev >= 0) {
         std::lock_guard<std::mutex> lock(mu);
-        done[dev] = true;
+        if (count < N) done[count++] = Done{fn, dev};
     }
     return rc;
 }

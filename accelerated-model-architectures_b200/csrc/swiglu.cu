@@ -14,141 +14,233 @@ namespace xma {
 
 constexpr int EW_THREADS = 256;
 
-__device__ __forceinline__ float swiglu_f(float g, float u) { return u * g * sigmoid_f32(g); }
+// Logistic function: exact (expf, IEEE division) for fp32 and fp16 tensors; for bf16 tensors the hardware
+// ex2 / rcp approximations (a few ulp in fp32, three orders of magnitude below the rounding of the bf16 result),
+// which keeps the kernel on the memory roof: with 8 elements per 128-bit packet the exact form is issue-bound.
+// fp16 keeps the exact form because its results are compared with absolute tolerances of one fp16 ulp, where a
+// last-bit difference in fp32 can flip the rounding.
+template <typename T>
+__device__ __forceinline__ float sigmoid_for(float x) {
+    if (sizeof(T) == 4 || TypeInfo<T>::code == XMA_F16) return sigmoid_f32(x);
+    return __fdividef(1.0f, 1.0f + __expf(-x));
+}
 
+template <typename T>
+__device__ __forceinline__ float swiglu_f(float g, float u) {
+    return u * g * sigmoid_for<T>(g);
+}
+
+template <typename T>
 __device__ __forceinline__ void swiglu_b(float g, float u, float dy, float& dg, float& du) {
-    const float s = sigmoid_f32(g);
+    const float s = sigmoid_for<T>(g);
     dg = dy * u * s * (1.0f + g * (1.0f - s));
     du = dy * g * s;
 }
 
-template <typename T, bool VEC>
+// Work items (128-bit packets, or single elements on the scalar path) are numbered row-major; a thread takes
+// EW_UNROLL of them per iteration, all loads issued before the first use. Index arithmetic is 32-bit whenever
+// the item count allows (a 64-bit division per packet costs more than the packet's math).
+constexpr int EW_UNROLL = 2;
+
+template <typename I>
+struct ItemIndex {
+    I cv;
+    __device__ __forceinline__ void split(int64_t i, int64_t& r, int64_t& c) const {
+        const I q = static_cast<I>(i) / cv;
+        r = static_cast<int64_t>(q);
+        c = static_cast<int64_t>(static_cast<I>(i) - q * cv);
+    }
+};
+
+#define XMA_EW_LOOP_BEGIN                                                                                  \
+    constexpr int V = VEC ? Vec16<T>::N : 1;                                                              \
+    const ItemIndex<I> index{static_cast<I>(cols / V)};                                                   \
+    const int64_t total = rows * (cols / V);                                                              \
+    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;                                    \
+    for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i0 < total;            \
+         i0 += step * EW_UNROLL) {                                                                        \
+        int64_t r[EW_UNROLL], c[EW_UNROLL];                                                               \
+        bool on[EW_UNROLL];                                                                               \
+        _Pragma("unroll") for (int k = 0; k < EW_UNROLL; ++k) {                                           \
+            const int64_t i = i0 + k * step;                                                              \
+            on[k] = i < total;                                                                            \
+            index.split(on[k] ? i : 0, r[k], c[k]);                                                       \
+            c[k] *= V;                                                                                    \
+        }
+#define XMA_EW_LOOP_END }
+
+template <typename T, bool VEC, typename I>
 __global__ void __launch_bounds__(EW_THREADS)
 swiglu_fwd_kernel(const T* __restrict__ g, int64_t g_stride, const T* __restrict__ u, int64_t u_stride,
                   T* __restrict__ y, int64_t y_stride, int64_t rows, int64_t cols) {
-    constexpr int V = VEC ? Vec16<T>::N : 1;
-    const int64_t cv = cols / V;
-    const int64_t total = rows * cv;
-    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total; i += step) {
-        const int64_t r = i / cv, c = (i - r * cv) * V;
-        if (VEC) {
-            Vec16<T> a = load16_stream(g + r * g_stride + c);
-            Vec16<T> b = load16_stream(u + r * u_stride + c);
-            Vec16<T> o;
+    XMA_EW_LOOP_BEGIN
+    if (VEC) {
+        Vec16<T> a[EW_UNROLL], b[EW_UNROLL];
 #pragma unroll
-            for (int j = 0; j < Vec16<T>::N; ++j) o.v[j] = from_f32<T>(swiglu_f(to_f32(a.v[j]), to_f32(b.v[j])));
-            store16_stream(y + r * y_stride + c, o);
-        } else {
-            y[r * y_stride + c] = from_f32<T>(swiglu_f(to_f32(g[r * g_stride + c]), to_f32(u[r * u_stride + c])));
-        }
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                a[k] = load16_stream(g + r[k] * g_stride + c[k]);
+                b[k] = load16_stream(u + r[k] * u_stride + c[k]);
+            }
+#pragma unroll
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                Vec16<T> o;
+#pragma unroll
+                for (int j = 0; j < Vec16<T>::N; ++j)
+                    o.v[j] = from_f32<T>(swiglu_f<T>(to_f32(a[k].v[j]), to_f32(b[k].v[j])));
+                store16_stream(y + r[k] * y_stride + c[k], o);
+            }
+    } else {
+#pragma unroll
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k])
+                y[r[k] * y_stride + c[k]] = from_f32<T>(
+                    swiglu_f<T>(to_f32(g[r[k] * g_stride + c[k]]), to_f32(u[r[k] * u_stride + c[k]])));
     }
+    XMA_EW_LOOP_END
 }
 
-template <typename T, bool VEC>
+template <typename T, bool VEC, typename I>
 __global__ void __launch_bounds__(EW_THREADS)
 swiglu_bwd_kernel(const T* __restrict__ g, int64_t g_stride, const T* __restrict__ u, int64_t u_stride,
                   const T* __restrict__ dy, int64_t dy_stride, T* __restrict__ dg, int64_t dg_stride,
                   T* __restrict__ du, int64_t du_stride, int64_t rows, int64_t cols) {
-    constexpr int V = VEC ? Vec16<T>::N : 1;
-    const int64_t cv = cols / V;
-    const int64_t total = rows * cv;
-    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total; i += step) {
-        const int64_t r = i / cv, c = (i - r * cv) * V;
-        if (VEC) {
-            Vec16<T> a = load16_stream(g + r * g_stride + c);
-            Vec16<T> b = load16_stream(u + r * u_stride + c);
-            Vec16<T> d = load16_stream(dy + r * dy_stride + c);
-            Vec16<T> og, ou;
+    XMA_EW_LOOP_BEGIN
+    if (VEC) {
+        Vec16<T> a[EW_UNROLL], b[EW_UNROLL], d[EW_UNROLL];
 #pragma unroll
-            for (int j = 0; j < Vec16<T>::N; ++j) {
-                float x, z;
-                swiglu_b(to_f32(a.v[j]), to_f32(b.v[j]), to_f32(d.v[j]), x, z);
-                og.v[j] = from_f32<T>(x);
-                ou.v[j] = from_f32<T>(z);
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                a[k] = load16_stream(g + r[k] * g_stride + c[k]);
+                b[k] = load16_stream(u + r[k] * u_stride + c[k]);
+                d[k] = load16_stream(dy + r[k] * dy_stride + c[k]);
             }
-            store16_stream(dg + r * dg_stride + c, og);
-            store16_stream(du + r * du_stride + c, ou);
-        } else {
-            float x, z;
-            swiglu_b(to_f32(g[r * g_stride + c]), to_f32(u[r * u_stride + c]), to_f32(dy[r * dy_stride + c]), x, z);
-            dg[r * dg_stride + c] = from_f32<T>(x);
-            du[r * du_stride + c] = from_f32<T>(z);
-        }
+#pragma unroll
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                Vec16<T> og, ou;
+#pragma unroll
+                for (int j = 0; j < Vec16<T>::N; ++j) {
+                    float x, z;
+                    swiglu_b<T>(to_f32(a[k].v[j]), to_f32(b[k].v[j]), to_f32(d[k].v[j]), x, z);
+                    og.v[j] = from_f32<T>(x);
+                    ou.v[j] = from_f32<T>(z);
+                }
+                store16_stream(dg + r[k] * dg_stride + c[k], og);
+                store16_stream(du + r[k] * du_stride + c[k], ou);
+            }
+    } else {
+#pragma unroll
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                float x, z;
+                swiglu_b<T>(to_f32(g[r[k] * g_stride + c[k]]), to_f32(u[r[k] * u_stride + c[k]]),
+                            to_f32(dy[r[k] * dy_stride + c[k]]), x, z);
+                dg[r[k] * dg_stride + c[k]] = from_f32<T>(x);
+                du[r[k] * du_stride + c[k]] = from_f32<T>(z);
+            }
     }
+    XMA_EW_LOOP_END
 }
 
 // Packed: x[r, 2c] = gate, x[r, 2c+1] = up; y[r, c]. `cols` is the width of y.
-template <typename T, bool VEC>
+template <typename T, bool VEC, typename I>
 __global__ void __launch_bounds__(EW_THREADS)
 swiglu_packed_fwd_kernel(const T* __restrict__ x, int64_t x_stride, T* __restrict__ y, int64_t y_stride,
                          int64_t rows, int64_t cols) {
-    constexpr int V = VEC ? Vec16<T>::N : 1;  // outputs per thread step
-    const int64_t cv = cols / V;
-    const int64_t total = rows * cv;
-    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total; i += step) {
-        const int64_t r = i / cv, c = (i - r * cv) * V;
-        if (VEC) {
-            Vec16<T> a = load16_stream(x + r * x_stride + 2 * c);
-            Vec16<T> b = load16_stream(x + r * x_stride + 2 * c + Vec16<T>::N);
-            Vec16<T> o;
+    XMA_EW_LOOP_BEGIN
+    if (VEC) {
+        constexpr int N = Vec16<T>::N;
+        Vec16<T> a[EW_UNROLL], b[EW_UNROLL];
 #pragma unroll
-            for (int j = 0; j < Vec16<T>::N / 2; ++j) {
-                o.v[j] = from_f32<T>(swiglu_f(to_f32(a.v[2 * j]), to_f32(a.v[2 * j + 1])));
-                o.v[j + Vec16<T>::N / 2] = from_f32<T>(swiglu_f(to_f32(b.v[2 * j]), to_f32(b.v[2 * j + 1])));
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                a[k] = load16_stream(x + r[k] * x_stride + 2 * c[k]);
+                b[k] = load16_stream(x + r[k] * x_stride + 2 * c[k] + N);
             }
-            store16_stream(y + r * y_stride + c, o);
-        } else {
-            y[r * y_stride + c] =
-                from_f32<T>(swiglu_f(to_f32(x[r * x_stride + 2 * c]), to_f32(x[r * x_stride + 2 * c + 1])));
-        }
+#pragma unroll
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                Vec16<T> o;
+#pragma unroll
+                for (int j = 0; j < N / 2; ++j) {
+                    o.v[j] = from_f32<T>(swiglu_f<T>(to_f32(a[k].v[2 * j]), to_f32(a[k].v[2 * j + 1])));
+                    o.v[j + N / 2] = from_f32<T>(swiglu_f<T>(to_f32(b[k].v[2 * j]), to_f32(b[k].v[2 * j + 1])));
+                }
+                store16_stream(y + r[k] * y_stride + c[k], o);
+            }
+    } else {
+#pragma unroll
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k])
+                y[r[k] * y_stride + c[k]] = from_f32<T>(swiglu_f<T>(to_f32(x[r[k] * x_stride + 2 * c[k]]),
+                                                                    to_f32(x[r[k] * x_stride + 2 * c[k] + 1])));
     }
+    XMA_EW_LOOP_END
 }
 
-template <typename T, bool VEC>
+template <typename T, bool VEC, typename I>
 __global__ void __launch_bounds__(EW_THREADS)
 swiglu_packed_bwd_kernel(const T* __restrict__ x, int64_t x_stride, const T* __restrict__ dy, int64_t dy_stride,
                          T* __restrict__ dx, int64_t dx_stride, int64_t rows, int64_t cols) {
-    constexpr int V = VEC ? Vec16<T>::N : 1;
-    const int64_t cv = cols / V;
-    const int64_t total = rows * cv;
-    const int64_t step = static_cast<int64_t>(gridDim.x) * EW_THREADS;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total; i += step) {
-        const int64_t r = i / cv, c = (i - r * cv) * V;
-        if (VEC) {
-            Vec16<T> a = load16_stream(x + r * x_stride + 2 * c);
-            Vec16<T> b = load16_stream(x + r * x_stride + 2 * c + Vec16<T>::N);
-            Vec16<T> d = load16_stream(dy + r * dy_stride + c);
-            Vec16<T> oa, ob;
+    XMA_EW_LOOP_BEGIN
+    if (VEC) {
+        constexpr int N = Vec16<T>::N;
+        Vec16<T> a[EW_UNROLL], b[EW_UNROLL], d[EW_UNROLL];
 #pragma unroll
-            for (int j = 0; j < Vec16<T>::N / 2; ++j) {
-                float p, q;
-                swiglu_b(to_f32(a.v[2 * j]), to_f32(a.v[2 * j + 1]), to_f32(d.v[j]), p, q);
-                oa.v[2 * j] = from_f32<T>(p);
-                oa.v[2 * j + 1] = from_f32<T>(q);
-                swiglu_b(to_f32(b.v[2 * j]), to_f32(b.v[2 * j + 1]), to_f32(d.v[j + Vec16<T>::N / 2]), p, q);
-                ob.v[2 * j] = from_f32<T>(p);
-                ob.v[2 * j + 1] = from_f32<T>(q);
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                a[k] = load16_stream(x + r[k] * x_stride + 2 * c[k]);
+                b[k] = load16_stream(x + r[k] * x_stride + 2 * c[k] + N);
+                d[k] = load16_stream(dy + r[k] * dy_stride + c[k]);
             }
-            store16_stream(dx + r * dx_stride + 2 * c, oa);
-            store16_stream(dx + r * dx_stride + 2 * c + Vec16<T>::N, ob);
-        } else {
-            float p, q;
-            swiglu_b(to_f32(x[r * x_stride + 2 * c]), to_f32(x[r * x_stride + 2 * c + 1]),
-                     to_f32(dy[r * dy_stride + c]), p, q);
-            dx[r * dx_stride + 2 * c] = from_f32<T>(p);
-            dx[r * dx_stride + 2 * c + 1] = from_f32<T>(q);
-        }
+#pragma unroll
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                Vec16<T> oa, ob;
+#pragma unroll
+                for (int j = 0; j < N / 2; ++j) {
+                    float p, q;
+                    swiglu_b<T>(to_f32(a[k].v[2 * j]), to_f32(a[k].v[2 * j + 1]), to_f32(d[k].v[j]), p, q);
+                    oa.v[2 * j] = from_f32<T>(p);
+                    oa.v[2 * j + 1] = from_f32<T>(q);
+                    swiglu_b<T>(to_f32(b[k].v[2 * j]), to_f32(b[k].v[2 * j + 1]), to_f32(d[k].v[j + N / 2]), p, q);
+                    ob.v[2 * j] = from_f32<T>(p);
+                    ob.v[2 * j + 1] = from_f32<T>(q);
+                }
+                store16_stream(dx + r[k] * dx_stride + 2 * c[k], oa);
+                store16_stream(dx + r[k] * dx_stride + 2 * c[k] + N, ob);
+            }
+    } else {
+#pragma unroll
+        for (int k = 0; k < EW_UNROLL; ++k)
+            if (on[k]) {
+                float p, q;
+                swiglu_b<T>(to_f32(x[r[k] * x_stride + 2 * c[k]]), to_f32(x[r[k] * x_stride + 2 * c[k] + 1]),
+                            to_f32(dy[r[k] * dy_stride + c[k]]), p, q);
+                dx[r[k] * dx_stride + 2 * c[k]] = from_f32<T>(p);
+                dx[r[k] * dx_stride + 2 * c[k] + 1] = from_f32<T>(q);
+            }
     }
+    XMA_EW_LOOP_END
 }
 
 static int ew_grid(int64_t work_items) {
-    int64_t want = ceil_div(work_items, EW_THREADS);
+    int64_t want = ceil_div(work_items, EW_THREADS * EW_UNROLL);
     int64_t cap = static_cast<int64_t>(num_sms()) * 16;
     return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
 }
+
+// 32-bit item arithmetic when every item index (and one unrolled step beyond the end) fits
+#define XMA_EW_LAUNCH(kernel, vec, items, stream, ...)                                                  \
+    do {                                                                                                \
+        const int64_t n_items = (items);                                                                \
+        if (n_items < (int64_t{1} << 31))                                                               \
+            kernel<T, vec, uint32_t><<<ew_grid(n_items), EW_THREADS, 0, stream>>>(__VA_ARGS__);         \
+        else                                                                                            \
+            kernel<T, vec, uint64_t><<<ew_grid(n_items), EW_THREADS, 0, stream>>>(__VA_ARGS__);         \
+    } while (0)
 
 template <typename T>
 static bool vec_ok(int64_t cols, std::initializer_list<int64_t> strides, std::initializer_list<const void*> ptrs) {
@@ -168,10 +260,9 @@ static int swiglu_fwd_impl(const void* g, int64_t gs, const void* u, int64_t us,
     const T* up = static_cast<const T*>(u);
     T* yp = static_cast<T*>(y);
     if (vec_ok<T>(cols, {gs, us, ys}, {g, u, y}))
-        swiglu_fwd_kernel<T, true><<<ew_grid(rows * cols / Vec16<T>::N), EW_THREADS, 0, st>>>(gp, gs, up, us, yp, ys,
-                                                                                               rows, cols);
+        XMA_EW_LAUNCH(swiglu_fwd_kernel, true, rows * cols / Vec16<T>::N, st, gp, gs, up, us, yp, ys, rows, cols);
     else
-        swiglu_fwd_kernel<T, false><<<ew_grid(rows * cols), EW_THREADS, 0, st>>>(gp, gs, up, us, yp, ys, rows, cols);
+        XMA_EW_LAUNCH(swiglu_fwd_kernel, false, rows * cols, st, gp, gs, up, us, yp, ys, rows, cols);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -185,11 +276,9 @@ static int swiglu_bwd_impl(const void* g, int64_t gs, const void* u, int64_t us,
     T* dgp = static_cast<T*>(dg);
     T* dup = static_cast<T*>(du);
     if (vec_ok<T>(cols, {gs, us, dys, dgs, dus}, {g, u, dy, dg, du}))
-        swiglu_bwd_kernel<T, true><<<ew_grid(rows * cols / Vec16<T>::N), EW_THREADS, 0, st>>>(
-            gp, gs, up, us, dyp, dys, dgp, dgs, dup, dus, rows, cols);
+        XMA_EW_LAUNCH(swiglu_bwd_kernel, true, rows * cols / Vec16<T>::N, st, gp, gs, up, us, dyp, dys, dgp, dgs, dup, dus, rows, cols);
     else
-        swiglu_bwd_kernel<T, false><<<ew_grid(rows * cols), EW_THREADS, 0, st>>>(gp, gs, up, us, dyp, dys, dgp, dgs,
-                                                                                 dup, dus, rows, cols);
+        XMA_EW_LAUNCH(swiglu_bwd_kernel, false, rows * cols, st, gp, gs, up, us, dyp, dys, dgp, dgs, dup, dus, rows, cols);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -199,10 +288,9 @@ static int swiglu_packed_fwd_impl(const void* x, int64_t xs, void* y, int64_t ys
     const T* xp = static_cast<const T*>(x);
     T* yp = static_cast<T*>(y);
     if (vec_ok<T>(cols, {xs, ys}, {x, y}))
-        swiglu_packed_fwd_kernel<T, true><<<ew_grid(rows * cols / Vec16<T>::N), EW_THREADS, 0, st>>>(xp, xs, yp, ys,
-                                                                                                      rows, cols);
+        XMA_EW_LAUNCH(swiglu_packed_fwd_kernel, true, rows * cols / Vec16<T>::N, st, xp, xs, yp, ys, rows, cols);
     else
-        swiglu_packed_fwd_kernel<T, false><<<ew_grid(rows * cols), EW_THREADS, 0, st>>>(xp, xs, yp, ys, rows, cols);
+        XMA_EW_LAUNCH(swiglu_packed_fwd_kernel, false, rows * cols, st, xp, xs, yp, ys, rows, cols);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -213,11 +301,9 @@ static int swiglu_packed_bwd_impl(const void* x, int64_t xs, const void* dy, int
     const T* dyp = static_cast<const T*>(dy);
     T* dxp = static_cast<T*>(dx);
     if (vec_ok<T>(cols, {xs, dys, dxs}, {x, dy, dx}))
-        swiglu_packed_bwd_kernel<T, true><<<ew_grid(rows * cols / Vec16<T>::N), EW_THREADS, 0, st>>>(
-            xp, xs, dyp, dys, dxp, dxs, rows, cols);
+        XMA_EW_LAUNCH(swiglu_packed_bwd_kernel, true, rows * cols / Vec16<T>::N, st, xp, xs, dyp, dys, dxp, dxs, rows, cols);
     else
-        swiglu_packed_bwd_kernel<T, false><<<ew_grid(rows * cols), EW_THREADS, 0, st>>>(xp, xs, dyp, dys, dxp, dxs,
-                                                                                        rows, cols);
+        XMA_EW_LAUNCH(swiglu_packed_bwd_kernel, false, rows * cols, st, xp, xs, dyp, dys, dxp, dxs, rows, cols);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -3,6 +3,7 @@
 Importing this package loads libxma_b200.so; it raises if the library has not been built."""
 
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is missing)
+from ._lib import check_device_status
 from .accelerator import Accelerator, KernelBackend
 from .utils import set_seed
 from . import functional, layers  # noqa: E402

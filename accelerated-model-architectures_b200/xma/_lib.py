@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int64, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 
 import torch
 
@@ -72,6 +72,12 @@ _SIGNATURES = {
     "xma_b200_swiglu_packed_fwd": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p],
     "xma_b200_swiglu_packed_bwd": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64,
                                    c_int64, c_void_p],
+    "xma_b200_rmsnorm_fwd": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                             c_void_p, c_int, c_int64, c_int64, c_float, c_float, c_void_p],
+    "xma_b200_rmsnorm_bwd_partial_rows": [c_int64],
+    "xma_b200_rmsnorm_bwd": [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                             c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int64, c_int64, c_float, c_float,
+                             c_void_p],
     "xma_b200_ep_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                          c_void_p, c_int64, c_void_p, c_void_p],
     "xma_b200_ep_dispatch": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
@@ -175,14 +181,28 @@ def read_and_clear_device_status(device: torch.device | None = None) -> int:
     return value
 
 
+def describe_device_status(value: int) -> str:
+    names = []
+    if value & DEV_ID_OUT_OF_RANGE:
+        names.append("expert/bin id or peer row word out of range")
+    if value & DEV_WAIT_TIMEOUT:
+        names.append("bounded device-side wait expired")
+    if value & DEV_BAD_TILE:
+        names.append("inconsistent tile table")
+    return f"xma_b200 device status {value}: " + ", ".join(names)
+
+
+def check_device_status(device: torch.device | None = None) -> None:
+    """Synchronises `device` (default: the current one) and raises if any kernel of this library flagged an
+    asynchronous condition since the last check: an id or row word out of range that was skipped, a
+    bounded wait that expired (the kernel left tiles unwritten), an inconsistent tile table. Results
+    computed while the word was non-zero are undefined. The kernels never stop a training loop by
+    themselves, so call this where a host synchronisation is acceptable (once per optimizer step, say), or set
+    XMA_B200_CHECK_STATUS=1 to have `MoE.forward` check after every call."""
+    raise_on_device_status(device)
+
+
 def raise_on_device_status(device: torch.device | None = None) -> None:
     value = read_and_clear_device_status(device)
     if value:
-        names = []
-        if value & DEV_ID_OUT_OF_RANGE:
-            names.append("expert/bin id out of range")
-        if value & DEV_WAIT_TIMEOUT:
-            names.append("bounded device-side wait expired")
-        if value & DEV_BAD_TILE:
-            names.append("inconsistent tile table")
-        raise RuntimeError(f"xma_b200 device status {value}: " + ", ".join(names))
+        raise RuntimeError(describe_device_status(value))

@@ -48,7 +48,8 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import ops
-from ._lib import EPI_DSWIGLU, EPI_PLAIN, EPI_SWIGLU, ROW_PAD, W_KN, W_NK, check, lib
+from ._lib import (EPI_DSWIGLU, EPI_PLAIN, EPI_SWIGLU, ROW_PAD, W_KN, W_NK, check, describe_device_status, lib,
+                   status_word)
 from .layers.moe import MoE, _FusedSwiGLUExperts, _plan_tensors, _TopKSoftmax, build_route_plan, SwiGLU
 
 
@@ -139,8 +140,12 @@ def _host_words(words: torch.Tensor):
     the copy engine behind bulk downloads of earlier steps."""
     if not words.is_cuda:
         return words.numpy().astype(np.int64)
+    shape = tuple(words.shape)
+    # the device status word rides along: this is the one host synchronisation of a step, so it is where a skipped
+    # row, an expired wait or a bad tile table of the previous step's kernels surfaces as an exception
+    status = status_word(words.device)
+    words = torch.cat([words.reshape(-1), status])
     n = words.numel()
-    words = words.contiguous()
     pinned = _PINNED.get(words.device)
     if pinned is None or pinned.numel() < n:
         pinned = _PINNED[words.device] = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
@@ -149,7 +154,11 @@ def _host_words(words: torch.Tensor):
     done = torch.cuda.Event()
     done.record(stream)
     done.synchronize()
-    return pinned[:n].numpy().reshape(tuple(words.shape)).astype(np.int64)
+    host = pinned[:n].numpy().astype(np.int64)
+    if host[-1]:
+        status.zero_()
+        raise RuntimeError(describe_device_status(int(host[-1])) + " (results since the last check are undefined)")
+    return host[:-1].reshape(shape)
 
 
 # ---- peer-memory transport ---------------------------------------------------------------------------
@@ -428,7 +437,7 @@ class ExpertParallelMoE(nn.Module):
         ranks' memory from their own epilogues (GEMM and exchange are one kernel; the tile is staged in
         shared memory so that each row leaves in 128-byte pieces); False runs a separate row kernel."""
         super().__init__()
-        if not (isinstance(local_moe.act, SwiGLU) and local_moe.is_glu):
+        if not (getattr(local_moe.act, "xma_fused_activation", None) == "swiglu" and local_moe.is_glu):
             raise ValueError("ExpertParallelMoE runs the fused SwiGLU expert block")
         if transport not in ("nccl", "peer"):
             raise ValueError("transport must be 'nccl' or 'peer'")

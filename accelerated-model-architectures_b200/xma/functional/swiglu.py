@@ -17,6 +17,15 @@ def _rows(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous()
 
 
+def _as_rows(t: torch.Tensor) -> torch.Tensor:
+    """Any shape the elementwise reference accepts -> [rows, last dimension] (0-D and 1-D become one row)."""
+    if t.dim() == 2:
+        return t
+    if t.dim() < 2:
+        return t.reshape(1, -1)
+    return t.flatten(0, -2)
+
+
 class _Swiglu(torch.autograd.Function):
     @staticmethod
     def forward(ctx, g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
@@ -72,8 +81,7 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor, *, kernel_backend: KernelBacken
         raise RuntimeError("xma.functional.swiglu (B200 build) needs CUDA tensors; there is no CPU path")
 
     original_shape = gate.size()
-    gate = gate.flatten(0, -2) if gate.dim() != 2 else gate
-    up = up.flatten(0, -2) if up.dim() != 2 else up
+    gate, up = _as_rows(gate), _as_rows(up)
 
     y = _Swiglu.apply(gate, up)
     return y.view(original_shape)
@@ -94,7 +102,21 @@ def swiglu_packed(x: torch.Tensor, *, kernel_backend: KernelBackend | None = Non
     original_shape = x.size()
     if original_shape[-1] % 2 != 0:
         raise ValueError(f"{original_shape[-1]} is not divisible by 2")
-    x = x.flatten(0, -2) if x.dim() != 2 else x
+    x = _as_rows(x)
 
     y = _SwigluPacked.apply(x)
     return y.view(*original_shape[:-1], original_shape[-1] // 2)
+
+
+def swiglu_chunked(x: torch.Tensor, *, kernel_backend: KernelBackend | None = None) -> torch.Tensor:
+    """`swiglu(*x.chunk(2, dim=-1))`: gate = first half of the last dimension, up = second half. The usual way to
+    give `xma.layers.MoE` a SwiGLU activation; unlike a lambda around `swiglu`, the layer can recognise this
+    function (and `swiglu_packed`) by the tag below and fuse it into its GEMM epilogues."""
+    gate, up = x.chunk(2, dim=-1)
+    return swiglu(gate, up, kernel_backend=kernel_backend)
+
+
+# `MoE` fuses an activation_function that carries one of these tags (a plain attribute, so user code can tag
+# its own equivalent callable): "swiglu" = gate | up halves, "swiglu_packed" = gate, up interleaved.
+swiglu_chunked.xma_fused_activation = "swiglu"
+swiglu_packed.xma_fused_activation = "swiglu_packed"

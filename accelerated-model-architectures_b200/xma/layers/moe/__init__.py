@@ -12,6 +12,8 @@ down projection is not recomputed (its unweighted output is kept for d_router_we
 
 from __future__ import annotations
 
+import os
+import warnings
 from dataclasses import dataclass
 from typing import Callable
 
@@ -20,7 +22,7 @@ import torch.nn as nn
 
 from ... import ops
 from ..._lib import (EPI_DSWIGLU, EPI_DSWIGLU_PACKED, EPI_PLAIN, EPI_SWIGLU, EPI_SWIGLU_PACKED, IMPL_SIMT, ROW_PAD,
-                     W_KN, W_NK, dtype_code, lib)
+                     W_KN, W_NK, dtype_code, lib, raise_on_device_status)
 from ...accelerator import KernelBackend, resolve_kernel_backend
 from ...functional import swiglu, swiglu_packed
 
@@ -30,6 +32,8 @@ class SwiGLU(nn.Module):
     instance as `activation_function` (with `is_glu=True`) lets `MoE` fuse the activation into the
     epilogue of the up-projection GEMM; called on its own it runs the stand-alone kernel."""
 
+    xma_fused_activation = "swiglu"
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         gate, up = x.chunk(2, dim=-1)
         return swiglu(gate, up)
@@ -37,6 +41,8 @@ class SwiGLU(nn.Module):
 
 class SwiGLUPacked(nn.Module):
     """`swiglu_packed(x)`: gate/up interleaved along the feature dimension."""
+
+    xma_fused_activation = "swiglu_packed"
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return swiglu_packed(x)
@@ -298,6 +304,10 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         return d_x, d_w1, d_w2, d_rw, None, None, None, None, None, None
 
 
+# XMA_B200_CHECK_STATUS=1: `MoE.forward` reads the device status word after every call (one host synchronisation)
+_CHECK_STATUS = os.environ.get("XMA_B200_CHECK_STATUS", "0") not in ("", "0")
+
+
 class Experts(nn.Module):
     """Per-expert linear weights `[num_experts, out_features, in_features]`; same parameters and
     buffers as the reference (xma/layers/moe/__init__.py:22-43, 112-119) so state dicts interchange."""
@@ -367,6 +377,7 @@ class MoE(nn.Module):
             std=std,
         )
         self.is_glu = is_glu
+        self._probed = False
 
     def forward(self, x: torch.Tensor, *, kernel_backend: KernelBackend | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         resolve_kernel_backend(kernel_backend)
@@ -378,7 +389,38 @@ class MoE(nn.Module):
         router_logits, router_weights, selected_experts = self._compute_routing_weights(x)
         x = self._compute_experts(x, router_weights, selected_experts)
         x = x.view(original_shape)
+        if _CHECK_STATUS and not torch.compiler.is_compiling():
+            raise_on_device_status(x.device)  # synchronises; off by default (see xma.check_device_status)
         return x, router_logits
+
+    def _fused_activation(self, x: torch.Tensor) -> str | None:
+        """"swiglu" / "swiglu_packed" when the activation is one the GEMM epilogues implement: recognised by its
+        `xma_fused_activation` tag (`xma.layers.SwiGLU`, `SwiGLUPacked`, `xma.functional.swiglu_chunked`,
+        `swiglu_packed`). An untagged callable (a lambda around `swiglu`, say) cannot be recognised by looking
+        at it; the first eager call evaluates it on 4 x 16 probe values and warns if it computes SwiGLU, because
+        it then runs as GEMM -> stand-alone kernel -> GEMM instead of the fused path."""
+        if not self.is_glu:
+            return None
+        tag = getattr(self.act, "xma_fused_activation", None)
+        if tag in ("swiglu", "swiglu_packed"):
+            return tag
+        if not self._probed and not torch.compiler.is_compiling():
+            self._probed = True
+            try:
+                with torch.no_grad():
+                    probe = torch.linspace(-3.0, 3.0, 64, device=x.device, dtype=torch.float32).view(4, 16)
+                    got = self.act(probe)
+                    for name, fn in (("swiglu_chunked", lambda h: swiglu(*h.chunk(2, dim=-1))),
+                                     ("swiglu_packed", swiglu_packed)):
+                        if got.shape == (4, 8) and torch.allclose(got, fn(probe), rtol=1e-5, atol=1e-6):
+                            warnings.warn(
+                                f"xma.layers.MoE: activation_function computes SwiGLU but is not tagged, so it runs "
+                                f"unfused; pass xma.functional.{name} (or xma.layers.SwiGLU / SwiGLUPacked, or set "
+                                f"`.xma_fused_activation` on the callable) to fuse it into the grouped GEMMs",
+                                stacklevel=3)
+            except Exception:  # an activation that rejects the probe is simply not SwiGLU
+                pass
+        return None
 
     def _compute_routing_weights(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         # x -> (total_q, hidden_size)
@@ -409,9 +451,10 @@ class MoE(nn.Module):
         plan = build_route_plan(selected_experts, self.num_experts)
         tensors = _plan_tensors(plan)
 
-        if isinstance(self.act, SwiGLU) and self.is_glu:
+        fused = self._fused_activation(x)
+        if fused == "swiglu":
             return _FusedSwiGLUExperts.apply(x, self.c_fc.weight, self.c_proj.weight, router_weights, *tensors)
-        if isinstance(self.act, SwiGLUPacked) and self.is_glu and self._tensor_cores(x):
+        if fused == "swiglu_packed" and self._tensor_cores(x):
             # the interleaved epilogues exist on the tensor-core kernels only
             return _FusedSwiGLUExperts.apply(x, self.c_fc.weight, self.c_proj.weight, router_weights, *tensors, True)
 

@@ -300,6 +300,36 @@ def _swiglu_packed_bwd_op(x: Tensor, dy: Tensor, dx: Tensor) -> None:
     )
 
 
+@torch.library.custom_op(f"{_NS}::rmsnorm_fwd", mutates_args={"y", "xr", "rstd"}, device_types="cuda")
+def _rmsnorm_fwd_op(x: Tensor, residual: Optional[Tensor], weight: Optional[Tensor], y: Tensor, xr: Optional[Tensor],
+                    rstd: Optional[Tensor], eps: float, multiplier: float) -> None:
+    require_cuda(x, residual, weight, y, xr, rstd)
+    check(
+        lib.xma_b200_rmsnorm_fwd(
+            ptr(x), _row_stride(x), ptr(residual), 0 if residual is None else _row_stride(residual), ptr(weight),
+            ptr(y), _row_stride(y), ptr(xr), 0 if xr is None else _row_stride(xr), ptr(rstd), dtype_code(x.dtype),
+            x.size(0), x.size(1), eps, multiplier, current_stream(x.device)
+        ),
+        "xma_b200_rmsnorm_fwd",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::rmsnorm_bwd", mutates_args={"dx", "dr", "dw_partial"}, device_types="cuda")
+def _rmsnorm_bwd_op(xr: Tensor, weight: Optional[Tensor], dy: Tensor, dxr: Optional[Tensor], rstd: Optional[Tensor],
+                    dx: Tensor, dr: Optional[Tensor], dw_partial: Optional[Tensor], eps: float,
+                    multiplier: float) -> None:
+    require_cuda(xr, weight, dy, dxr, rstd, dx, dr, dw_partial)
+    check(
+        lib.xma_b200_rmsnorm_bwd(
+            ptr(xr), _row_stride(xr), ptr(weight), ptr(dy), _row_stride(dy), ptr(dxr),
+            0 if dxr is None else _row_stride(dxr), ptr(rstd), ptr(dx), _row_stride(dx), ptr(dr),
+            0 if dr is None else _row_stride(dr), ptr(dw_partial), 0 if dw_partial is None else dw_partial.size(0),
+            dtype_code(xr.dtype), xr.size(0), xr.size(1), eps, multiplier, current_stream(xr.device)
+        ),
+        "xma_b200_rmsnorm_bwd",
+    )
+
+
 # ---- launch accounting and per-kernel timing ------------------------------------------------------
 class KernelStats:
     """Counts the kernels this library launches and, when `timing` is on, brackets every op with
@@ -357,6 +387,8 @@ swiglu_fwd_ = _wrap(_swiglu_fwd_op, "swiglu_fwd", 1)
 swiglu_bwd_ = _wrap(_swiglu_bwd_op, "swiglu_bwd", 1)
 swiglu_packed_fwd_ = _wrap(_swiglu_packed_fwd_op, "swiglu_packed_fwd", 1)
 swiglu_packed_bwd_ = _wrap(_swiglu_packed_bwd_op, "swiglu_packed_bwd", 1)
+rmsnorm_fwd_ = _wrap(_rmsnorm_fwd_op, "rmsnorm_fwd", 1)
+rmsnorm_bwd_ = _wrap(_rmsnorm_bwd_op, "rmsnorm_bwd", 1)
 
 
 # Kernel-family override for the grouped GEMMs (tests, tuning): 0 automatic, 1 CUDA cores,

@@ -214,6 +214,31 @@ int xma_b200_swiglu_packed_bwd(const void* x, int64_t x_row_stride, const void* 
                                void* dx, int64_t dx_row_stride, int dtype, int64_t rows, int64_t out_cols,
                                cudaStream_t stream);
 
+/* ---- fused residual add + RMSNorm (the step in front of the MoE layer) ----------------------- */
+
+/* v = x * multiplier + residual (residual NULL: v = x * multiplier), rounded to the storage type;
+ * xr = v (written when xr != NULL; required when residual != NULL); rstd[r] = rsqrt(mean(v[r]^2) + eps)
+ * (written when rstd != NULL); y = v * rstd * weight (weight NULL: 1). fp32 arithmetic, one rounding per output.
+ * Replaces fused_residual_add_rmsnorm and its Triton forward:
+ *   xma/functional/fused_residual_add_rmsnorm/__init__.py:27-83, template.py:12-34,
+ *   triton_implementation/forward.py. */
+int xma_b200_rmsnorm_fwd(const void* x, int64_t x_row_stride, const void* residual, int64_t residual_row_stride,
+                         const void* weight, void* y, int64_t y_row_stride, void* xr, int64_t xr_row_stride,
+                         float* rstd, int dtype, int64_t rows, int64_t cols, float eps, float multiplier,
+                         cudaStream_t stream);
+/* Backward of the above, given xr (the value the norm saw), dy and optionally d(xr) (gradient that arrives
+ * through the residual stream) and rstd (NULL: recomputed from xr):
+ *   z = xr * rstd, g = dy * weight, d = (g - z * mean(g * z)) * rstd + dxr;  dresidual = d (when != NULL),
+ *   dx = d * multiplier,  dweight_partial[b, :] = sum over the rows CTA b handled of dy * z  (fp32,
+ *   [partial_rows, cols] with partial_rows = xma_b200_rmsnorm_bwd_partial_rows(rows); the caller sums over b).
+ * Replaces template.py:37-84 and triton_implementation/backward.py:15-150 (same partial-sum scheme). */
+int xma_b200_rmsnorm_bwd_partial_rows(int64_t rows);
+int xma_b200_rmsnorm_bwd(const void* xr, int64_t xr_row_stride, const void* weight, const void* dy,
+                         int64_t dy_row_stride, const void* dxr, int64_t dxr_row_stride, const float* rstd, void* dx,
+                         int64_t dx_row_stride, void* dresidual, int64_t dresidual_row_stride, float* dweight_partial,
+                         int partial_rows, int dtype, int64_t rows, int64_t cols, float eps, float multiplier,
+                         cudaStream_t stream);
+
 /* ---- expert parallelism over peer memory ------------------------------------------------------ */
 /* None of these has a counterpart in the reference (single-device MoE, xma/layers/moe/__init__.py:144-160).
  * Rank r of `world` owns experts [r * E / world, (r + 1) * E / world). An owner keeps the rows it receives

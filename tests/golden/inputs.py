@@ -22,6 +22,16 @@ COUNT_CASES = {"n1": (1, 72), "n33": (33, 72), "n1024_e8": (1024, 8), "n4099": (
 
 SWIGLU_CASES = {"s17x24": (17, 24), "s64x128": (64, 128), "s5x3": (5, 3)}
 
+# name -> (rows, cols, residual, weight, multiplier)
+RMSNORM_CASES = {
+    "r9x7": (9, 7, True, True, 0.9),
+    "r33x64": (33, 64, True, True, None),
+    "r12x100_noweight": (12, 100, True, False, 0.9),
+    "r8x256_noresidual": (8, 256, False, True, None),
+    "r5x3000": (5, 3000, True, True, 0.9),
+}
+RMSNORM_EPS = 1e-5
+
 
 def moe_inputs(name: str, dtype: torch.dtype = torch.float32, seed: int = 0):
     """x ~ N(0,1); gate and expert weights ~ N(0, 0.02); dy ~ N(0,1). Values are rounded to `dtype`
@@ -55,6 +65,19 @@ def swiglu_inputs(name: str, seed: int = 7):
     g = torch.from_numpy(rng.randint(-8, 8, size=(rows, cols)).astype(np.float32))
     u = torch.from_numpy(rng.randint(-8, 8, size=(rows, cols)).astype(np.float32))
     return g, u
+
+
+def rmsnorm_inputs(name: str, seed: int = 11):
+    """x, residual ~ N(0,1); weight ~ N(1, 0.1); upstream gradients of both outputs ~ N(0,1)."""
+    rows, cols, has_r, has_w, multiplier = RMSNORM_CASES[name]
+    rng = np.random.RandomState(seed)
+    f = lambda a: torch.from_numpy(a.astype(np.float32))
+    x = f(rng.standard_normal((rows, cols)))
+    r = f(rng.standard_normal((rows, cols))) if has_r else None
+    w = f(1.0 + 0.1 * rng.standard_normal(cols)) if has_w else None
+    dy = f(rng.standard_normal((rows, cols)))
+    dxr = f(rng.standard_normal((rows, cols))) if has_r else None
+    return dict(x=x, residual=r, weight=w, dy=dy, dxr=dxr, multiplier=multiplier)
 
 
 def sample(t: torch.Tensor, limit: int = 4096) -> np.ndarray:

@@ -72,13 +72,36 @@ def summarize(prefix: str, t: torch.Tensor, out: dict) -> None:
     out[prefix + ".shape"] = np.array(t.shape, dtype=np.int64)
 
 
-def main(root: str) -> None:
+def main(root: str, only: str | None = None) -> None:
     ref = load_reference(root)
     from xma_ref.functional import continuous_count, swiglu, swiglu_packed
     from xma_ref.layers import MoE
 
     KB = ref.KernelBackend.torch
     torch.set_num_threads(max(1, (os.cpu_count() or 2) // 2))
+
+    # ---- fused_residual_add_rmsnorm (forward and gradients for given upstream gradients) ----------
+    from xma_ref.functional import fused_residual_add_rmsnorm
+
+    out = {}
+    for name in gi.RMSNORM_CASES:
+        inp = gi.rmsnorm_inputs(name)
+        x = inp["x"].clone().requires_grad_()
+        r = None if inp["residual"] is None else inp["residual"].clone().requires_grad_()
+        w = None if inp["weight"] is None else inp["weight"].clone().requires_grad_()
+        y, xr = fused_residual_add_rmsnorm(x, r, w, gi.RMSNORM_EPS, inp["multiplier"], kernel_backend=KB)
+        loss = (y * inp["dy"]).sum()
+        if xr is not None:
+            loss = loss + (xr * inp["dxr"]).sum()
+        loss.backward()
+        out[name + ".y"], out[name + ".dx"] = y.detach().numpy(), x.grad.numpy()
+        if xr is not None:
+            out[name + ".xr"], out[name + ".dr"] = xr.detach().numpy(), r.grad.numpy()
+        if w is not None:
+            out[name + ".dw"] = w.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "rmsnorm.npz"), **out)
+    if only == "rmsnorm":
+        return
 
     # ---- continuous_count -------------------------------------------------------------------
     out = {}
@@ -145,6 +168,6 @@ def main(root: str) -> None:
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: make_golden.py <path-to-reference-checkout>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        sys.exit("usage: make_golden.py <path-to-reference-checkout> [rmsnorm]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

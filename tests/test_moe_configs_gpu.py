@@ -68,7 +68,9 @@ def test_layer_parity_at_benchmark_shape(name):
     assert np.array_equal(plan.pad_offsets.cpu().numpy(), srt.pad_offsets)
     assert np.array_equal(plan.tile_prefix.cpu().numpy(), srt.tile_prefix)
     assert np.array_equal(plan.row_src.cpu().numpy()[:used], srt.row_src)
-    assert torch.equal(rw.cpu(), ref_weights)  # softmax over the selected logits, rounded once
+    # routing weights are floating point: softmax over the selected logits in fp32, rounded once to the
+    # storage type; the device's exp may differ from the host's in the last place, i.e. one bf16 step (2^-8 relative)
+    torch.testing.assert_close(rw.float().cpu(), ref_weights.float(), rtol=2.0 ** -7, atol=1e-7)
 
     # (c) weight gradients of single experts, all of their rows, a strided subset of the intermediate features
     counts = srt.counts.astype(np.int64)

@@ -173,23 +173,33 @@ def test_moe_reference_grid_shape():
     torch.testing.assert_close(f32(moe.c_proj.weight.grad), ref.grads["c_proj"], rtol=0, atol=7.9e-3)
 
 
+_GRID = [(E, K, 2048, 8192) for E in (2, 4, 6, 8) for K in (2, 4) if K <= E] + [(128, 8, 576, 256), (4, 1, 2048, 8192)]
+# every point runs eagerly; these also run under torch.compile(fullgraph=True), as the reference's grid does
+_COMPILED = {(4, 2, 2048, 8192), (8, 4, 2048, 8192), (128, 8, 576, 256), (4, 1, 2048, 8192)}
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("num_experts,top_k", [(2, 2), (6, 2), (6, 4)])
+@pytest.mark.parametrize("num_experts,top_k,H,I", _GRID)
 @pytest.mark.parametrize("is_glu", [True, False])
-def test_moe_reference_grid(dtype, num_experts, top_k, is_glu):
-    """The reference's own MoE test (tests/layers/moe_test.py:26-157) on a subset of its grid: 7 tokens,
-    hidden 2048, intermediate 8192, nn.GLU / GELU(tanh), `y.sum().backward()`, its absolute tolerances
-    (rtol 0), gate gradients not compared - with the CPU oracle in the place of its torch path."""
+@pytest.mark.parametrize("compiled", [False, True])
+def test_moe_reference_grid(dtype, num_experts, top_k, H, I, is_glu, compiled):
+    """The reference's own MoE test (tests/layers/moe_test.py:26-157) on its grid: 7 tokens; E in {2,4,6,8} x
+    K in {2,4} at hidden 2048 / intermediate 8192, and E=128, K=8 at 576 / 256; three dtypes; nn.GLU /
+    GELU(tanh); eager and compiled; `y.sum().backward()`; its absolute tolerances (rtol 0); gate gradients not
+    compared - with the CPU oracle in the place of its torch path. One more point, K=1, takes the `.max`
+    branch of the reference's top-k (xma/layers/moe/__init__.py:256-260)."""
     import torch.nn as nn
 
     from xma.layers import MoE
 
-    H, I = 2048, 8192
+    if compiled and (num_experts, top_k, H, I) not in _COMPILED:
+        pytest.skip("compiled on a subset of the grid")
     torch.manual_seed(42)
     act = nn.GLU() if is_glu else nn.GELU(approximate="tanh")
     moe = MoE(num_experts, top_k, H, I, act, is_glu, False, 0.02).to(device="cuda", dtype=dtype)
     x = torch.randn(7, H, device="cuda", dtype=dtype, requires_grad=True)
-    y, logits = moe(x)
+    module = torch.compile(moe, fullgraph=True) if compiled else moe
+    y, logits = module(x)
     y.sum().backward()
     # like the reference test, both sides run in `dtype`: the oracle is the torch path's arithmetic in
     # that dtype on the CPU (the tolerances were chosen for a comparison between two `dtype` results)
@@ -225,3 +235,41 @@ def test_moe_empty_batch():
     y.sum().backward()
     assert x.grad.shape == (0, 64)
     assert float(moe.c_fc.weight.grad.abs().max()) == 0.0 and float(moe.c_proj.weight.grad.abs().max()) == 0.0
+
+
+def test_tagged_activation_is_fused_and_lambda_warns():
+    """`xma.functional.swiglu_chunked` / `swiglu_packed` (or any callable tagged `xma_fused_activation`) take the
+    fused GEMM epilogues, bit for bit like `xma.layers.SwiGLU`; an untagged lambda that computes SwiGLU runs the
+    generic path (same result within rounding) and warns once."""
+    import warnings
+
+    from xma import ops
+    from xma.functional import swiglu, swiglu_chunked, swiglu_packed
+    from xma.layers import MoE, SwiGLU, SwiGLUPacked
+
+    torch.manual_seed(1)
+    x = torch.randn(300, 128, device="cuda", dtype=torch.bfloat16)
+
+    def run(act):
+        torch.manual_seed(2)
+        moe = MoE(8, 2, 128, 256, act, True, False, 0.02).to(device="cuda", dtype=torch.bfloat16)
+        ops.STATS.enabled, ops.STATS.timing = True, False
+        ops.STATS.reset()
+        try:
+            y, _ = moe(x)
+        finally:
+            ops.STATS.enabled = False
+        return y, ops.STATS.launches
+
+    y_cls, n_cls = run(SwiGLU())
+    y_fn, n_fn = run(swiglu_chunked)
+    assert torch.equal(y_cls, y_fn) and n_cls == n_fn
+    y_pcls, n_pcls = run(SwiGLUPacked())
+    y_pfn, n_pfn = run(swiglu_packed)
+    assert torch.equal(y_pcls, y_pfn) and n_pcls == n_pfn
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        y_lambda, n_lambda = run(lambda h: swiglu(*h.chunk(2, dim=-1)))
+    assert any("runs unfused" in str(w.message) for w in caught)
+    assert n_lambda == n_cls + 1  # the stand-alone activation kernel between the two GEMMs
+    torch.testing.assert_close(y_lambda.float(), y_cls.float(), rtol=2e-2, atol=2e-3)

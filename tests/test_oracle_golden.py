@@ -114,3 +114,23 @@ def test_route_tie_rule():
     w, sel = orc.route(logits, 2)
     assert sel.tolist() == [[1, 2], [0, 1]]
     assert torch.allclose(w, torch.full((2, 2), 0.5))
+
+
+@pytest.mark.parametrize("name", list(gi.RMSNORM_CASES))
+def test_rmsnorm_oracle_matches_reference(name):
+    """fused_residual_add_rmsnorm: the float64 restatement against the reference's fp32 torch path."""
+    from oracle import rmsnorm_oracle as rn
+
+    gold = np.load(os.path.join(GOLDEN, "rmsnorm.npz"))
+    inp = gi.rmsnorm_inputs(name)
+    np_ = lambda t: None if t is None else t.numpy()
+    x, r, w = np_(inp["x"]), np_(inp["residual"]), np_(inp["weight"])
+    y, xr, _ = rn.forward(x, r, w, gi.RMSNORM_EPS, inp["multiplier"])
+    dx, dr, dw = rn.backward(x, r, w, gi.RMSNORM_EPS, inp["multiplier"], np_(inp["dy"]), np_(inp["dxr"]))
+    np.testing.assert_allclose(y, gold[name + ".y"], rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(dx, gold[name + ".dx"], rtol=2e-5, atol=5e-6)
+    if r is not None:
+        np.testing.assert_allclose(xr, gold[name + ".xr"], rtol=1e-6, atol=1e-6)
+        np.testing.assert_allclose(dr, gold[name + ".dr"], rtol=2e-5, atol=5e-6)
+    if w is not None:
+        np.testing.assert_allclose(dw, gold[name + ".dw"], rtol=2e-5, atol=2e-5)
