@@ -3,8 +3,8 @@
 //   * route_topk_softmax (+ backward): top-k over router logits and softmax over the k picked
 //     values (xma/layers/moe/__init__.py:182-195, 256-262)
 //   * count_sort : replaces `selected_experts.flatten().sort()` + continuous_count + cumsum
-//     (xma/layers/moe/__init__.py:210-217) by a stable counting sort: histogram -> table kernel
-//     -> one-pass scatter whose cross-tile prefix is a decoupled look-back scan.
+//     (xma/layers/moe/__init__.py:210-217) by a stable counting sort: per-tile histograms -> table
+//     kernel -> single-pass scan over the tiles (decoupled look-back) -> stable scatter.
 //
 // Integer outputs are bit-exact functions of the input: counts equal bincount, the permutation is
 // the stable ascending order (ties by flat index), top-k ties go to the lowest expert index.
@@ -169,14 +169,23 @@ __global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __r
 }
 
 // ------------------------------------------------------------------------------------------------
-// Stable scatter with a decoupled look-back scan
+// Stable counting sort: per-tile histograms -> scan over the tiles (decoupled look-back) -> scatter
 // ------------------------------------------------------------------------------------------------
+// The ids are cut into tiles of SORT_TILE. Pass 1 counts every bin per tile (and the global counts); the
+// exclusive scan of those counts down the tiles, bin by bin, tells each tile where its share of a bin starts;
+// pass 2 ranks the ids of a tile and writes them there. The scan is a single pass with a decoupled look-back
+// between chunks of SCAN_TILES tiles. The look-back sits here, on 4 bytes per tile and bin, and not inside
+// pass 2 (where the first version had it, one status word per tile and bin): a look-back front advances a
+// fixed number of status words per round trip to L2, so with one word per 8192-id tile the whole 64 Mi-id
+// sort was bounded by about 500 such round trips per bin chain (1 ms) whatever the occupancy.
 constexpr int SORT_THREADS = 512;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 constexpr int SORT_ITEMS = 16;
 constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 8192 ids per CTA
-constexpr int LB_BATCH = 16;                          // predecessors fetched per look-back round
 constexpr int SORT_MAX_BINS = 1024;
+constexpr int SCAN_TILES = 64;    // tiles per chunk of the scan
+constexpr int SCAN_THREADS = 256;
+constexpr int LB_BATCH = 8;       // predecessors fetched per look-back round
 
 // Look-back status word: [63:62] state, [31:0] value. One 64-bit store/load moves both at once,
 // so no fence is needed between flag and payload.
@@ -196,118 +205,131 @@ __host__ __device__ inline size_t sort_smem_bytes(int E) {
     return (b + 15) & ~static_cast<size_t>(15);
 }
 
-__host__ __device__ inline size_t sort_scratch_bytes(int64_t n, int E) {
+// Scratch of one count_sort call (the caller's memory, zeroed by the call before use):
+//   [0, 256)            ticket counter of the scan kernel
+//   tile_counts         [tiles][E] u32   per-tile counts, turned into exclusive prefixes inside the chunk
+//   chunk_base          [chunks][E] u32  sorted position of the chunk's first id of the bin
+//   lb                  [chunks][E] u64  look-back status words of the scan
+struct SortScratch {
+    unsigned* ticket;
+    unsigned* tile_counts;
+    unsigned* chunk_base;
+    unsigned long long* lb;
+    size_t bytes;
+};
+
+__host__ __device__ inline SortScratch sort_scratch_layout(unsigned char* base, int64_t n, int E) {
     int64_t tiles = (n + SORT_TILE - 1) / SORT_TILE;
     if (tiles < 1) tiles = 1;
-    return 256 + static_cast<size_t>(tiles) * E * sizeof(unsigned long long);
+    const int64_t chunks = (tiles + SCAN_TILES - 1) / SCAN_TILES;
+    SortScratch s;
+    size_t off = 256;
+    s.ticket = reinterpret_cast<unsigned*>(base);
+    s.tile_counts = reinterpret_cast<unsigned*>(base + off);
+    off += static_cast<size_t>(tiles) * E * sizeof(unsigned);
+    s.chunk_base = reinterpret_cast<unsigned*>(base + off);
+    off += static_cast<size_t>(chunks) * E * sizeof(unsigned);
+    off = (off + 7) & ~static_cast<size_t>(7);
+    s.lb = reinterpret_cast<unsigned long long*>(base + off);
+    off += static_cast<size_t>(chunks) * E * sizeof(unsigned long long);
+    s.bytes = off;
+    return s;
 }
 
-// The scratch area starts with the dynamic tile counter (256 bytes reserved), followed by
-// status[tile][bin]. The whole area must be zero when the kernel starts.
-//
-// Per tile of SORT_TILE ids: every warp loads its 512 contiguous ids row by row (coalesced), ranks
-// them (peer masks from per-bit votes) against its own per-bin counters (stable: rows in order, lanes in order),
-// then one thread per bin scans the warps, publishes the tile's count and looks back over the
-// earlier tiles for the bin's running total. The tile is then sorted locally into shared memory (one
-// packed word per id: position in the tile and bin), so that each bin's run leaves the CTA as
-// consecutive addresses: scattering straight from registers would touch one 32-byte sector per id.
+__host__ __device__ inline size_t sort_scratch_bytes(int64_t n, int E) {
+    return sort_scratch_layout(nullptr, n, E).bytes;
+}
+
+// Pass 1. Each CTA takes whole tiles: counts them in `copies` shared-memory histograms (one per group of
+// warps, which spreads same-bin contention: the MoE layer feeds nearly sorted ids), writes the tile's counts
+// and keeps a running total per bin that goes to the global counters once at the end.
 template <typename IdT>
-__global__ void __launch_bounds__(SORT_THREADS, 2)
-sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __restrict__ offsets_incl,
-                    const int* __restrict__ pad_offsets, int* __restrict__ sorted_expert,
-                    int* __restrict__ sorted_scattered, int* __restrict__ row_src,
-                    unsigned char* __restrict__ scratch, int* __restrict__ status) {
-    extern __shared__ __align__(16) unsigned char s_raw[];
-    unsigned* s_staged = reinterpret_cast<unsigned*>(s_raw);          // [TILE] (index in tile << 16) | bin
-    unsigned* s_warp_cnt = s_staged + SORT_TILE;                      // [WARPS][E+1]
-    unsigned* s_bin_first = s_warp_cnt + SORT_WARPS * (E + 1);        // [E+1] start of each bin inside the tile
-    int* s_dst_base = reinterpret_cast<int*>(s_bin_first + (E + 1));  // [E] global position - position in tile
-    int* s_pad_delta = s_dst_base + E;                                // [E] padded row - sorted row
-    unsigned* s_scan = reinterpret_cast<unsigned*>(s_pad_delta + E);  // [32]
-    unsigned* s_tile = s_scan + 32;
-
-    unsigned* tile_counter = reinterpret_cast<unsigned*>(scratch);
-    unsigned long long* lb = reinterpret_cast<unsigned long long*>(scratch + 256);
-
+__global__ void __launch_bounds__(SORT_THREADS)
+tile_histogram_kernel(const IdT* __restrict__ ids, int64_t n, int E, int copies, unsigned* __restrict__ tile_counts,
+                      unsigned* __restrict__ counts, int* __restrict__ status) {
+    extern __shared__ unsigned s_hist[];  // [copies][E] + totals [E]
+    unsigned* s_total = s_hist + copies * E;
     const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    const int EB = E + 1;  // bin E collects ids that are out of range (dropped)
-
-    if (tid == 0) *s_tile = atomicAdd(tile_counter, 1u);
-    for (int i = tid; i < SORT_WARPS * EB; i += SORT_THREADS) s_warp_cnt[i] = 0u;
+    for (int i = tid; i < (copies + 1) * E; i += SORT_THREADS) s_hist[i] = 0u;
     __syncthreads();
-    const unsigned tile = *s_tile;
-    const int64_t base = static_cast<int64_t>(tile) * SORT_TILE;
-    if (base >= n) return;  // uniform for the CTA
-    const int cnt = static_cast<int>((n - base) < SORT_TILE ? (n - base) : SORT_TILE);
-
-    // 1. load (16 independent coalesced loads per thread) and rank
-    unsigned my_bin[SORT_ITEMS];
-    unsigned peers[SORT_ITEMS];
+    unsigned* my = s_hist + ((tid >> 5) % copies) * E;
+    const int64_t tiles = (n + SORT_TILE - 1) / SORT_TILE;
+    constexpr int V = 16 / sizeof(IdT);
+    const bool aligned = (reinterpret_cast<uintptr_t>(ids) & 15u) == 0;
     bool bad = false;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int64_t base = tile * SORT_TILE;
+        const int cnt = static_cast<int>((n - base) < SORT_TILE ? (n - base) : SORT_TILE);
+        if (aligned && cnt == SORT_TILE) {
+            Vec16<IdT> q[SORT_ITEMS / V];
 #pragma unroll
-    for (int r = 0; r < SORT_ITEMS; ++r) {
-        const int i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
-        unsigned b = static_cast<unsigned>(E);
-        if (i < cnt) {
-            const IdT id = __ldcs(ids + base + i);
-            if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(E)) b = static_cast<unsigned>(id);
-            else bad = true;
+            for (int j = 0; j < SORT_ITEMS / V; ++j) q[j] = load16_stream(ids + base + (j * SORT_THREADS + tid) * V);
+#pragma unroll
+            for (int j = 0; j < SORT_ITEMS / V; ++j)
+#pragma unroll
+                for (int i = 0; i < V; ++i) hist_add<IdT, true>(q[j].v[i], E, my, nullptr, bad);
+        } else {
+            for (int i = tid; i < cnt; i += SORT_THREADS) hist_add<IdT, true>(ids[base + i], E, my, nullptr, bad);
         }
-        my_bin[r] = b;
-    }
-    // Lanes holding the same bin, from one ballot per bit of the bin index (the native match
-    // instruction is several times slower than log2(E) votes).
-    int bits = 1;
-    while ((1 << bits) <= E) ++bits;  // bins 0..E (E = dropped) need this many bits
-#pragma unroll
-    for (int r = 0; r < SORT_ITEMS; ++r) {
-        unsigned m = 0xffffffffu;
-#pragma unroll
-        for (int k = 0; k < 11; ++k) {
-            if (k < bits) {
-                const bool bit = (my_bin[r] >> k) & 1u;
-                const unsigned vote = __ballot_sync(0xffffffffu, bit);
-                m &= bit ? vote : ~vote;
+        __syncthreads();
+        for (int b = tid; b < E; b += SORT_THREADS) {
+            unsigned sum = 0;
+            for (int c = 0; c < copies; ++c) {
+                sum += s_hist[c * E + b];
+                s_hist[c * E + b] = 0u;
             }
+            tile_counts[tile * E + b] = sum;
+            s_total[b] += sum;
         }
-        peers[r] = m;
+        __syncthreads();
     }
+    for (int b = tid; b < E; b += SORT_THREADS)
+        if (s_total[b]) atomicAdd(&counts[b], s_total[b]);
+    if (bad && status) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
+}
 
-    // from here on my_bin[r] holds bin | (rank inside the warp's 512 ids) << 16
-    unsigned* wc = s_warp_cnt + warp * EB;
-    const unsigned lt_mask = (1u << lane) - 1u;
+// Scan of one chunk of tiles, bin `b`: tile_counts[t][b] becomes the number of ids of bin b in the chunk's
+// earlier tiles; returns the chunk's total. Eight independent loads at a time.
+__device__ __forceinline__ unsigned scan_chunk_bin(unsigned* __restrict__ tile_counts, int64_t t0, int64_t t1, int E,
+                                                   int b) {
+    unsigned run = 0;
+    for (int64_t t = t0; t < t1; t += 8) {
+        unsigned v[8];
 #pragma unroll
-    for (int r = 0; r < SORT_ITEMS; ++r) {
-        const unsigned b = my_bin[r];
-        const unsigned before = wc[b];
-        __syncwarp();
-        if ((peers[r] & lt_mask) == 0u) wc[b] = before + __popc(peers[r]);
-        __syncwarp();
-        my_bin[r] = b | ((before + __popc(peers[r] & lt_mask)) << 16);
+        for (int j = 0; j < 8; ++j) v[j] = (t + j < t1) ? tile_counts[(t + j) * E + b] : 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (t + j < t1) tile_counts[(t + j) * E + b] = run;
+            run += v[j];
+        }
     }
+    return run;
+}
+
+// Scan over the tiles, one chunk of SCAN_TILES tiles per CTA, chunk ids handed out by an atomic ticket (so a
+// waiting chunk only waits on chunks that are resident). Per bin: scan the chunk, publish its total, look back
+// over the earlier chunks (LB_BATCH status words per round, independent loads) until one that already knows
+// its inclusive prefix, publish the own inclusive prefix. chunk_base = bin's first sorted position + prefix.
+// The wait is bounded: after LB_MAX_POLLS empty rounds the chunk sets status bit 2 and goes on with prefix 0.
+__global__ void __launch_bounds__(SCAN_THREADS)
+tile_scan_kernel(SortScratch sc, int64_t tiles, int E, const int* __restrict__ offsets_incl,
+                 int* __restrict__ status) {
+    __shared__ unsigned s_chunk;
+    if (threadIdx.x == 0) s_chunk = atomicAdd(sc.ticket, 1u);
     __syncthreads();
-
-    // 2. per bin: exclusive scan over warps, publish the tile aggregate, look back for the prefix,
-    //    fold the bin's global base into the warp counters
-    for (int b = tid; b < E; b += SORT_THREADS) {
-        unsigned run = 0;
-#pragma unroll
-        for (int w = 0; w < SORT_WARPS; ++w) {
-            const unsigned t = s_warp_cnt[w * EB + b];
-            s_warp_cnt[w * EB + b] = run;
-            run += t;
-        }
-        unsigned long long* mine = lb + static_cast<size_t>(tile) * E + b;
+    const int64_t chunk = s_chunk;
+    const int64_t t0 = chunk * SCAN_TILES;
+    if (t0 >= tiles) return;
+    const int64_t t1 = (t0 + SCAN_TILES < tiles) ? t0 + SCAN_TILES : tiles;
+    for (int b = threadIdx.x; b < E; b += SCAN_THREADS) {
+        const unsigned run = scan_chunk_bin(sc.tile_counts, t0, t1, E, b);
+        unsigned long long* mine = sc.lb + static_cast<size_t>(chunk) * E + b;
         unsigned excl = 0;
-        if (tile == 0) {
+        if (chunk == 0) {
             atomicExch(mine, LB_PREFIX | run);
         } else {
             atomicExch(mine, LB_AGGREGATE | run);
-            // Walk back over the predecessors, LB_BATCH status words per round (independent loads),
-            // adding aggregates until a tile that already knows its inclusive prefix is met.
-            int64_t prev = static_cast<int64_t>(tile) - 1;
+            int64_t prev = chunk - 1;
             unsigned polls = 0;
             bool gave_up = false, done = false;
             while (!done) {
@@ -315,8 +337,9 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
 #pragma unroll
                 for (int j = 0; j < LB_BATCH; ++j) {
                     const int64_t t = prev - j;
-                    unsigned long long word = 2ull << 62;  // beyond tile 0: an empty prefix
-                    if (t >= 0) word = *reinterpret_cast<volatile unsigned long long*>(lb + static_cast<size_t>(t) * E + b);
+                    unsigned long long word = LB_PREFIX;  // beyond chunk 0: an empty prefix
+                    if (t >= 0)
+                        word = *reinterpret_cast<volatile unsigned long long*>(sc.lb + static_cast<size_t>(t) * E + b);
                     v[j] = word;
                 }
                 int used = 0;
@@ -330,7 +353,7 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
                     if (st == LB_PREFIX) done = true;
                 }
                 prev -= used;
-                if (!done && used < LB_BATCH) {  // ran into a tile that has not published yet
+                if (!done && used < LB_BATCH) {  // ran into a chunk that has not published yet
                     if (++polls > LB_MAX_POLLS) {
                         gave_up = true;
                         break;
@@ -345,9 +368,105 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
             atomicExch(mine, LB_PREFIX | static_cast<unsigned long long>(excl + run));
         }
         const unsigned gbase = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
-        s_bin_first[b] = run;                                   // tile count for now, scanned below
-        s_dst_base[b] = static_cast<int>(gbase + excl);         // minus the bin's start in the tile, below
-        s_pad_delta[b] = pad_offsets[b] - static_cast<int>(gbase);
+        sc.chunk_base[static_cast<size_t>(chunk) * E + b] = gbase + excl;
+    }
+}
+
+// Pass 2, one tile of SORT_TILE ids per CTA: every warp loads its 512 contiguous ids row by row (coalesced)
+// and ranks them against its own per-bin counters (stable: rows in order, lanes in order); one thread per bin
+// scans the warps and fetches the bin's base for this tile from the scanned tables. The tile is then sorted
+// locally into shared memory (one packed word per id: position in the tile and bin), so that each bin's run
+// leaves the CTA as consecutive addresses: scattering straight from registers would touch one 32-byte
+// sector per id. No CTA waits for another.
+template <typename IdT>
+__global__ void __launch_bounds__(SORT_THREADS, 3)
+sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __restrict__ offsets_incl,
+                    const int* __restrict__ pad_offsets, int* __restrict__ sorted_expert,
+                    int* __restrict__ sorted_scattered, int* __restrict__ row_src, SortScratch sc,
+                    int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    unsigned* s_staged = reinterpret_cast<unsigned*>(s_raw);          // [TILE] (index in tile << 16) | bin
+    unsigned* s_warp_cnt = s_staged + SORT_TILE;                      // [WARPS][E+1]
+    unsigned* s_bin_first = s_warp_cnt + SORT_WARPS * (E + 1);        // [E+1] start of each bin inside the tile
+    int* s_dst_base = reinterpret_cast<int*>(s_bin_first + (E + 1));  // [E] global position - position in tile
+    int* s_pad_delta = s_dst_base + E;                                // [E] padded row - sorted row
+    unsigned* s_scan = reinterpret_cast<unsigned*>(s_pad_delta + E);  // [32]
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int EB = E + 1;  // bin E collects ids that are out of range (dropped)
+
+    for (int i = tid; i < SORT_WARPS * EB; i += SORT_THREADS) s_warp_cnt[i] = 0u;
+    __syncthreads();
+    const int64_t tile = blockIdx.x;
+    const int64_t base = tile * SORT_TILE;
+    if (base >= n) return;  // uniform for the CTA
+    const int cnt = static_cast<int>((n - base) < SORT_TILE ? (n - base) : SORT_TILE);
+
+    // 1. load (16 independent coalesced loads per thread) and rank
+    unsigned my_bin[SORT_ITEMS];
+    bool bad = false;
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; ++r) {
+        const int i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
+        unsigned b = static_cast<unsigned>(E);
+        if (i < cnt) {
+            const IdT id = __ldcs(ids + base + i);
+            if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(E)) b = static_cast<unsigned>(id);
+            else bad = true;
+        }
+        my_bin[r] = b;
+    }
+    // Rank of every id inside its warp's 512 ids (rows in order, lanes in order: stable). Per row of 32 ids:
+    // the lanes holding the same bin come from one ballot per bit of the bin index (the native match
+    // instruction is several times slower than log2(E) votes); the lowest of them adds the group's size to the
+    // warp's counter of that bin with a shared-memory atomic, whose return value - the count of the rows
+    // before - reaches the group by shuffle (one atomic, one shuffle and one warp barrier per row; the first
+    // version went through a read, two warp barriers and a write).
+    // From here on my_bin[r] holds bin | (rank inside the warp's 512 ids) << 16.
+    int bits = 1;
+    while ((1 << bits) <= E) ++bits;  // bins 0..E (E = dropped) need this many bits
+    unsigned* wc = s_warp_cnt + warp * EB;
+    const unsigned lt_mask = (1u << lane) - 1u;
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; ++r) {
+        const unsigned b = my_bin[r];
+        unsigned m = 0xffffffffu;
+#pragma unroll
+        for (int k = 0; k < 11; ++k) {
+            if (k < bits) {
+                const bool bit = (b >> k) & 1u;
+                const unsigned vote = __ballot_sync(0xffffffffu, bit);
+                m &= bit ? vote : ~vote;
+            }
+        }
+        const int leader = __ffs(m) - 1;
+        unsigned before = 0;
+        if (lane == leader) before = atomicAdd(&wc[b], static_cast<unsigned>(__popc(m)));
+        before = __shfl_sync(0xffffffffu, before, leader);
+        my_bin[r] = b | ((before + __popc(m & lt_mask)) << 16);
+        __syncwarp();  // orders this row's atomics before the next row's, whichever lanes issue them
+    }
+    __syncthreads();
+
+    // 2. per bin: exclusive scan over warps; the bin's base for this tile comes from the scanned tables
+    const unsigned* tile_excl = sc.tile_counts + static_cast<size_t>(tile) * E;
+    const unsigned* chunk_base = sc.chunk_base + static_cast<size_t>(tile / SCAN_TILES) * E;
+    for (int b = tid; b < E; b += SORT_THREADS) {
+        const unsigned first = chunk_base[b] + tile_excl[b];  // sorted position of the tile's first id of bin b
+        const unsigned gbase = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
+        const int pad0 = pad_offsets[b];
+        unsigned run = 0;
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; ++w) {
+            const unsigned t = s_warp_cnt[w * EB + b];
+            s_warp_cnt[w * EB + b] = run;
+            run += t;
+        }
+        s_bin_first[b] = run;                          // tile count for now, scanned below
+        s_dst_base[b] = static_cast<int>(first);       // minus the bin's start in the tile, below
+        s_pad_delta[b] = pad0 - static_cast<int>(gbase);
     }
     __syncthreads();
 
@@ -586,24 +705,35 @@ int count_sort_impl(const IdT* ids, int64_t n, int E, uint32_t* counts, int* off
                     int* tile_prefix, int* tile_expert, int64_t tile_cap, int* sorted_expert, int* sorted_scattered,
                     int* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes, int* device_status,
                     cudaStream_t stream) {
-    int rc = xma::launch_histogram(ids, n, E, counts, device_status, stream);
-    if (rc) return rc;
+    XMA_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(uint32_t) * E, stream));
+    const int64_t tiles = xma::ceil_div(n, xma::SORT_TILE);
+    const xma::SortScratch sc = xma::sort_scratch_layout(static_cast<unsigned char*>(scratch), n, E);
+    if (n > 0) {
+        XMA_CUDA_TRY(cudaMemsetAsync(scratch, 0, sc.bytes, stream));
+        int copies = static_cast<int>((40 * 1024) / (static_cast<int64_t>(E) * sizeof(unsigned)));
+        copies = copies < 1 ? 1 : (copies > xma::SORT_WARPS ? xma::SORT_WARPS : copies);
+        const int64_t cap = static_cast<int64_t>(xma::num_sms()) * 4;
+        const int grid = static_cast<int>(tiles < cap ? tiles : cap);
+        xma::tile_histogram_kernel<IdT><<<grid, xma::SORT_THREADS, static_cast<size_t>(copies + 1) * E * sizeof(unsigned),
+                                         stream>>>(ids, n, E, copies, sc.tile_counts, counts, device_status);
+        XMA_CUDA_TRY(cudaGetLastError());
+    }
     xma::plan_kernel<<<1, 256, 0, stream>>>(counts, E, offsets_incl, pad_offsets, tile_prefix, tile_expert,
                                             static_cast<int>(tile_cap), row_src, device_status);
     XMA_CUDA_TRY(cudaGetLastError());
     (void)row_cap;
     if (n == 0) return XMA_OK;
-    const size_t need = xma::sort_scratch_bytes(n, E);
-    XMA_CUDA_TRY(cudaMemsetAsync(scratch, 0, need, stream));
+    const int64_t chunks = xma::ceil_div(tiles, static_cast<int64_t>(xma::SCAN_TILES));
+    xma::tile_scan_kernel<<<static_cast<int>(chunks), xma::SCAN_THREADS, 0, stream>>>(sc, tiles, E, offsets_incl,
+                                                                                      device_status);
+    XMA_CUDA_TRY(cudaGetLastError());
     const size_t smem = xma::sort_smem_bytes(E);
     auto kernel = xma::sort_scatter_kernel<IdT>;
     if (smem > 48 * 1024) {
         XMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     }
-    const int64_t tiles = xma::ceil_div(n, xma::SORT_TILE);
     kernel<<<static_cast<int>(tiles), xma::SORT_THREADS, smem, stream>>>(
-        ids, n, E, offsets_incl, pad_offsets, sorted_expert, sorted_scattered, row_src,
-        static_cast<unsigned char*>(scratch), device_status);
+        ids, n, E, offsets_incl, pad_offsets, sorted_expert, sorted_scattered, row_src, sc, device_status);
     (void)scratch_bytes;
     return static_cast<int>(cudaGetLastError());
 }
@@ -716,10 +846,10 @@ int xma_b200_route_topk_softmax_bwd(const void* logits, int dtype, int64_t logit
 // ================================================================================================
 // Some hosts of this library must not allocate device memory while they run: a serving engine that
 // has handed its whole memory budget to a pool at start-up, or a step that sits between other
-// frameworks' allocators and may not disturb them. For those callers the look-back scan's scratch
-// lives in this fixed array instead of a caller buffer. Every GPU that loads the library holds it
-// until the process exits.
-#define XMA_STATIC_SORT_SCRATCH_BYTES (256 + 256 * 256 * 8) /* tile counter + 256 tiles x 256 experts */
+// frameworks' allocators and may not disturb them. For those callers the sort's scratch (per-tile
+// counts and the look-back words of the scan over them) lives in this fixed array instead of a caller
+// buffer. Every GPU that loads the library holds it until the process exits.
+#define XMA_STATIC_SORT_SCRATCH_BYTES (256 + 256 * 256 * 8) /* e.g. 480 tiles of 8192 ids x 256 experts */
 
 static __device__ __align__(256) unsigned char g_static_sort_scratch[XMA_STATIC_SORT_SCRATCH_BYTES];
 
@@ -739,7 +869,9 @@ int64_t xma_b200_count_sort_static_scratch_limit(void) { return XMA_STATIC_SORT_
 // fixed device array. Nothing is allocated or freed, here or in anything this calls.
 //  - The first call on each device looks up the array's device address (the name is only a host-side
 //    handle, not an address a kernel could use) with that device current; make that first call
-//    before any stream capture begins.
+//    before any stream capture begins. With CUDA's lazy module loading that first use may also be the
+//    moment the driver loads this library's code and the array onto the device (a driver-side
+//    allocation of the module image): issue it at start-up, before a pool takes the memory budget.
 //  - All calls on a device share the one array. It is cleared at the start of every call; two calls
 //    whose kernels overlap on the GPU (different streams, no ordering) would corrupt each other.
 //  - Problems whose scratch exceeds the limit are refused with XMA_ERR_TOO_LARGE.

@@ -41,6 +41,7 @@ every call.
 from __future__ import annotations
 
 import ctypes
+import weakref
 
 import numpy as np
 import torch
@@ -269,13 +270,34 @@ class _Exchange:
     came from; `home_rows` [home_cap, H]: expert outputs returned to this rank, one row per token slot.
     `*_table`: int64 [W] device tensors with every rank's address of the same buffer."""
 
-    def __init__(self, link, device: torch.device, dtype: torch.dtype, hidden: int, fused_return: bool) -> None:
+    def __init__(self, link, device: torch.device, dtype: torch.dtype, hidden: int, fused_return: bool,
+                 private_copies: bool = False) -> None:
         self.link, self.device, self.dtype, self.hidden = link, device, dtype, hidden
         self.fused_return = fused_return
+        self.private_copies = private_copies
         self.recv_cap = self.home_cap = 0
         self._held: list = []
         self.recv_rows = self.recv_meta = self.home_rows = None
         self.recv_table = self.meta_table = self.home_table = None
+        # Without private copies the forward's received rows and returned rows stay in the exchange buffers
+        # until the backward has read them, and the backward exchanges through a second pair of buffers.
+        self.recv_rows_bwd = self.home_rows_bwd = None
+        self.recv_table_bwd = self.home_table_bwd = None
+        self._in_use = None  # weak reference to the forward whose tensors live in the buffers
+
+    def claim(self, owner) -> None:
+        """The forward `owner` is about to fill the forward buffers. An earlier forward whose backward has not
+        run yet still needs them: peers would overwrite its rows, and no local copy could be ordered before
+        their stores without one more barrier, so that use is refused."""
+        if self.private_copies:
+            return
+        previous = self._in_use() if self._in_use is not None else None
+        if previous is not None and not previous.done:
+            raise RuntimeError(
+                "ExpertParallelMoE(transport='peer'): a second forward started before the backward of the previous "
+                "one; its saved rows live in the exchange buffers. Construct the layer with private_copies=True "
+                "to run several forwards before their backwards (one extra copy of the received and returned rows)")
+        self._in_use = weakref.ref(owner) if owner is not None else None
 
     def _shared(self, nbytes: int):
         block, addresses, mapped = self.link.share(nbytes, self.device)
@@ -298,10 +320,18 @@ class _Exchange:
         self.recv_meta = raw.view(torch.int32)
         raw, self.home_table = self._shared(self.home_cap * self.hidden * item)
         self.home_rows = raw.view(self.dtype).view(self.home_cap, self.hidden)
+        if self.private_copies:
+            self.recv_rows_bwd, self.recv_table_bwd = self.recv_rows, self.recv_table
+            self.home_rows_bwd, self.home_table_bwd = self.home_rows, self.home_table
+        else:
+            raw, self.recv_table_bwd = self._shared(self.recv_cap * self.hidden * item)
+            self.recv_rows_bwd = raw.view(self.dtype).view(self.recv_cap, self.hidden)
+            raw, self.home_table_bwd = self._shared(self.home_cap * self.hidden * item)
+            self.home_rows_bwd = raw.view(self.dtype).view(self.home_cap, self.hidden)
 
     def close(self) -> None:
         """Collective."""
-        self.recv_rows = self.recv_meta = self.home_rows = None
+        self.recv_rows = self.recv_meta = self.home_rows = self.recv_rows_bwd = self.home_rows_bwd = None
         for block, mapped in self._held:
             self.link.release(block, mapped)
         self._held = []
@@ -322,6 +352,17 @@ class _PeerRoute:
                      self.tile_expert, exchange.recv_meta)
 
 
+class _KeptRows:
+    """Tensors of one forward that the backward reads: the rows this rank's experts received (`xs`) and the
+    expert outputs returned to this rank (`ys`): private copies, or views of the exchange buffers."""
+
+    __slots__ = ("xs", "ys", "done", "__weakref__")
+
+    def __init__(self) -> None:
+        self.xs = self.ys = None
+        self.done = False
+
+
 class _PeerSwiGLUExperts(torch.autograd.Function):
     """The fused SwiGLU expert block with the experts sharded over the ranks: dispatch and combine are
     stores into the other ranks' exchange buffers (see the module docstring)."""
@@ -338,13 +379,19 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
         rows = route.rows                              # padded rows of this rank's experts in use
         alloc = route.tile_expert.numel() * ROW_PAD    # grouped buffers span the whole tile table
 
+        kept = _KeptRows() if any(ctx.needs_input_grad) else None
+        exchange.claim(kept)
         ops.ep_dispatch_(x, sorted_expert_idxs, sorted_scattered_idxs, None, K, route.send_delta, route.world,
                          route.rank, exchange.recv_table, exchange.meta_table, exchange.recv_cap)
         link.barrier()
 
-        xs = torch.empty(alloc, H, **opts)
         meta = exchange.recv_meta[:alloc].clone()
-        ops.ep_copy_rows_(exchange.recv_rows, meta, xs[:rows])
+        if exchange.private_copies:
+            xs = torch.empty(alloc, H, **opts)
+            ops.ep_copy_rows_(exchange.recv_rows, meta, xs[:rows])
+        else:
+            xs = exchange.recv_rows[:alloc]
+            ops.ep_copy_rows_(xs, meta, xs[:rows])  # in place: zero the pad rows (nobody else writes them)
         gu = torch.empty(alloc, two_i, **opts)
         act = torch.empty(alloc, I, **opts)
         ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, route.tile_expert, route.tile_prefix, H, two_i,
@@ -360,20 +407,22 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
             ops.ep_return_(out[:rows], meta, route.world, exchange.home_table, exchange.home_cap)
         link.barrier()
 
-        ys = exchange.home_rows[:R].clone()
+        ys = exchange.home_rows[:R].clone() if exchange.private_copies else exchange.home_rows[:R]
         y = torch.empty(T, H, **opts)
         router_weights = router_weights.contiguous()
         if T > 0:
             ops.combine_rows_(ys, router_weights, K, y)
-        ctx.save_for_backward(xs, gu, act, ys, meta, w1, w2, router_weights, sorted_expert_idxs,
-                              sorted_scattered_idxs)
-        ctx.route, ctx.exchange = route, exchange
+        ctx.save_for_backward(gu, act, meta, w1, w2, router_weights, sorted_expert_idxs, sorted_scattered_idxs)
+        if kept is not None:
+            kept.xs, kept.ys = xs, ys
+        ctx.route, ctx.exchange, ctx.kept = route, exchange, kept
         return y
 
     @staticmethod
     def backward(ctx, grad_out):
-        xs, gu, act, ys, meta, w1, w2, router_weights, sorted_expert_idxs, sorted_scattered_idxs = ctx.saved_tensors
-        route, exchange = ctx.route, ctx.exchange
+        gu, act, meta, w1, w2, router_weights, sorted_expert_idxs, sorted_scattered_idxs = ctx.saved_tensors
+        route, exchange, kept = ctx.route, ctx.exchange, ctx.kept
+        xs, ys = kept.xs, kept.ys
         link = exchange.link
         T, K = router_weights.shape
         e_local, two_i, H = w1.shape
@@ -393,8 +442,8 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
 
         # dY rows, scaled by their routing weight, to the owners (same slots as the forward rows)
         ops.ep_dispatch_(grad_out, sorted_expert_idxs, sorted_scattered_idxs, router_weights.view(-1), K,
-                         route.send_delta, route.world, route.rank, exchange.recv_table, None, exchange.recv_cap)
-        dys = exchange.recv_rows[:alloc]
+                         route.send_delta, route.world, route.rank, exchange.recv_table_bwd, None, exchange.recv_cap)
+        dys = exchange.recv_rows_bwd[:alloc]
         ops.ep_copy_rows_(dys, meta, dys[:rows])  # in place: zero the pad rows (nobody else writes them)
         link.barrier()
 
@@ -407,19 +456,22 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
         ops.grouped_gemm_dw_(dgu, xs, route.counts, route.pad_offsets, d_w1, impl, tag="gemm_dw1")
         # dX rows straight back to the token's home rank
         if exchange.fused_return:
-            ops.grouped_gemm_rows_(dgu, w1, W_KN, exchange.home_rows, None, meta, route.tile_expert,
-                                   route.tile_prefix, two_i, H, EPI_PLAIN, impl, exchange.home_table,
+            ops.grouped_gemm_rows_(dgu, w1, W_KN, exchange.home_rows_bwd, None, meta, route.tile_expert,
+                                   route.tile_prefix, two_i, H, EPI_PLAIN, impl, exchange.home_table_bwd,
                                    exchange.home_cap, tag="gemm_dx")
         else:
             dxs = torch.empty(alloc, H, **opts)
             ops.grouped_gemm_rows_(dgu, w1, W_KN, dxs, None, None, route.tile_expert, route.tile_prefix, two_i, H,
                                    EPI_PLAIN, impl, tag="gemm_dx")
-            ops.ep_return_(dxs[:rows], meta, route.world, exchange.home_table, exchange.home_cap)
+            ops.ep_return_(dxs[:rows], meta, route.world, exchange.home_table_bwd, exchange.home_cap)
+        # every read of the forward's rows (xs for dW1, ys for d_router_weights) is queued in front of this
+        # barrier, so the buffers are free for the next forward once it has passed
+        kept.done = True
         link.barrier()
 
         d_x = torch.empty(T, H, **opts)
         if T > 0:
-            ops.combine_rows_(exchange.home_rows[:R], None, K, d_x)
+            ops.combine_rows_(exchange.home_rows_bwd[:R], None, K, d_x)
         return d_x, d_rw, d_w1, d_w2, None, None, None, None
 
 
@@ -429,13 +481,16 @@ class ExpertParallelMoE(nn.Module):
 
     def __init__(self, local_moe: MoE, gate_weight: torch.Tensor, world_group=None,
                  overlap_chunks: int | None = None, transport: str = "nccl", link=None,
-                 fused_return: bool = True) -> None:
+                 fused_return: bool = True, private_copies: bool = False) -> None:
         """`transport`: "nccl" (all-to-all collectives; any process group) or "peer" (stores into the
         other ranks' memory; the ranks must be GPUs of one node with peer access). `link` replaces the
         `PeerLink` built from the process group (the tests run several ranks on one GPU with it).
         `fused_return` (peer transport): the down-projection and dX GEMMs store their rows into the home
         ranks' memory from their own epilogues (GEMM and exchange are one kernel; the tile is staged in
-        shared memory so that each row leaves in 128-byte pieces); False runs a separate row kernel."""
+        shared memory so that each row leaves in 128-byte pieces); False runs a separate row kernel.
+        `private_copies` (peer transport): False keeps what the backward needs of the exchanged rows in the
+        exchange buffers themselves (the backward exchanges through a second pair of buffers), which saves two
+        passes over `[rows, hidden]` per step but allows one forward per backward at a time; True copies them."""
         super().__init__()
         if not (getattr(local_moe.act, "xma_fused_activation", None) == "swiglu" and local_moe.is_glu):
             raise ValueError("ExpertParallelMoE runs the fused SwiGLU expert block")
@@ -444,6 +499,7 @@ class ExpertParallelMoE(nn.Module):
         self.local = local_moe
         self.transport = transport
         self.fused_return = fused_return
+        self.private_copies = private_copies
         if link is not None:
             self.link, self.group = link, None
             self.world, self.rank = link.world, link.rank
@@ -494,7 +550,8 @@ class ExpertParallelMoE(nn.Module):
     def _exchange(self, slot: int, x: torch.Tensor) -> _Exchange:
         key = (slot, x.device, x.dtype)
         if key not in self._exchanges:
-            self._exchanges[key] = _Exchange(self.link, x.device, x.dtype, self.hidden_size, self.fused_return)
+            self._exchanges[key] = _Exchange(self.link, x.device, x.dtype, self.hidden_size, self.fused_return,
+                                             self.private_copies)
         return self._exchanges[key]
 
     def close(self) -> None:

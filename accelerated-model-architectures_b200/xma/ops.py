@@ -373,7 +373,7 @@ def _wrap(op, name: str, kernels: int):
 continuous_count_ = _wrap(_continuous_count_op, "continuous_count", 1)
 route_topk_softmax_ = _wrap(_route_topk_softmax_op, "route_topk_softmax", 1)
 route_topk_softmax_bwd_ = _wrap(_route_topk_softmax_bwd_op, "route_topk_softmax_bwd", 1)
-count_sort_ = _wrap(_count_sort_op, "count_sort", 3)
+count_sort_ = _wrap(_count_sort_op, "count_sort", 4)
 gather_rows_ = _wrap(_gather_rows_op, "gather_rows", 1)
 combine_rows_ = _wrap(_combine_rows_op, "combine_rows", 1)
 combine_bwd_ = _wrap(_combine_bwd_op, "combine_bwd", 1)

@@ -95,8 +95,10 @@ int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_expert
  * (xma_b200_count_sort_scratch_bytes) must not exceed
  * xma_b200_count_sort_static_scratch_limit() = 524544 bytes, e.g. up to 2 Mi ids with 256
  * experts, else XMA_ERR_TOO_LARGE (-8). The first call on a device resolves the array's device
- * address; issue it before any stream capture. Calls on one device share the array (cleared at
- * the start of each call); calls that overlap on the GPU race.
+ * address; issue it before any stream capture, and at start-up: under lazy module loading it may be
+ * the moment the driver places the library's code and the array on the device (a driver-side
+ * allocation), which should happen before a memory pool takes the budget. Calls on one device share
+ * the array (cleared at the start of each call); calls that overlap on the GPU race.
  * This entry point has no counterpart in the reference. */
 int64_t xma_b200_count_sort_static_scratch_limit(void);
 int xma_b200_count_sort_static(const void* ids, int id_dtype, int64_t n, int num_experts, uint32_t* counts,

@@ -45,7 +45,8 @@ def test_host_side_argument_errors_need_no_gpu():
     assert lib.xma_b200_tile_capacity(1024, 8) == 16
     assert lib.xma_b200_tile_capacity(-1, 8) < 0
     assert lib.xma_b200_count_sort_scratch_bytes(10, 2000) < 0  # more than 1024 experts
-    assert lib.xma_b200_count_sort_scratch_bytes(8193, 8) == 256 + 2 * 8 * 8
+    # 2 tiles of 8192 ids, 1 chunk of the scan: ticket | counts [2][8] u32 | chunk base [8] u32 | status words [8] u64
+    assert lib.xma_b200_count_sort_scratch_bytes(8193, 8) == 256 + 2 * 8 * 4 + 8 * 4 + 8 * 8
     # null pointers and bad dtypes are refused before anything is launched
     assert lib.xma_b200_continuous_count(None, _lib.I32, 10, 4, None, None, None) == -1
     assert lib.xma_b200_swiglu_fwd(None, 0, None, 0, None, 0, _lib.BF16, 4, 4, None) == -1

@@ -182,6 +182,7 @@ _COMPILED = {(4, 2, 2048, 8192), (8, 4, 2048, 8192), (128, 8, 576, 256), (4, 1, 
 @pytest.mark.parametrize("num_experts,top_k,H,I", _GRID)
 @pytest.mark.parametrize("is_glu", [True, False])
 @pytest.mark.parametrize("compiled", [False, True])
+@torch._dynamo.config.patch(recompile_limit=1024)  # every point is a new module, as in the reference's test
 def test_moe_reference_grid(dtype, num_experts, top_k, H, I, is_glu, compiled):
     """The reference's own MoE test (tests/layers/moe_test.py:26-157) on its grid: 7 tokens; E in {2,4,6,8} x
     K in {2,4} at hidden 2048 / intermediate 8192, and E=128, K=8 at 576 / 256; three dtypes; nn.GLU /

@@ -2,7 +2,7 @@
 
 `xma_b200_count_sort_static` exists for callers that must not allocate device memory while they run
 (an inference engine that reserved its whole budget up front, a plug-in that lives between other
-allocators): it keeps the look-back scan's scratch in a fixed array inside the library. This test
+allocators): it keeps the sort's scratch (per-tile counts, look-back words) in a fixed array inside the library. This test
 drives it exactly as such a caller would - raw pointers, no scratch argument - twice in a row on the
 same device, so the second call meets whatever the first one left in the shared array, and requires
 the same bits as the regular entry point, which gets a fresh caller-owned scratch buffer each time.
@@ -25,13 +25,16 @@ def _outputs(n, E, tile_cap):
     )
 
 
-def _call(lib, ids, E, static):
+def _call(lib, ids, E, static, check_no_allocation=False):
     from xma import _lib
 
     n = ids.numel()
     tile_cap = int(lib.xma_b200_tile_capacity(n, E))
     o = _outputs(n, E, tile_cap)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    if check_no_allocation:
+        torch.cuda.synchronize()
+        free_before, pool_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
     stream = torch.cuda.current_stream().cuda_stream
     head = (ids.data_ptr(), _lib.I32, n, E, o["counts"].data_ptr(), o["offsets"].data_ptr(),
             o["pad_offsets"].data_ptr(), o["tile_prefix"].data_ptr(), o["tile_expert"].data_ptr(), tile_cap,
@@ -44,6 +47,10 @@ def _call(lib, ids, E, static):
         rc = lib.xma_b200_count_sort(*head, scratch.data_ptr(), need, status.data_ptr(), stream)
     assert rc == 0, _lib.error_string(rc)
     torch.cuda.synchronize()
+    if check_no_allocation:
+        # outputs were allocated before the call: neither the driver's free memory nor torch's pool may move
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.cuda.memory_allocated() == pool_before
     assert int(status.item()) == 0
     used_tiles = int(o["tile_prefix"][-1])
     used_rows = int(o["pad_offsets"][-1])
@@ -61,10 +68,12 @@ def test_static_scratch_sort_matches_regular_entry_point_twice():
     rng = np.random.RandomState(123)
     # first call: many tiles and experts (fills most of the array); second: fewer of both, so any
     # state left behind by the first call would be read as look-back status if it were not cleared
-    for n, E in ((900_001, 256), (70_003, 40)):
+    # (the first static call on a device may load the module, a driver-side allocation; from the second on the
+    # call must leave the device's free memory and torch's pool exactly as they were)
+    for call, (n, E) in enumerate(((900_001, 256), (70_003, 40))):
         assert int(lib.xma_b200_count_sort_scratch_bytes(n, E)) <= limit
         ids = torch.from_numpy(rng.randint(0, E, size=n).astype(np.int32)).cuda()
-        got = _call(lib, ids, E, static=True)
+        got = _call(lib, ids, E, static=True, check_no_allocation=call > 0)
         want = _call(lib, ids, E, static=False)
         for key in want:
             assert torch.equal(got[key], want[key]), (n, E, key)
