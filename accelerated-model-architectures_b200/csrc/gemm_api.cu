@@ -23,6 +23,7 @@ Tuning& tuning() {
         env("XMA_B200_TMA_PREFETCH_MASK", t.tma_prefetch_mask);
         env("XMA_B200_EPI_WARPS", t.epi_warps);
         env("XMA_B200_PLAIN_PAIRS", t.plain_pairs);
+        env("XMA_B200_DW_DYNAMIC", t.dw_dynamic);
     });
     return t;
 }
@@ -213,7 +214,7 @@ int xma_b200_grouped_gemm_choice(int kind, int dtype, int num_experts, int64_t t
 // Tuning switches of the tensor-core kernels (process-wide). key: 0 = gate|up L2 prefetch in the SwiGLU-backward
 // epilogue (0/1), 1 = TMA L2 prefetch distance in reduction blocks (0..255), 2 = operands it covers (bit 0 A,
 // bit 1 B), 3 = epilogue warps (0 = per-kernel default, 4, 8), 4 = CTA pairs for plain epilogues in the
-// automatic choice (0/1). Returns the previous value, or XMA_ERR_BAD_SHAPE for an unknown key. Not synchronised
+// automatic choice (0/1), 5 = weight-gradient tiles by atomic ticket, heaviest experts first (0/1). Returns the previous value, or XMA_ERR_BAD_SHAPE for an unknown key. Not synchronised
 // with launches in flight on other threads.
 int xma_b200_tuning_set(int key, int value) {
     xma::Tuning& t = xma::tuning();
@@ -224,6 +225,7 @@ int xma_b200_tuning_set(int key, int value) {
         case 2: field = &t.tma_prefetch_mask; break;
         case 3: field = &t.epi_warps; break;
         case 4: field = &t.plain_pairs; break;
+        case 5: field = &t.dw_dynamic; break;
         default: return XMA_ERR_BAD_SHAPE;
     }
     const int previous = *field;
@@ -252,6 +254,6 @@ const char* xma_b200_error_string(int code) {
     return "unknown error";
 }
 
-int xma_b200_abi_version(void) { return 2; }
+int xma_b200_abi_version(void) { return 3; }
 
 }  // extern "C"

@@ -78,6 +78,7 @@ struct Tuning {
     int tma_prefetch_mask = 3;  // bit 0: A operand, bit 1: B operand
     int epi_warps = 0;          // 4 or 8 epilogue warps; 0 = per-kernel default
     int plain_pairs = 1;        // automatic choice: CTA pairs also for the plain epilogues of large experts
+    int dw_dynamic = 1;         // weight-gradient pair kernel: tiles by atomic ticket, heaviest experts first
 };
 Tuning& tuning();
 uint32_t tune_word();  // the switches the kernels read, packed (see sm100_common.cuh)

@@ -366,22 +366,113 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 // ======================================================================================================
 // Weight-gradient GEMM, CTA pair: 256 x 256 tile of dW_e; CTA `rank` owns rows [128 * rank, +128) of it
 // and stages columns [128 * rank, +128) of the Y operand.
+//
+// Work hand-out. A tile of dW_e costs as much as expert e has rows, and loads are anything but equal (a Zipf-
+// skewed router gives some experts ten times the mean and some nothing), so with DYN the pairs do not walk a
+// fixed stride through the tiles: experts are ranked by row count, tiles are numbered heaviest expert first,
+// and a pair takes the next number from an atomic ticket whenever it starts a tile (longest-processing-time
+// order: the light tiles at the end level the finish line). The leader's producer thread draws the ticket;
+// the other roles of the pair (the second CTA's producer, the MMA thread, the epilogue warps of both CTAs)
+// run at their own pace behind it, so the drawn numbers are handed on through a small ring per pair in
+// global memory: one 64-bit word per entry, (sequence number + 1) << 32 | tile number, written with release
+// and polled with acquire semantics - tag and payload in one word, no separate flag. A consumer is at most
+// 8 tiles behind the producer (6 ring stages of at least one reduction block each, 2 accumulator buffers), the
+// ring holds 16. Experts without rows get their zeros from the epilogue warps up front and take no ticket.
+// Every poll is bounded like the mbarrier waits.
 // ======================================================================================================
-template <typename T>
+constexpr int SCHED_RING = 16;
+constexpr int SCHED_MAX_PAIRS = 128;
+constexpr int SCHED_SLOTS = 16;  // launches that may be in flight on one device, each with its own ticket and rings
+constexpr uint32_t SCHED_END = 0xffffffffu;
+
+struct DwSched {
+    unsigned long long ring[SCHED_MAX_PAIRS][SCHED_RING];
+    unsigned ticket;
+    unsigned pad[31];
+};
+
+static __device__ DwSched g_dw_sched[SCHED_SLOTS];
+
+__device__ __forceinline__ void sched_publish(DwSched* sc, int64_t pair, uint32_t seq, uint32_t value) {
+    const unsigned long long word = (static_cast<unsigned long long>(seq + 1u) << 32) | value;
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(&sc->ring[pair][seq % SCHED_RING]), "l"(word) : "memory");
+}
+
+// False when the bounded wait gave up (the CTA-wide abort flag is raised then).
+__device__ __forceinline__ bool sched_fetch(const DwSched* sc, int64_t pair, uint32_t seq, volatile int* abort_flag,
+                                            uint32_t& value) {
+    const unsigned long long* p = &sc->ring[pair][seq % SCHED_RING];
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        unsigned long long v;
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+        if (static_cast<uint32_t>(v >> 32) == seq + 1u) {
+            value = static_cast<uint32_t>(v);
+            return true;
+        }
+        if ((++spins & 0x3fu) == 0u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+template <typename T, bool DYN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                    const uint32_t* __restrict__ counts, const int* __restrict__ pad_offsets, int E, int m, int n,
-                   T* __restrict__ dw, uint32_t idesc, uint32_t tune, int* __restrict__ status) {
+                   T* __restrict__ dw, uint32_t idesc, uint32_t tune, DwSched* __restrict__ sched,
+                   int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const Shared2 s = carve_smem2(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = static_cast<int>(cluster_ctarank());
     const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const uint32_t tmem_base = prologue2(s, warp);
 
     const int m_tiles = (m + 2 * BM - 1) / (2 * BM);
     const int n_tiles = (n + BN - 1) / BN;
-    const int64_t total = static_cast<int64_t>(E) * m_tiles * n_tiles;
+    const int per_e = m_tiles * n_tiles;
+
+    // DYN: the experts ranked by row count (ties by index), the ones without rows last. s_order[k] = k-th
+    // heaviest expert, s_cnt = the counts (the two prefix tables of the rows kernel are free here).
+    int* s_cnt = s.pair_prefix;
+    int* s_order = s.tile_prefix;
+    int n_busy = E;  // experts that have rows
+    if (DYN) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = static_cast<int>(counts[e]);
+        __syncthreads();
+        n_busy = 0;
+        for (int base = 0; base < E; base += blockDim.x) {
+            const int e = base + threadIdx.x;
+            bool busy = false;
+            if (e < E) {
+                const int c = s_cnt[e];
+                busy = c > 0;
+                int pos = 0;
+                for (int j = 0; j < E; ++j) {
+                    const int cj = s_cnt[j];
+                    pos += (cj > c || (cj == c && j < e)) ? 1 : 0;
+                }
+                s_order[pos] = e;
+            }
+            n_busy += __syncthreads_count(busy);
+        }
+    }
+    const uint32_t tmem_base = prologue2(s, warp);
+    const int64_t total = static_cast<int64_t>(n_busy) * per_e;  // DYN: tickets; else every (expert, tile)
+    const int64_t total_static = static_cast<int64_t>(E) * per_e;
+
+    // work item of a ticket (DYN) or of a static index
+    auto item = [&](int64_t w) {
+        DwWork wk = decode_dw(w, m_tiles, n_tiles);
+        if (DYN) wk.e = s_order[wk.e];
+        return wk;
+    };
+    auto rows_of = [&](int e) { return DYN ? s_cnt[e] : static_cast<int>(counts[e]); };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -399,75 +490,112 @@ dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     else if (tune & TUNE_PREFETCH_B) tma_prefetch_2d(&tm_y, c0, row);
                 }
             };
-            // L2 prefetch cursor, `ahead` reduction blocks in front of the loads (experts without rows have none)
-            const int ahead = static_cast<int>(tune_prefetch_distance(tune));
-            int64_t w_pf = pair;
-            int kb_pf = 0, kbs_pf = 0, row_pf = 0;
-            DwWork wk_pf;
-            bool pf_on = ahead > 0;
-            auto pf_seek = [&]() {  // first work item at or after w_pf that has reduction blocks
-                for (; w_pf < total; w_pf += num_pairs) {
-                    wk_pf = decode_dw(w_pf, m_tiles, n_tiles);
-                    kbs_pf = (static_cast<int>(counts[wk_pf.e]) + BK - 1) / BK;
-                    if (kbs_pf > 0) break;
-                }
-                pf_on = w_pf < total;
-                if (pf_on) row_pf = pad_offsets[wk_pf.e];
-                kb_pf = 0;
-            };
-            if (pf_on) pf_seek();
-            auto prefetch_step = [&]() {
-                if (!pf_on) return;
-                boxes(wk_pf, row_pf + kb_pf * BK, false, nullptr, nullptr, 0u);
-                if (++kb_pf == kbs_pf) {
-                    w_pf += num_pairs;
-                    pf_seek();
-                }
-            };
-            for (int i = 0; i < ahead; ++i) prefetch_step();
             uint32_t it = 0;
-            for (int64_t w = pair; w < total; w += num_pairs) {
-                const DwWork wk = decode_dw(w, m_tiles, n_tiles);
-                const int k_blocks = (static_cast<int>(counts[wk.e]) + BK - 1) / BK;
+            auto load_item = [&](const DwWork& wk) {
+                const int k_blocks = (rows_of(wk.e) + BK - 1) / BK;
                 const int row0 = pad_offsets[wk.e];
-                bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int st = it % STAGES2;
-                    ok = mbar_wait(&s.empty[st], ((it / STAGES2) & 1u) ^ 1u, s.abort_flag);
-                    if (!ok) break;
+                    if (!mbar_wait(&s.empty[st], ((it / STAGES2) & 1u) ^ 1u, s.abort_flag)) return false;
                     uint8_t* sa = s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES;
                     const uint32_t full0 = map_to_cta(smem_u32(&s.full[st]), 0);
                     if (rank == 0) mbar_expect_tx(&s.full[st], 2 * STAGE2_BYTES);
                     boxes(wk, row0 + kb * BK, true, sa, sa + A2_BYTES, full0);
-                    prefetch_step();
                 }
-                if (!ok) break;
+                return true;
+            };
+            if (DYN) {
+                for (uint32_t seq = 0;; ++seq) {
+                    uint32_t t;
+                    if (rank == 0) {  // the pair's scheduler
+                        t = atomicAdd(&sched->ticket, 1u);
+                        if (t >= total) t = SCHED_END;
+                        sched_publish(sched, pair, seq, t);
+                    } else if (!sched_fetch(sched, pair, seq, s.abort_flag, t)) {
+                        break;
+                    }
+                    if (t == SCHED_END || !load_item(item(t))) break;
+                }
+            } else {
+                // L2 prefetch cursor, `ahead` reduction blocks in front of the loads (experts without rows have none)
+                const int ahead = static_cast<int>(tune_prefetch_distance(tune));
+                int64_t w_pf = pair;
+                int kb_pf = 0, kbs_pf = 0, row_pf = 0;
+                DwWork wk_pf;
+                bool pf_on = ahead > 0;
+                auto pf_seek = [&]() {  // first work item at or after w_pf that has reduction blocks
+                    for (; w_pf < total_static; w_pf += num_pairs) {
+                        wk_pf = decode_dw(w_pf, m_tiles, n_tiles);
+                        kbs_pf = (static_cast<int>(counts[wk_pf.e]) + BK - 1) / BK;
+                        if (kbs_pf > 0) break;
+                    }
+                    pf_on = w_pf < total_static;
+                    if (pf_on) row_pf = pad_offsets[wk_pf.e];
+                    kb_pf = 0;
+                };
+                if (pf_on) pf_seek();
+                auto prefetch_step = [&]() {
+                    if (!pf_on) return;
+                    boxes(wk_pf, row_pf + kb_pf * BK, false, nullptr, nullptr, 0u);
+                    if (++kb_pf == kbs_pf) {
+                        w_pf += num_pairs;
+                        pf_seek();
+                    }
+                };
+                for (int i = 0; i < ahead; ++i) prefetch_step();
+                for (int64_t w = pair; w < total_static; w += num_pairs) {
+                    const DwWork wk = decode_dw(w, m_tiles, n_tiles);
+                    const int k_blocks = (static_cast<int>(counts[wk.e]) + BK - 1) / BK;
+                    const int row0 = pad_offsets[wk.e];
+                    bool ok = true;
+                    for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                        const int st = it % STAGES2;
+                        ok = mbar_wait(&s.empty[st], ((it / STAGES2) & 1u) ^ 1u, s.abort_flag);
+                        if (!ok) break;
+                        uint8_t* sa = s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES;
+                        const uint32_t full0 = map_to_cta(smem_u32(&s.full[st]), 0);
+                        if (rank == 0) mbar_expect_tx(&s.full[st], 2 * STAGE2_BYTES);
+                        boxes(wk, row0 + kb * BK, true, sa, sa + A2_BYTES, full0);
+                        prefetch_step();
+                    }
+                    if (!ok) break;
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             uint32_t it = 0, lt = 0;
-            for (int64_t w = pair; w < total; w += num_pairs) {
-                const DwWork wk = decode_dw(w, m_tiles, n_tiles);
-                const int k_blocks = (static_cast<int>(counts[wk.e]) + BK - 1) / BK;
-                if (k_blocks == 0) continue;
+            // main loop of one tile with k_blocks >= 1 reduction blocks; false when a bounded wait gave up
+            auto mma_item = [&](int k_blocks) {
                 const uint32_t buf = lt & 1u;
-                if (!mbar_wait(&s.acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, s.abort_flag)) break;
+                if (!mbar_wait(&s.acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, s.abort_flag)) return false;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int st = it % STAGES2;
-                    ok = mbar_wait(&s.full[st], (it / STAGES2) & 1u, s.abort_flag);
-                    if (!ok) break;
+                    if (!mbar_wait(&s.full[st], (it / STAGES2) & 1u, s.abort_flag)) return false;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(s.stage_base + static_cast<size_t>(st) * STAGE2_BYTES);
                     issue_stage_pair<true, true>(sa, sa + A2_BYTES, tmem_d, idesc, kb == 0);
                     umma_commit_pair(&s.empty[st]);
                 }
-                if (!ok) break;
                 umma_commit_pair(&s.acc_full[buf]);
                 ++lt;
+                return true;
+            };
+            if (DYN) {
+                for (uint32_t seq = 0;; ++seq) {
+                    uint32_t t;
+                    if (!sched_fetch(sched, pair, seq, s.abort_flag, t) || t == SCHED_END) break;
+                    if (!mma_item((rows_of(item(t).e) + BK - 1) / BK)) break;
+                }
+            } else {
+                for (int64_t w = pair; w < total_static; w += num_pairs) {
+                    const DwWork wk = decode_dw(w, m_tiles, n_tiles);
+                    const int k_blocks = (static_cast<int>(counts[wk.e]) + BK - 1) / BK;
+                    if (k_blocks == 0) continue;
+                    if (!mma_item(k_blocks)) break;
+                }
             }
         }
     } else {
@@ -477,21 +605,21 @@ dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const int chunks = (BN / 32) / parts;
         const int row_in_tile = quarter * 32 + lane;
         uint32_t lt = 0;
-        for (int64_t w = pair; w < total; w += num_pairs) {
-            const DwWork wk = decode_dw(w, m_tiles, n_tiles);
+        auto zero_tile = [&](const DwWork& wk) {
+            const int row = wk.m_tile * 2 * BM + rank * BM + row_in_tile;
+            const int n0 = wk.n_tile * BN;
+            if (row >= m) return;
+            T* dst = dw + (static_cast<int64_t>(wk.e) * m + row) * n + n0;
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            for (int c = part * chunks * 32; c < (part + 1) * chunks * 32 && n0 + c < n; c += 8)
+                *reinterpret_cast<uint4*>(dst + c) = z;
+        };
+        auto store_tile = [&](const DwWork& wk) {
             const int row = wk.m_tile * 2 * BM + rank * BM + row_in_tile;
             const int n0 = wk.n_tile * BN;
             T* dst = dw + (static_cast<int64_t>(wk.e) * m + row) * n + n0;
-            if (counts[wk.e] == 0u) {
-                if (row < m) {
-                    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                    for (int c = part * chunks * 32; c < (part + 1) * chunks * 32 && n0 + c < n; c += 8)
-                        *reinterpret_cast<uint4*>(dst + c) = z;
-                }
-                continue;
-            }
             const uint32_t buf = lt & 1u;
-            if (!mbar_wait_epilogue(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
+            if (!mbar_wait_epilogue(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) return false;
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
@@ -513,6 +641,30 @@ dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s.acc_empty[buf]), 0));
             ++lt;
+            return true;
+        };
+        if (DYN) {
+            // experts without rows: exact zeros, handed out by a fixed stride (they sit behind the busy ones)
+            const int64_t idle_items = static_cast<int64_t>(E - n_busy) * per_e;
+            for (int64_t z = pair; z < idle_items; z += num_pairs) zero_tile(item(total + z));
+            for (uint32_t seq = 0;; ++seq) {
+                uint32_t t = SCHED_END;
+                int ok = 1;
+                if (lane == 0) ok = sched_fetch(sched, pair, seq, s.abort_flag, t) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                t = __shfl_sync(0xffffffffu, t, 0);
+                if (!ok || t == SCHED_END) break;
+                if (!store_tile(item(t))) break;
+            }
+        } else {
+            for (int64_t w = pair; w < total_static; w += num_pairs) {
+                const DwWork wk = decode_dw(w, m_tiles, n_tiles);
+                if (counts[wk.e] == 0u) {
+                    zero_tile(wk);
+                    continue;
+                }
+                if (!store_tile(wk)) break;
+            }
         }
     }
     teardown2(s, tmem_base, warp, status);
@@ -561,15 +713,55 @@ static int rows_dispatch2(const RowsGemmArgs& g, const CUtensorMap& ta, const CU
     return XMA_ERR_UNSUPPORTED;
 }
 
+// One scheduler slot of the current device for one launch, cleared on `stream` in front of the launch. The
+// slots go round: a launch meets a slot that an earlier launch still uses only with SCHED_SLOTS weight-gradient
+// GEMMs in flight on one device at once.
+static int sched_slot(cudaStream_t stream, DwSched** out) {
+    static std::mutex mu;
+    static DwSched* base[64] = {nullptr};
+    static unsigned next[64] = {0};
+    int dev = 0;
+    XMA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return XMA_ERR_UNSUPPORTED;
+    DwSched* slot;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!base[dev]) {
+            void* p = nullptr;
+            XMA_CUDA_TRY(cudaGetSymbolAddress(&p, g_dw_sched));
+            base[dev] = static_cast<DwSched*>(p);
+        }
+        slot = base[dev] + (next[dev]++ % SCHED_SLOTS);
+    }
+    XMA_CUDA_TRY(cudaMemsetAsync(slot, 0, sizeof(DwSched), stream));
+    *out = slot;
+    return XMA_OK;
+}
+
 template <typename T>
 static int launch_dw2(const DwGemmArgs& g, const CUtensorMap& tx, const CUtensorMap& ty) {
-    auto kernel = dw_gemm_tc2_kernel<T>;
-    int rc = set_smem2(kernel);
-    if (rc) return rc;
     const uint32_t idesc = make_idesc_mn(g.dtype, true, true, 2 * BM, BN);
-    kernel<<<pair_grid(), block_threads(4), SMEM2_BYTES, g.stream>>>(
-        tx, ty, g.counts, g.pad_offsets, g.num_experts, static_cast<int>(g.m), static_cast<int>(g.n),
-        static_cast<T*>(g.dw), idesc, tune_word(), g.device_status);
+    const int64_t m_tiles = (g.m + 2 * BM - 1) / (2 * BM), n_tiles = (g.n + BN - 1) / BN;
+    const bool dynamic = tuning().dw_dynamic && g.num_experts <= MAX_EXPERTS && pair_grid() / 2 <= SCHED_MAX_PAIRS &&
+                         g.num_experts * m_tiles * n_tiles < (int64_t{1} << 31);
+    if (dynamic) {
+        auto kernel = dw_gemm_tc2_kernel<T, true>;
+        int rc = set_smem2(kernel);
+        if (rc) return rc;
+        DwSched* sched = nullptr;
+        rc = sched_slot(g.stream, &sched);
+        if (rc) return rc;
+        kernel<<<pair_grid(), block_threads(4), SMEM2_BYTES, g.stream>>>(
+            tx, ty, g.counts, g.pad_offsets, g.num_experts, static_cast<int>(g.m), static_cast<int>(g.n),
+            static_cast<T*>(g.dw), idesc, tune_word(), sched, g.device_status);
+    } else {
+        auto kernel = dw_gemm_tc2_kernel<T, false>;
+        int rc = set_smem2(kernel);
+        if (rc) return rc;
+        kernel<<<pair_grid(), block_threads(4), SMEM2_BYTES, g.stream>>>(
+            tx, ty, g.counts, g.pad_offsets, g.num_experts, static_cast<int>(g.m), static_cast<int>(g.n),
+            static_cast<T*>(g.dw), idesc, tune_word(), nullptr, g.device_status);
+    }
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -137,40 +137,75 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, int64_t x_stride, const T* __restric
     }
 }
 
-// d weight: every CTA adds dy * z of its rows into row blockIdx.x of `dw_partial` [gridDim.x, cols] (fp32);
-// the caller sums the partial rows. Cached items accumulate in registers, the others in the CTA's own partial row.
+// d weight: every CTA adds dy * z of its rows into row blockIdx.x of `dw_partial` [gridDim.x, cols] (fp32); the
+// caller sums the partial rows. A thread always meets the same columns, so the CTA's running sums live in shared
+// memory without atomics (cached items; 32 KiB at most) or in the CTA's own partial row (rows too long to cache).
+// The cached items stay in registers in their storage type (a 128-bit packet is four registers, its eight
+// fp32 values would be eight), and the three streams of a row (xr, dy, d xr) are all requested before the first
+// use: with 114 registers and the d(xr) load issued behind the row reduction the first version kept too few
+// bytes in flight (0.49 of the copy bandwidth).
+template <typename T, bool VEC>
+struct Raw {
+    static constexpr int N = VEC ? Vec16<T>::N : 1;
+    Vec16<T> q;  // only element 0 is used on the scalar path
+    __device__ __forceinline__ void load(const T* p) {
+        if (VEC) q = load16(p);
+        else q.v[0] = p[0];
+    }
+    __device__ __forceinline__ float at(int j) const { return to_f32(q.v[j]); }
+};
+
 template <typename T, bool VEC, int CACHE>
-__global__ void __launch_bounds__(RN_THREADS)
+__global__ void __launch_bounds__(RN_THREADS, (CACHE <= 2 ? 2 : 1))
 rmsnorm_bwd_kernel(const T* __restrict__ xr, int64_t xr_stride, const T* __restrict__ w, const T* __restrict__ dy,
                    int64_t dy_stride, const T* __restrict__ dxr, int64_t dxr_stride, const float* __restrict__ s,
                    T* __restrict__ dx, int64_t dx_stride, T* __restrict__ dr, int64_t dr_stride,
                    float* __restrict__ dw_partial, int64_t rows, int64_t cols, float eps, float multiplier) {
     using It = Item<T, VEC>;
+    using Rw = Raw<T, VEC>;
     constexpr int N = It::N;
+    constexpr int C = CACHE > 0 ? CACHE : 1;
     __shared__ float red[RN_THREADS / 32];
+    extern __shared__ float s_dw[];  // [CACHE * RN_THREADS * N] when the weight gradient is wanted
     const int64_t items = cols / N;
     const float inv_cols = 1.0f / static_cast<float>(cols);
-    float dw_acc[CACHE > 0 ? CACHE : 1][N];
-#pragma unroll
-    for (int k = 0; k < (CACHE > 0 ? CACHE : 1); ++k)
-#pragma unroll
-        for (int j = 0; j < N; ++j) dw_acc[k][j] = 0.0f;
     float* my_dw = dw_partial ? dw_partial + static_cast<int64_t>(blockIdx.x) * cols : nullptr;
-    if (my_dw)
+    if (my_dw) {
+        for (int i = threadIdx.x; i < CACHE * RN_THREADS * N; i += RN_THREADS) s_dw[i] = 0.0f;
         for (int64_t i = threadIdx.x + static_cast<int64_t>(CACHE) * RN_THREADS; i < items; i += RN_THREADS)
 #pragma unroll
             for (int j = 0; j < N; ++j) my_dw[i * N + j] = 0.0f;
+        // (each thread only ever touches its own entries of s_dw and of my_dw: no barrier needed)
+    }
 
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const T* xp = xr + row * xr_stride;
         const T* dyp = dy + row * dy_stride;
-        It cx[CACHE > 0 ? CACHE : 1], cg[CACHE > 0 ? CACHE : 1];
+        const T* dxrp = dxr ? dxr + row * dxr_stride : nullptr;
+        Rw cx[C], cg[C], ce[C];
+        // every cached packet of the row's three streams is requested here
+#pragma unroll
+        for (int k = 0; k < CACHE; ++k) {
+            const int64_t i = threadIdx.x + static_cast<int64_t>(k) * RN_THREADS;
+            if (i < items) {
+                cx[k].load(xp + i * N);
+                cg[k].load(dyp + i * N);
+                if (dxrp) ce[k].load(dxrp + i * N);
+            }
+        }
         float rstd;
         if (s) {
             rstd = s[row];
         } else {
             float sumsq = 0.0f;
-            for (int64_t i = threadIdx.x; i < items; i += RN_THREADS) {
+#pragma unroll
+            for (int k = 0; k < CACHE; ++k) {
+                const int64_t i = threadIdx.x + static_cast<int64_t>(k) * RN_THREADS;
+                if (i < items)
+#pragma unroll
+                    for (int j = 0; j < N; ++j) sumsq += cx[k].at(j) * cx[k].at(j);
+            }
+            for (int64_t i = threadIdx.x + static_cast<int64_t>(CACHE) * RN_THREADS; i < items; i += RN_THREADS) {
                 It a;
                 a.load(xp + i * N);
 #pragma unroll
@@ -179,53 +214,39 @@ rmsnorm_bwd_kernel(const T* __restrict__ xr, int64_t xr_stride, const T* __restr
             rstd = rsqrtf(block_sum(sumsq, red) * inv_cols + eps);
         }
         // pass 1: z = xr * rstd, g = dy * weight, dot = sum g * z; d weight += dy * z
-        auto first = [&](int64_t i, It& z, It& g, float* acc, bool in_regs) {
-            z.load(xp + i * N);
-            g.load(dyp + i * N);
-#pragma unroll
-            for (int j = 0; j < N; ++j) z.v[j] *= rstd;
-            if (my_dw) {
-                if (in_regs) {
-#pragma unroll
-                    for (int j = 0; j < N; ++j) acc[j] += g.v[j] * z.v[j];
-                } else {
-#pragma unroll
-                    for (int j = 0; j < N; ++j) my_dw[i * N + j] += g.v[j] * z.v[j];
-                }
-            }
-            if (w) {
-                It ww;
-                ww.load(w + i * N);
-#pragma unroll
-                for (int j = 0; j < N; ++j) g.v[j] *= ww.v[j];
-            }
-            float d = 0.0f;
-#pragma unroll
-            for (int j = 0; j < N; ++j) d += g.v[j] * z.v[j];
-            return d;
-        };
         float dot = 0.0f;
 #pragma unroll
         for (int k = 0; k < CACHE; ++k) {
             const int64_t i = threadIdx.x + static_cast<int64_t>(k) * RN_THREADS;
-            if (i < items) dot += first(i, cx[k], cg[k], dw_acc[k], true);
+            if (i < items) {
+                It ww;
+                if (w) ww.load(w + i * N);
+#pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    const float z = cx[k].at(j) * rstd, g = cg[k].at(j);
+                    if (my_dw) s_dw[(k * RN_THREADS + threadIdx.x) * N + j] += g * z;
+                    dot += (w ? g * ww.v[j] : g) * z;
+                }
+            }
         }
         for (int64_t i = threadIdx.x + static_cast<int64_t>(CACHE) * RN_THREADS; i < items; i += RN_THREADS) {
-            It z, g;
-            dot += first(i, z, g, nullptr, false);
+            It z, g, ww;
+            z.load(xp + i * N);
+            g.load(dyp + i * N);
+            if (w) ww.load(w + i * N);
+#pragma unroll
+            for (int j = 0; j < N; ++j) {
+                const float zz = z.v[j] * rstd;
+                if (my_dw) my_dw[i * N + j] += g.v[j] * zz;
+                dot += (w ? g.v[j] * ww.v[j] : g.v[j]) * zz;
+            }
         }
         const float c = block_sum(dot, red) * inv_cols;
         // pass 2: d = (g - z * c) * rstd + d(xr)
-        auto second = [&](int64_t i, const It& z, const It& g) {
+        auto emit = [&](int64_t i, const float* z, const float* g, const float* e) {
             It d;
 #pragma unroll
-            for (int j = 0; j < N; ++j) d.v[j] = (g.v[j] - z.v[j] * c) * rstd;
-            if (dxr) {
-                It e;
-                e.load(dxr + row * dxr_stride + i * N);
-#pragma unroll
-                for (int j = 0; j < N; ++j) d.v[j] += e.v[j];
-            }
+            for (int j = 0; j < N; ++j) d.v[j] = (g[j] - z[j] * c) * rstd + (e ? e[j] : 0.0f);
             if (dr) d.store(dr + row * dr_stride + i * N);
 #pragma unroll
             for (int j = 0; j < N; ++j) d.v[j] *= multiplier;
@@ -234,12 +255,24 @@ rmsnorm_bwd_kernel(const T* __restrict__ xr, int64_t xr_stride, const T* __restr
 #pragma unroll
         for (int k = 0; k < CACHE; ++k) {
             const int64_t i = threadIdx.x + static_cast<int64_t>(k) * RN_THREADS;
-            if (i < items) second(i, cx[k], cg[k]);
+            if (i < items) {
+                It ww;
+                if (w) ww.load(w + i * N);
+                float z[N], g[N], e[N];
+#pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    z[j] = cx[k].at(j) * rstd;
+                    g[j] = w ? cg[k].at(j) * ww.v[j] : cg[k].at(j);
+                    e[j] = dxrp ? ce[k].at(j) : 0.0f;
+                }
+                emit(i, z, g, dxrp ? e : nullptr);
+            }
         }
         for (int64_t i = threadIdx.x + static_cast<int64_t>(CACHE) * RN_THREADS; i < items; i += RN_THREADS) {
-            It z, g;
+            It z, g, e;
             z.load(xp + i * N);
             g.load(dyp + i * N);
+            if (dxrp) e.load(dxrp + i * N);
 #pragma unroll
             for (int j = 0; j < N; ++j) z.v[j] *= rstd;
             if (w) {
@@ -248,7 +281,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ xr, int64_t xr_stride, const T* __restr
 #pragma unroll
                 for (int j = 0; j < N; ++j) g.v[j] *= ww.v[j];
             }
-            second(i, z, g);
+            emit(i, z.v, g.v, dxrp ? e.v : nullptr);
         }
     }
     if (my_dw) {
@@ -257,7 +290,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ xr, int64_t xr_stride, const T* __restr
             const int64_t i = threadIdx.x + static_cast<int64_t>(k) * RN_THREADS;
             if (i < items)
 #pragma unroll
-                for (int j = 0; j < N; ++j) my_dw[i * N + j] = dw_acc[k][j];
+                for (int j = 0; j < N; ++j) my_dw[i * N + j] = s_dw[(k * RN_THREADS + threadIdx.x) * N + j];
         }
     }
 }
@@ -287,13 +320,14 @@ static int cache_for(int64_t items) {
     return 0;
 }
 
-#define XMA_RN_DISPATCH(KERNEL, VEC, items, grid, stream, ...)                                       \
-    switch (cache_for(items)) {                                                                      \
-        case 1: KERNEL<T, VEC, 1><<<grid, RN_THREADS, 0, stream>>>(__VA_ARGS__); break;              \
-        case 2: KERNEL<T, VEC, 2><<<grid, RN_THREADS, 0, stream>>>(__VA_ARGS__); break;              \
-        case 4: KERNEL<T, VEC, 4><<<grid, RN_THREADS, 0, stream>>>(__VA_ARGS__); break;              \
-        case 8: KERNEL<T, VEC, 8><<<grid, RN_THREADS, 0, stream>>>(__VA_ARGS__); break;              \
-        default: KERNEL<T, VEC, 0><<<grid, RN_THREADS, 0, stream>>>(__VA_ARGS__); break;             \
+// SMEM_PER_ITEM: dynamic shared memory per cached item slot (the backward's weight-gradient sums), 0 for none
+#define XMA_RN_DISPATCH(KERNEL, VEC, items, grid, SMEM_PER_ITEM, stream, ...)                                       \
+    switch (cache_for(items)) {                                                                                     \
+        case 1: KERNEL<T, VEC, 1><<<grid, RN_THREADS, 1 * (SMEM_PER_ITEM), stream>>>(__VA_ARGS__); break;           \
+        case 2: KERNEL<T, VEC, 2><<<grid, RN_THREADS, 2 * (SMEM_PER_ITEM), stream>>>(__VA_ARGS__); break;           \
+        case 4: KERNEL<T, VEC, 4><<<grid, RN_THREADS, 4 * (SMEM_PER_ITEM), stream>>>(__VA_ARGS__); break;           \
+        case 8: KERNEL<T, VEC, 8><<<grid, RN_THREADS, 8 * (SMEM_PER_ITEM), stream>>>(__VA_ARGS__); break;           \
+        default: KERNEL<T, VEC, 0><<<grid, RN_THREADS, 0, stream>>>(__VA_ARGS__); break;                            \
     }
 
 template <typename T>
@@ -307,10 +341,10 @@ static int rmsnorm_fwd_impl(const void* x, int64_t xs, const void* r, int64_t rs
     T* xrp = static_cast<T*>(xr);
     const int grid = rn_grid(rows);
     if (rn_vec_ok<T>(cols, {xs, r ? rs : 0, ys, xr ? xrs : 0}, {x, r, w, y, xr})) {
-        XMA_RN_DISPATCH(rmsnorm_fwd_kernel, true, cols / Vec16<T>::N, grid, st, xp, xs, rp, rs, wp, yp, ys, xrp, xrs, s,
+        XMA_RN_DISPATCH(rmsnorm_fwd_kernel, true, cols / Vec16<T>::N, grid, 0, st, xp, xs, rp, rs, wp, yp, ys, xrp, xrs, s,
                         rows, cols, eps, multiplier)
     } else {
-        XMA_RN_DISPATCH(rmsnorm_fwd_kernel, false, cols, grid, st, xp, xs, rp, rs, wp, yp, ys, xrp, xrs, s, rows, cols,
+        XMA_RN_DISPATCH(rmsnorm_fwd_kernel, false, cols, grid, 0, st, xp, xs, rp, rs, wp, yp, ys, xrp, xrs, s, rows, cols,
                         eps, multiplier)
     }
     return static_cast<int>(cudaGetLastError());
@@ -328,10 +362,11 @@ static int rmsnorm_bwd_impl(const void* xr, int64_t xrs, const void* w, const vo
     T* dxp = static_cast<T*>(dx);
     T* drp = static_cast<T*>(dr);
     if (rn_vec_ok<T>(cols, {xrs, dys, dxr ? dxrs : 0, dxs, dr ? drs : 0}, {xr, w, dy, dxr, dx, dr})) {
-        XMA_RN_DISPATCH(rmsnorm_bwd_kernel, true, cols / Vec16<T>::N, grid, st, xp, xrs, wp, dyp, dys, dxrp, dxrs, s,
+        XMA_RN_DISPATCH(rmsnorm_bwd_kernel, true, cols / Vec16<T>::N, grid,
+                        (dw_partial ? RN_THREADS * Vec16<T>::N * sizeof(float) : 0), st, xp, xrs, wp, dyp, dys, dxrp, dxrs, s,
                         dxp, dxs, drp, drs, dw_partial, rows, cols, eps, multiplier)
     } else {
-        XMA_RN_DISPATCH(rmsnorm_bwd_kernel, false, cols, grid, st, xp, xrs, wp, dyp, dys, dxrp, dxrs, s, dxp, dxs, drp,
+        XMA_RN_DISPATCH(rmsnorm_bwd_kernel, false, cols, grid, (dw_partial ? RN_THREADS * sizeof(float) : 0), st, xp, xrs, wp, dyp, dys, dxrp, dxrs, s, dxp, dxs, drp,
                         drs, dw_partial, rows, cols, eps, multiplier)
     }
     return static_cast<int>(cudaGetLastError());

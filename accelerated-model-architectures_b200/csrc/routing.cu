@@ -129,10 +129,14 @@ __global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __r
                             int* __restrict__ tile_expert, int tile_cap, int* __restrict__ row_src,
                             int* __restrict__ status) {
     __shared__ int s_tiles_total;
+    __shared__ int s_cnt[1024];  // E <= 1024 (checked by the callers)
+    // counts are read in parallel (one dependent global load per expert in a serial loop cost ~0.3 us each)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = static_cast<int>(counts[e]);
+    __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0, pad = 0, tiles = 0;
         for (int e = 0; e < E; ++e) {
-            int c = static_cast<int>(counts[e]);
+            const int c = s_cnt[e];
             run += c;
             offsets_incl[e] = run;
             pad_offsets[e] = pad;
@@ -151,19 +155,30 @@ __global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __r
     }
     __syncthreads();
     const int total = s_tiles_total;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int t0 = tile_prefix[e];
-        int t1 = t0 + (static_cast<int>(counts[e]) + XMA_ROW_PAD - 1) / XMA_ROW_PAD;
-        if (t1 > total) t1 = total;
-        for (int t = t0; t < t1; ++t) tile_expert[t] = e;
-        if (row_src) {  // pad rows at the end of the expert's block
-            const int c = static_cast<int>(counts[e]);
-            const int r1 = min(pad_offsets[e] + (t1 - t0) * XMA_ROW_PAD, tile_cap * XMA_ROW_PAD);
-            for (int r = pad_offsets[e] + c; r < r1; ++r) row_src[r] = -1;
+    // tile_expert[t] and the pad rows of row_src, written with consecutive threads on consecutive addresses
+    // (one thread per expert walking its own tiles and pad rows issued a store per 128-byte line: with
+    // 2048 tiles per expert the single CTA spent 0.3 ms there)
+    __shared__ int s_tile0[1025];
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) s_tile0[e] = tile_prefix[e];
+    __syncthreads();
+    for (int t = threadIdx.x; t < total; t += blockDim.x) {
+        int lo = 0, hi = E;  // largest e with s_tile0[e] <= t
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_tile0[mid] <= t) lo = mid;
+            else hi = mid;
         }
+        tile_expert[t] = lo;
     }
-    if (row_src) {  // allocated rows behind the last expert's block
+    if (row_src) {
         const int rows_cap = tile_cap * XMA_ROW_PAD;
+        for (int i = threadIdx.x; i < E * XMA_ROW_PAD; i += blockDim.x) {  // pad rows at the end of each expert's block
+            const int e = i / XMA_ROW_PAD;
+            const int t1 = min(s_tile0[e + 1], total);
+            const int r = s_tile0[e] * XMA_ROW_PAD + s_cnt[e] + (i % XMA_ROW_PAD);
+            if (r < t1 * XMA_ROW_PAD && r < rows_cap) row_src[r] = -1;
+        }
+        // allocated rows behind the last expert's block
         for (int r = total * XMA_ROW_PAD + threadIdx.x; r < rows_cap; r += blockDim.x) row_src[r] = -1;
     }
 }
@@ -378,12 +393,12 @@ tile_scan_kernel(SortScratch sc, int64_t tiles, int E, const int* __restrict__ o
 // locally into shared memory (one packed word per id: position in the tile and bin), so that each bin's run
 // leaves the CTA as consecutive addresses: scattering straight from registers would touch one 32-byte
 // sector per id. No CTA waits for another.
-template <typename IdT>
+template <typename IdT, int BITS>
 __global__ void __launch_bounds__(SORT_THREADS, 3)
 sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __restrict__ offsets_incl,
                     const int* __restrict__ pad_offsets, int* __restrict__ sorted_expert,
-                    int* __restrict__ sorted_scattered, int* __restrict__ row_src, SortScratch sc,
-                    int* __restrict__ status) {
+                    int* __restrict__ sorted_scattered, int* __restrict__ row_src, int* __restrict__ row_dst,
+                    SortScratch sc, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char s_raw[];
     unsigned* s_staged = reinterpret_cast<unsigned*>(s_raw);          // [TILE] (index in tile << 16) | bin
     unsigned* s_warp_cnt = s_staged + SORT_TILE;                      // [WARPS][E+1]
@@ -403,6 +418,24 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
     const int64_t base = tile * SORT_TILE;
     if (base >= n) return;  // uniform for the CTA
     const int cnt = static_cast<int>((n - base) < SORT_TILE ? (n - base) : SORT_TILE);
+    // what step 2 needs from global memory, asked for now so that it arrives while the ids are ranked
+    // (E <= 1024 bins over 512 threads: two bins per thread)
+    constexpr int BINS_PER_THREAD = SORT_MAX_BINS / SORT_THREADS;
+    unsigned pre_first[BINS_PER_THREAD], pre_gbase[BINS_PER_THREAD];
+    int pre_pad[BINS_PER_THREAD];
+    {
+        const unsigned* tile_excl = sc.tile_counts + static_cast<size_t>(tile) * E;
+        const unsigned* chunk_base = sc.chunk_base + static_cast<size_t>(tile / SCAN_TILES) * E;
+#pragma unroll
+        for (int j = 0; j < BINS_PER_THREAD; ++j) {
+            const int b = tid + j * SORT_THREADS;
+            if (b < E) {
+                pre_first[j] = chunk_base[b] + tile_excl[b];  // sorted position of the tile's first id of bin b
+                pre_gbase[j] = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
+                pre_pad[j] = pad_offsets[b];
+            }
+        }
+    }
 
     // 1. load (16 independent coalesced loads per thread) and rank
     unsigned my_bin[SORT_ITEMS];
@@ -413,8 +446,12 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
         unsigned b = static_cast<unsigned>(E);
         if (i < cnt) {
             const IdT id = __ldcs(ids + base + i);
-            if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(E)) b = static_cast<unsigned>(id);
-            else bad = true;
+            if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(E)) {
+                b = static_cast<unsigned>(id);
+            } else {
+                bad = true;
+                if (row_dst) row_dst[base + i] = -1;  // a dropped id has no grouped row
+            }
         }
         my_bin[r] = b;
     }
@@ -425,8 +462,9 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
     // before - reaches the group by shuffle (one atomic, one shuffle and one warp barrier per row; the first
     // version went through a read, two warp barriers and a write).
     // From here on my_bin[r] holds bin | (rank inside the warp's 512 ids) << 16.
-    int bits = 1;
-    while ((1 << bits) <= E) ++bits;  // bins 0..E (E = dropped) need this many bits
+    // BITS = bits of the bin index for bins 0..E (E = dropped), a template argument so that the votes unroll
+    // without a branch per bit; per bit one vote and one three-input logic operation on the running mask:
+    // m &= ~(vote ^ ones_if_bit_set).
     unsigned* wc = s_warp_cnt + warp * EB;
     const unsigned lt_mask = (1u << lane) - 1u;
 #pragma unroll
@@ -434,12 +472,10 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
         const unsigned b = my_bin[r];
         unsigned m = 0xffffffffu;
 #pragma unroll
-        for (int k = 0; k < 11; ++k) {
-            if (k < bits) {
-                const bool bit = (b >> k) & 1u;
-                const unsigned vote = __ballot_sync(0xffffffffu, bit);
-                m &= bit ? vote : ~vote;
-            }
+        for (int k = 0; k < BITS; ++k) {
+            const unsigned vote = __ballot_sync(0xffffffffu, (b >> k) & 1u);
+            const unsigned ones = 0u - ((b >> k) & 1u);  // all ones when the bit is set
+            m &= ~(vote ^ ones);
         }
         const int leader = __ffs(m) - 1;
         unsigned before = 0;
@@ -451,22 +487,21 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
     __syncthreads();
 
     // 2. per bin: exclusive scan over warps; the bin's base for this tile comes from the scanned tables
-    const unsigned* tile_excl = sc.tile_counts + static_cast<size_t>(tile) * E;
-    const unsigned* chunk_base = sc.chunk_base + static_cast<size_t>(tile / SCAN_TILES) * E;
-    for (int b = tid; b < E; b += SORT_THREADS) {
-        const unsigned first = chunk_base[b] + tile_excl[b];  // sorted position of the tile's first id of bin b
-        const unsigned gbase = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
-        const int pad0 = pad_offsets[b];
-        unsigned run = 0;
 #pragma unroll
-        for (int w = 0; w < SORT_WARPS; ++w) {
-            const unsigned t = s_warp_cnt[w * EB + b];
-            s_warp_cnt[w * EB + b] = run;
-            run += t;
+    for (int j = 0; j < BINS_PER_THREAD; ++j) {
+        const int b = tid + j * SORT_THREADS;
+        if (b < E) {
+            unsigned run = 0;
+#pragma unroll
+            for (int w = 0; w < SORT_WARPS; ++w) {
+                const unsigned t = s_warp_cnt[w * EB + b];
+                s_warp_cnt[w * EB + b] = run;
+                run += t;
+            }
+            s_bin_first[b] = run;                                // tile count for now, scanned below
+            s_dst_base[b] = static_cast<int>(pre_first[j]);      // minus the bin's start in the tile, below
+            s_pad_delta[b] = pre_pad[j] - static_cast<int>(pre_gbase[j]);
         }
-        s_bin_first[b] = run;                          // tile count for now, scanned below
-        s_dst_base[b] = static_cast<int>(first);       // minus the bin's start in the tile, below
-        s_pad_delta[b] = pad0 - static_cast<int>(gbase);
     }
     __syncthreads();
 
@@ -504,13 +539,16 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
     }
     __syncthreads();
 
-    // 4. local stable sort into shared memory
+    // 4. local stable sort into shared memory; the inverse map row_dst leaves from here, in the order of the
+    //    ids (consecutive lanes, consecutive addresses)
 #pragma unroll
     for (int r = 0; r < SORT_ITEMS; ++r) {
         const unsigned b = my_bin[r] & 0xffffu;
         if (b < static_cast<unsigned>(E)) {
             const unsigned i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
-            s_staged[s_bin_first[b] + wc[b] + (my_bin[r] >> 16)] = (i << 16) | b;
+            const unsigned j = s_bin_first[b] + wc[b] + (my_bin[r] >> 16);  // position in the sorted tile
+            s_staged[j] = (i << 16) | b;
+            if (row_dst) row_dst[base + i] = s_dst_base[b] + static_cast<int>(j) + s_pad_delta[b];
         }
     }
     __syncthreads();
@@ -703,8 +741,8 @@ namespace {
 template <typename IdT>
 int count_sort_impl(const IdT* ids, int64_t n, int E, uint32_t* counts, int* offsets_incl, int* pad_offsets,
                     int* tile_prefix, int* tile_expert, int64_t tile_cap, int* sorted_expert, int* sorted_scattered,
-                    int* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes, int* device_status,
-                    cudaStream_t stream) {
+                    int* row_src, int64_t row_cap, int* row_dst, void* scratch, int64_t scratch_bytes,
+                    int* device_status, cudaStream_t stream) {
     XMA_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(uint32_t) * E, stream));
     const int64_t tiles = xma::ceil_div(n, xma::SORT_TILE);
     const xma::SortScratch sc = xma::sort_scratch_layout(static_cast<unsigned char*>(scratch), n, E);
@@ -718,7 +756,7 @@ int count_sort_impl(const IdT* ids, int64_t n, int E, uint32_t* counts, int* off
                                          stream>>>(ids, n, E, copies, sc.tile_counts, counts, device_status);
         XMA_CUDA_TRY(cudaGetLastError());
     }
-    xma::plan_kernel<<<1, 256, 0, stream>>>(counts, E, offsets_incl, pad_offsets, tile_prefix, tile_expert,
+    xma::plan_kernel<<<1, 1024, 0, stream>>>(counts, E, offsets_incl, pad_offsets, tile_prefix, tile_expert,
                                             static_cast<int>(tile_cap), row_src, device_status);
     XMA_CUDA_TRY(cudaGetLastError());
     (void)row_cap;
@@ -728,13 +766,26 @@ int count_sort_impl(const IdT* ids, int64_t n, int E, uint32_t* counts, int* off
                                                                                       device_status);
     XMA_CUDA_TRY(cudaGetLastError());
     const size_t smem = xma::sort_smem_bytes(E);
-    auto kernel = xma::sort_scatter_kernel<IdT>;
-    if (smem > 48 * 1024) {
-        XMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    }
-    kernel<<<static_cast<int>(tiles), xma::SORT_THREADS, smem, stream>>>(
-        ids, n, E, offsets_incl, pad_offsets, sorted_expert, sorted_scattered, row_src, sc, device_status);
+    int bits = 1;
+    while ((1 << bits) <= E) ++bits;  // bins 0..E (E = dropped ids) need this many bits: 1..11
     (void)scratch_bytes;
+#define XMA_SORT_CASE(B)                                                                                          \
+    case B: {                                                                                                     \
+        auto kernel = xma::sort_scatter_kernel<IdT, B>;                                                           \
+        if (smem > 48 * 1024)                                                                                     \
+            XMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                                              static_cast<int>(smem)));                                          \
+        kernel<<<static_cast<int>(tiles), xma::SORT_THREADS, smem, stream>>>(                                     \
+            ids, n, E, offsets_incl, pad_offsets, sorted_expert, sorted_scattered, row_src, row_dst, sc,          \
+            device_status);                                                                                       \
+        break;                                                                                                    \
+    }
+    switch (bits) {
+        XMA_SORT_CASE(1) XMA_SORT_CASE(2) XMA_SORT_CASE(3) XMA_SORT_CASE(4) XMA_SORT_CASE(5) XMA_SORT_CASE(6)
+        XMA_SORT_CASE(7) XMA_SORT_CASE(8) XMA_SORT_CASE(9) XMA_SORT_CASE(10) XMA_SORT_CASE(11)
+        default: return XMA_ERR_BAD_SHAPE;
+    }
+#undef XMA_SORT_CASE
     return static_cast<int>(cudaGetLastError());
 }
 }  // namespace
@@ -773,8 +824,8 @@ int64_t xma_b200_tile_capacity(int64_t n, int num_experts) {
 int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_experts, uint32_t* counts,
                         int32_t* offsets_incl, int32_t* pad_offsets, int32_t* tile_prefix, int32_t* tile_expert,
                         int64_t tile_cap, int32_t* sorted_expert_idxs, int32_t* sorted_scattered_idxs,
-                        int32_t* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes, int* device_status,
-                        cudaStream_t stream) {
+                        int32_t* row_src, int64_t row_cap, int32_t* row_dst, void* scratch, int64_t scratch_bytes,
+                        int* device_status, cudaStream_t stream) {
     if (!counts || !offsets_incl || !pad_offsets || !tile_prefix || !tile_expert || !scratch ||
         (n > 0 && (!ids || !sorted_expert_idxs || !sorted_scattered_idxs)))
         return XMA_ERR_NULL_POINTER;
@@ -787,12 +838,12 @@ int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_expert
     if (id_dtype == XMA_I32)
         return count_sort_impl(static_cast<const int*>(ids), n, num_experts, counts, offsets_incl, pad_offsets,
                                tile_prefix, tile_expert, tile_cap, sorted_expert_idxs, sorted_scattered_idxs,
-                               row_src, row_cap, scratch, scratch_bytes, device_status, stream);
+                               row_src, row_cap, row_dst, scratch, scratch_bytes, device_status, stream);
     if (id_dtype == XMA_I64)
         return count_sort_impl(static_cast<const long long*>(ids), n, num_experts, counts, offsets_incl,
                                pad_offsets, tile_prefix, tile_expert, tile_cap, sorted_expert_idxs,
-                               sorted_scattered_idxs, row_src, row_cap, scratch, scratch_bytes, device_status,
-                               stream);
+                               sorted_scattered_idxs, row_src, row_cap, row_dst, scratch, scratch_bytes,
+                               device_status, stream);
     return XMA_ERR_BAD_DTYPE;
 }
 
@@ -857,6 +908,26 @@ namespace {
 constexpr int kMaxDevices = 64;
 std::mutex g_static_scratch_mutex;
 void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+template <typename IdT, int B>
+cudaError_t preload_scatter() {
+    cudaFuncAttributes a;
+    cudaError_t rc = cudaFuncGetAttributes(&a, xma::sort_scatter_kernel<IdT, B>);
+    if (rc != cudaSuccess) return rc;
+    if constexpr (B < 11) return preload_scatter<IdT, B + 1>();
+    return cudaSuccess;
+}
+
+cudaError_t preload_sort_kernels() {
+    cudaFuncAttributes a;
+    cudaError_t rc;
+    if ((rc = preload_scatter<int, 1>()) != cudaSuccess) return rc;
+    if ((rc = preload_scatter<long long, 1>()) != cudaSuccess) return rc;
+    if ((rc = cudaFuncGetAttributes(&a, xma::tile_histogram_kernel<int>)) != cudaSuccess) return rc;
+    if ((rc = cudaFuncGetAttributes(&a, xma::tile_histogram_kernel<long long>)) != cudaSuccess) return rc;
+    if ((rc = cudaFuncGetAttributes(&a, xma::tile_scan_kernel)) != cudaSuccess) return rc;
+    return cudaFuncGetAttributes(&a, xma::plan_kernel);
+}
 }  // namespace
 
 extern "C" {
@@ -892,13 +963,16 @@ int xma_b200_count_sort_static(const void* ids, int id_dtype, int64_t n, int num
         if (!g_static_scratch_addr[dev]) {
             void* p = nullptr;
             XMA_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_sort_scratch));
+            // every kernel a later call may launch is loaded now (the scatter kernel has one instance per width
+            // of the bin index), so that lazy loading cannot allocate behind a later call
+            XMA_CUDA_TRY(preload_sort_kernels());
             g_static_scratch_addr[dev] = p;
         }
         scratch = g_static_scratch_addr[dev];
     }
     return xma_b200_count_sort(ids, id_dtype, n, num_experts, counts, offsets_incl, pad_offsets, tile_prefix,
                                tile_expert, tile_cap, sorted_expert_idxs, sorted_scattered_idxs, row_src, row_cap,
-                               scratch, XMA_STATIC_SORT_SCRATCH_BYTES, device_status, stream);
+                               nullptr, scratch, XMA_STATIC_SORT_SCRATCH_BYTES, device_status, stream);
 }
 
 }  // extern "C"

@@ -21,8 +21,8 @@ EPI_PLAIN, EPI_SWIGLU, EPI_DSWIGLU, EPI_SWIGLU_PACKED, EPI_DSWIGLU_PACKED = 0, 1
 IMPL_AUTO, IMPL_SIMT, IMPL_TC, IMPL_TC_PAIR = 0, 1, 2, 3
 
 DEV_ID_OUT_OF_RANGE, DEV_WAIT_TIMEOUT, DEV_BAD_TILE = 1, 2, 4
-ABI_VERSION = 2
-TUNE_GU_PREFETCH, TUNE_TMA_PREFETCH, TUNE_TMA_PREFETCH_MASK, TUNE_EPI_WARPS, TUNE_PLAIN_PAIRS = 0, 1, 2, 3, 4
+ABI_VERSION = 3
+TUNE_GU_PREFETCH, TUNE_TMA_PREFETCH, TUNE_TMA_PREFETCH_MASK, TUNE_EPI_WARPS, TUNE_PLAIN_PAIRS, TUNE_DW_DYNAMIC = 0, 1, 2, 3, 4, 5
 
 _DTYPE_CODES = {
     torch.float32: F32,
@@ -44,12 +44,15 @@ _SIGNATURES = {
     "xma_b200_count_sort_scratch_bytes": [c_int64, c_int],
     "xma_b200_tile_capacity": [c_int64, c_int],
     "xma_b200_count_sort": [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p],
+                            c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
+                            c_void_p],
     "xma_b200_count_sort_static_scratch_limit": [],
     "xma_b200_count_sort_static": [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     "xma_b200_gather_rows": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int64,
                              c_void_p, c_int64, c_void_p],
+    "xma_b200_spread_rows": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64,
+                             c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p],
     "xma_b200_combine_rows": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,
                               c_int64, c_void_p],
     "xma_b200_combine_bwd": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64,

@@ -64,6 +64,7 @@ class RoutePlan:
     sorted_expert_idxs: torch.Tensor  # [R]
     sorted_scattered_idxs: torch.Tensor  # [R]
     row_src: torch.Tensor  # [tile_cap * 128] flat index of each padded grouped row, -1 = pad
+    row_dst: torch.Tensor = None  # [R] the inverse: padded grouped row of each flat index
 
     @property
     def row_cap(self) -> int:
@@ -101,10 +102,11 @@ def build_route_plan(selected_experts: torch.Tensor, num_experts: int) -> RouteP
         sorted_expert_idxs=torch.empty(R, **i32),
         sorted_scattered_idxs=torch.empty(R, **i32),
         row_src=torch.empty(tile_cap * ROW_PAD, **i32),
+        row_dst=torch.empty(R, **i32),
     )
     ops.count_sort_(
         ids, num_experts, plan.counts, plan.offsets_incl, plan.pad_offsets, plan.tile_prefix, plan.tile_expert,
-        plan.sorted_expert_idxs, plan.sorted_scattered_idxs, plan.row_src,
+        plan.sorted_expert_idxs, plan.sorted_scattered_idxs, plan.row_src, plan.row_dst,
     )
     return plan
 
@@ -221,7 +223,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w1, w2, router_weights, counts, pad_offsets, tile_prefix, tile_expert, row_src,
-                packed=False):
+                packed=False, row_dst=None):
         E, two_i, H = w1.shape
         I = two_i // 2
         ctx.packed = packed
@@ -232,7 +234,11 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         impl = ops.GEMM_IMPL
 
         xs = torch.empty(row_cap, H, **opts)
-        ops.gather_rows_(x, row_src, None, K, pad_offsets[E:], xs)
+        if row_dst is not None:
+            # token-major: every token row is read once and written to the rows of its K slots
+            ops.spread_rows_(x, row_dst, None, None, None, K, counts, pad_offsets, xs)
+        else:
+            ops.gather_rows_(x, row_src, None, K, pad_offsets[E:], xs)
         gu = torch.empty(row_cap, two_i, **opts)
         act = torch.empty(row_cap, I, **opts)
         ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, tile_expert, tile_prefix, H, two_i,
@@ -251,6 +257,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
             ctx.save_for_backward(xs, gu, act, w1, w2, counts, pad_offsets, tile_prefix, tile_expert, row_src)
         ctx.weighted = weighted
         ctx.tokens, ctx.top_k = T, K
+        ctx.row_dst = row_dst
         return y
 
     @staticmethod
@@ -271,13 +278,20 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         need_x, need_w1, need_w2, need_rw = ctx.needs_input_grad[:4]
 
         d_rw = None
-        if need_rw and ctx.weighted:
-            d_rw = torch.empty_like(router_weights)
-            ops.combine_bwd_(ys, grad_out, K, d_rw)
-
         dys = torch.empty(row_cap, H, **opts)
         coeff = router_weights.view(-1) if ctx.weighted else None
-        ops.gather_rows_(grad_out, row_src, coeff, K, pad_offsets[E:], dys)
+        if ctx.row_dst is not None:
+            # one pass: dY[t] is read once, scaled into its K grouped rows, and dotted with the K expert outputs
+            if need_rw and ctx.weighted:
+                d_rw = torch.empty_like(router_weights)
+                ops.spread_rows_(grad_out, ctx.row_dst, coeff, ys, d_rw, K, counts, pad_offsets, dys)
+            else:
+                ops.spread_rows_(grad_out, ctx.row_dst, coeff, None, None, K, counts, pad_offsets, dys)
+        else:
+            if need_rw and ctx.weighted:
+                d_rw = torch.empty_like(router_weights)
+                ops.combine_bwd_(ys, grad_out, K, d_rw)
+            ops.gather_rows_(grad_out, row_src, coeff, K, pad_offsets[E:], dys)
 
         d_w2 = None
         if need_w2:
@@ -301,7 +315,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
                 else:
                     d_x = torch.empty(T, H, **opts)
                     ops.combine_rows_(dxs, None, K, d_x)
-        return d_x, d_w1, d_w2, d_rw, None, None, None, None, None, None
+        return d_x, d_w1, d_w2, d_rw, None, None, None, None, None, None, None
 
 
 # XMA_B200_CHECK_STATUS=1: `MoE.forward` reads the device status word after every call (one host synchronisation)
@@ -453,10 +467,12 @@ class MoE(nn.Module):
 
         fused = self._fused_activation(x)
         if fused == "swiglu":
-            return _FusedSwiGLUExperts.apply(x, self.c_fc.weight, self.c_proj.weight, router_weights, *tensors)
+            return _FusedSwiGLUExperts.apply(x, self.c_fc.weight, self.c_proj.weight, router_weights, *tensors,
+                                             False, plan.row_dst)
         if fused == "swiglu_packed" and self._tensor_cores(x):
             # the interleaved epilogues exist on the tensor-core kernels only
-            return _FusedSwiGLUExperts.apply(x, self.c_fc.weight, self.c_proj.weight, router_weights, *tensors, True)
+            return _FusedSwiGLUExperts.apply(x, self.c_fc.weight, self.c_proj.weight, router_weights, *tensors,
+                                             True, plan.row_dst)
 
         h = _UpProjectionExperts.apply(x, self.c_fc.weight, self.top_k, *tensors)
         h = self.act(h)

@@ -81,6 +81,7 @@ def _count_sort_op(
     sorted_expert_idxs: Tensor,
     sorted_scattered_idxs: Tensor,
     row_src: Tensor,
+    row_dst: Optional[Tensor] = None,
 ) -> None:
     require_cuda(ids)
     n = ids.numel()
@@ -92,7 +93,7 @@ def _count_sort_op(
         lib.xma_b200_count_sort(
             ptr(ids), dtype_code(ids.dtype), n, num_experts, ptr(counts), ptr(offsets_incl), ptr(pad_offsets),
             ptr(tile_prefix), ptr(tile_expert), tile_expert.numel(), ptr(sorted_expert_idxs),
-            ptr(sorted_scattered_idxs), ptr(row_src), row_src.numel(), ptr(scratch), scratch_bytes,
+            ptr(sorted_scattered_idxs), ptr(row_src), row_src.numel(), ptr(row_dst), ptr(scratch), scratch_bytes,
             ptr(status_word(ids.device)), current_stream(ids.device)
         ),
         "xma_b200_count_sort",
@@ -110,6 +111,20 @@ def _gather_rows_op(
             ptr(rows_in_use), src.size(1), ptr(out), _row_stride(out), current_stream(src.device)
         ),
         "xma_b200_gather_rows",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::spread_rows", mutates_args={"out", "d_weights"}, device_types="cuda")
+def _spread_rows_op(src: Tensor, row_dst: Tensor, coeff: Optional[Tensor], ys: Optional[Tensor],
+                    d_weights: Optional[Tensor], top_k: int, counts: Tensor, pad_offsets: Tensor, out: Tensor) -> None:
+    require_cuda(src, row_dst, out)
+    check(
+        lib.xma_b200_spread_rows(
+            ptr(src), dtype_code(src.dtype), _row_stride(src), ptr(row_dst), ptr(coeff), ptr(ys),
+            0 if ys is None else _row_stride(ys), ptr(d_weights), top_k, src.size(0), src.size(1), ptr(out),
+            _row_stride(out), ptr(counts), ptr(pad_offsets), counts.numel(), current_stream(src.device)
+        ),
+        "xma_b200_spread_rows",
     )
 
 
@@ -375,6 +390,7 @@ route_topk_softmax_ = _wrap(_route_topk_softmax_op, "route_topk_softmax", 1)
 route_topk_softmax_bwd_ = _wrap(_route_topk_softmax_bwd_op, "route_topk_softmax_bwd", 1)
 count_sort_ = _wrap(_count_sort_op, "count_sort", 4)
 gather_rows_ = _wrap(_gather_rows_op, "gather_rows", 1)
+spread_rows_ = _wrap(_spread_rows_op, "spread_rows", 1)
 combine_rows_ = _wrap(_combine_rows_op, "combine_rows", 1)
 combine_bwd_ = _wrap(_combine_bwd_op, "combine_bwd", 1)
 grouped_gemm_rows_ = _wrap(_grouped_gemm_rows_op, "grouped_gemm_rows", 1)

@@ -266,9 +266,9 @@ def run_routing_microbench(args) -> None:
     torch.cuda.set_device(device)
     peaks, peak_kind = measured_peaks()
     hbm = float(peaks.get("hbm_gbs", PEAK_FALLBACK["hbm_gbs"]))
-    n, bins, width = 1 << 26, 256, 2048
-    rows = 1 << 23
-    steps, warm = max(args.steps, 5), max(args.warmup, 3)
+    n, bins, width = 1 << args.ids_log2, 256, 2048
+    rows = min(1 << 23, n)
+    steps, warm = max(args.steps, 5 if not args.ids_only else 1), max(args.warmup, 3 if not args.ids_only else 1)
 
     def timed(fn) -> float:
         for _ in range(warm):
@@ -296,6 +296,10 @@ def run_routing_microbench(args) -> None:
                                          "bytes": n * 20}
         if dist_name == "uniform":
             plan = build_route_plan(ids[:rows].view(-1, 1), bins)
+    if args.ids_only:  # the id kernels alone (a small, short run for a profiler capture)
+        print(json.dumps({"metric": "routing_hbm_gb_per_s", "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warm,
+                          "config": {"workload": f"c5 ids only: {n} ids over {bins} bins"}, "kernels": out}), flush=True)
+        return
     src = torch.randn(rows, width, device=device, dtype=torch.bfloat16)
     dst = torch.empty(plan.row_cap, width, device=device, dtype=torch.bfloat16)
     ms = timed(lambda: ops.gather_rows_(src, plan.row_src, None, 1, plan.rows_in_use, dst))
@@ -314,7 +318,7 @@ def run_routing_microbench(args) -> None:
         "metric": "routing_hbm_gb_per_s", "value": best["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
         "warmup": warm, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int32/bf16", "data": "synthetic",
-        "config": {"workload": "c5: routing microbench, 64 Mi ids over 256 bins; permute of 8 Mi x 2048 bf16 rows",
+        "config": {"workload": f"c5: routing microbench, {n} ids over 256 bins; permute of {rows} x 2048 bf16 rows",
                    "l2_policy": "inputs_exceed_l2"},
         "roofline": {"bound": "hbm", "kernel": "gather_rows_kernel", "achieved": best["gbs"], "peak": hbm,
                      "unit": "GB/s", "frac": best["frac"], "peak_source": f"{peak_kind} copy bandwidth",
@@ -486,6 +490,69 @@ def run_swiglu_microbench(args) -> None:
         "config": {"workload": f"swiglu: stand-alone swiglu / swiglu_packed, {B} x {H}, fp32/fp16/bf16, forward and backward",
                    "l2_policy": "inputs_exceed_l2"},
         "roofline": {"bound": "hbm", "kernel": "swiglu_bwd_kernel<bf16>", "achieved": head["gbs"], "peak": hbm,
+                     "unit": "GB/s", "frac": head["frac"], "peak_source": f"{peak_kind} copy bandwidth",
+                     "traffic": None},
+        "lowest": {"kernel": worst, **out[worst]},
+        "kernels": out,
+    }), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# fused_residual_add_rmsnorm (HBM-bound)
+# ---------------------------------------------------------------------------------------------------
+def run_rmsnorm_microbench(args) -> None:
+    """`fused_residual_add_rmsnorm` forward and backward on [16 * 4096, 4096] (the activation shape in front of the
+    dense-expert layer), fp32 / fp16 / bf16, with weight, residual and multiplier. Algorithmic bytes: forward reads
+    x and the residual and writes y and the new residual stream (4 * B * H * itemsize); backward reads the stream,
+    dy and d(stream) and writes dx and d(residual) (5 * B * H * itemsize); weight and row statistics are noise."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    from xma.functional import fused_residual_add_rmsnorm
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks.get("hbm_gbs", PEAK_FALLBACK["hbm_gbs"]))
+    B, H = 16 * 4096, 4096
+    steps, warm = max(args.steps, 20), max(args.warmup, 5)
+
+    def timed(fn) -> float:
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    out = {}
+    for dtype, tag in ((torch.float32, "f32"), (torch.float16, "f16"), (torch.bfloat16, "bf16")):
+        item = torch.empty((), dtype=dtype).element_size()
+        x = torch.randn(B, H, device=device, dtype=dtype, requires_grad=True)
+        r = torch.randn(B, H, device=device, dtype=dtype, requires_grad=True)
+        w = torch.randn(H, device=device, dtype=dtype, requires_grad=True)
+        dy, dxr = torch.randn(B, H, device=device, dtype=dtype), torch.randn(B, H, device=device, dtype=dtype)
+        ms = timed(lambda: fused_residual_add_rmsnorm(x.detach(), r.detach(), w.detach(), 1e-5, 0.9))
+        out[f"rmsnorm_fwd_{tag}"] = {"ms": ms, "gbs": 4 * B * H * item / ms / 1e6}
+        y, xr = fused_residual_add_rmsnorm(x, r, w, 1e-5, 0.9)
+        ms = timed(lambda: torch.autograd.grad((y, xr), (x, r, w), grad_outputs=(dy, dxr), retain_graph=True))
+        out[f"rmsnorm_bwd_{tag}"] = {"ms": ms, "gbs": 5 * B * H * item / ms / 1e6}
+        del y, xr, x, r, w, dy, dxr
+    for v in out.values():
+        v["frac"] = v["gbs"] / hbm
+    worst = min(out, key=lambda k: out[k]["frac"])
+    head = out["rmsnorm_fwd_bf16"]
+    print(json.dumps({
+        "metric": "rmsnorm_hbm_gb_per_s", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
+        "warmup": warm, "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"rmsnorm: fused_residual_add_rmsnorm, {B} x {H}, fp32/fp16/bf16, forward and backward "
+                               "(backward includes the sum of the weight-gradient partial rows)",
+                   "l2_policy": "inputs_exceed_l2"},
+        "roofline": {"bound": "hbm", "kernel": "rmsnorm_fwd_kernel<bf16>", "achieved": head["gbs"], "peak": hbm,
                      "unit": "GB/s", "frac": head["frac"], "peak_source": f"{peak_kind} copy bandwidth",
                      "traffic": None},
         "lowest": {"kernel": worst, **out[worst]},
@@ -868,8 +935,11 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "ep", "swiglu"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "ep", "swiglu", "rmsnorm"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--ids-log2", type=int, default=26, help="workload c5: log2 of the number of ids (default 64 Mi)")
+    ap.add_argument("--ids-only", action="store_true",
+                    help="workload c5: histogram and counting sort only, no row permute (small profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the secondary workloads (configs2 / configs3) and the parity check")
@@ -886,6 +956,8 @@ def main() -> None:
     if args.workload == "ep":
         run_ep_microbench(args)
         return
+    if args.workload == "rmsnorm":
+        return run_rmsnorm_microbench(args)
     if args.workload == "swiglu":
         run_swiglu_microbench(args)
         return

@@ -77,6 +77,8 @@ int64_t xma_b200_tile_capacity(int64_t n, int num_experts); /* 128-row tiles: n 
  *   sorted_expert_idxs[n]     ids ascending
  *   sorted_scattered_idxs[n]  flat index of each sorted row (stable: ties by flat index)
  *   row_src[row_cap]          flat index of each PADDED grouped row, -1 for pad rows (may be NULL)
+ *   row_dst[n]                the inverse map: padded grouped row of each flat index, -1 for an id
+ *                             out of range (may be NULL)
  * tile_cap >= xma_b200_tile_capacity(n, E); row_cap >= 128 * tile_cap; scratch is 256-byte
  * aligned, scratch_bytes >= xma_b200_count_sort_scratch_bytes(n, E); num_experts <= 1024.
  * Replaces `selected_experts.flatten().sort()`, continuous_count and cumsum in
@@ -84,7 +86,7 @@ int64_t xma_b200_tile_capacity(int64_t n, int num_experts); /* 128-row tiles: n 
 int xma_b200_count_sort(const void* ids, int id_dtype, int64_t n, int num_experts, uint32_t* counts,
                         int32_t* offsets_incl, int32_t* pad_offsets, int32_t* tile_prefix, int32_t* tile_expert,
                         int64_t tile_cap, int32_t* sorted_expert_idxs, int32_t* sorted_scattered_idxs,
-                        int32_t* row_src, int64_t row_cap, void* scratch, int64_t scratch_bytes,
+                        int32_t* row_src, int64_t row_cap, int32_t* row_dst, void* scratch, int64_t scratch_bytes,
                         int* device_status, cudaStream_t stream);
 
 /* xma_b200_count_sort for callers that may not allocate device memory while they run (an engine
@@ -116,6 +118,19 @@ int xma_b200_count_sort_static(const void* ids, int id_dtype, int64_t n, int num
 int xma_b200_gather_rows(const void* src, int dtype, int64_t src_row_stride, const int32_t* row_src,
                          const void* coeff, int fan_out, int64_t rows, const int32_t* rows_in_use, int64_t width,
                          void* out, int64_t out_row_stride, cudaStream_t stream);
+
+/* Token-major form of xma_b200_gather_rows for the routed rows (row_dst from xma_b200_count_sort): for every
+ * token t and slot k < top_k
+ *   out[row_dst[t * top_k + k], :] = src[t, :] * coeff[t * top_k + k]     (coeff NULL: 1; row_dst < 0: skipped)
+ * and every expert's pad rows [pad_offsets[e] + counts[e], pad_offsets[e + 1]) of `out` are written as zeros.
+ * With ys / d_weights (both or neither): d_weights[t * top_k + k] = <ys[t * top_k + k, :], src[t, :]>, which is
+ * xma_b200_combine_bwd on the row that is in registers anyway. A token's row is read once instead of once per
+ * slot. top_k <= 32. Replaces group (group_kernel.py:69-100) and, fused, the bmm of
+ * xma/layers/moe/triton_implementation/__init__.py:130-131. */
+int xma_b200_spread_rows(const void* src, int dtype, int64_t src_row_stride, const int32_t* row_dst, const void* coeff,
+                         const void* ys, int64_t ys_row_stride, void* d_weights, int top_k, int64_t tokens,
+                         int64_t width, void* out, int64_t out_row_stride, const uint32_t* counts,
+                         const int32_t* pad_offsets, int num_experts, cudaStream_t stream);
 
 /* y[t, :] = sum_k weights[t, k] * ys[row(t * top_k + k), :], fp32 accumulate, one rounding
  * (weights NULL: plain sum over the top_k slots). row(f) = row_index[f] when row_index is given
@@ -192,9 +207,11 @@ int xma_b200_grouped_gemm_choice(int kind, int dtype, int num_experts, int64_t t
  * key 0: SwiGLU-backward epilogue asks for the next tile's gate|up rows in L2 (0/1, default 1);
  * key 1: reduction blocks that the TMA producer prefetches into L2 ahead of its loads (0..255, default 0);
  * key 2: operands that prefetch covers (bit 0 = A, bit 1 = B); key 3: epilogue warps (0 = per-kernel
- * default, 4, 8); key 4: CTA pairs also for plain epilogues in the automatic choice (0/1, default 1).
+ * default, 4, 8); key 4: CTA pairs also for plain epilogues in the automatic choice (0/1, default 1);
+ * key 5: the CTA-pair weight-gradient kernel hands its tiles out by an atomic ticket, heaviest experts first,
+ * instead of a fixed stride (0/1, default 1).
  * The environment variables XMA_B200_GU_PREFETCH, XMA_B200_TMA_PREFETCH, XMA_B200_TMA_PREFETCH_MASK,
- * XMA_B200_EPI_WARPS and XMA_B200_PLAIN_PAIRS set the initial values. Stands where the reference has its
+ * XMA_B200_EPI_WARPS, XMA_B200_PLAIN_PAIRS and XMA_B200_DW_DYNAMIC set the initial values. Stands where the reference has its
  * autotune configurations (scatter_kernel.py:12-52). */
 int xma_b200_tuning_set(int key, int value);
 

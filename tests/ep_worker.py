@@ -77,7 +77,8 @@ def run_rank(rank: int, world: int, port: int, results, cfg: dict) -> None:
             moe.c_proj.weight.copy_(g0["w2"][rank * e_local : (rank + 1) * e_local])
         link = HostSyncLink(dist.group.WORLD) if (shared_gpu and transport == "peer") else None
         layer = ExpertParallelMoE(moe, g0["gate"].to(dev), overlap_chunks=cfg["chunks"], transport=transport,
-                                  link=link, fused_return=cfg.get("fused_return", True))
+                                  link=link, fused_return=cfg.get("fused_return", True),
+                                  private_copies=cfg.get("private_copies", False))
 
         errs = {}
         for step in range(cfg["steps"]):

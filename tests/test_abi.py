@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(LIB)
     for name in declared_symbols():
         assert hasattr(lib, name), f"{name} declared in include/xma_b200.h but not exported"
-    assert lib.xma_b200_abi_version() == 2
+    assert lib.xma_b200_abi_version() == 3
 
 
 def test_python_binding_covers_header():

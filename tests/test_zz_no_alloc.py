@@ -44,7 +44,7 @@ def _call(lib, ids, E, static, check_no_allocation=False):
     else:
         need = int(lib.xma_b200_count_sort_scratch_bytes(n, E))
         scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
-        rc = lib.xma_b200_count_sort(*head, scratch.data_ptr(), need, status.data_ptr(), stream)
+        rc = lib.xma_b200_count_sort(*head, None, scratch.data_ptr(), need, status.data_ptr(), stream)
     assert rc == 0, _lib.error_string(rc)
     torch.cuda.synchronize()
     if check_no_allocation:
