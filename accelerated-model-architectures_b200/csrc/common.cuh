@@ -122,6 +122,45 @@ __device__ __forceinline__ void store16_stream(T* p, const Vec16<T>& r) {
     __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&r));
 }
 
+// Whole-packet conversions. 16-bit types convert two elements per instruction (cvt.*x2), which halves the
+// conversion and packing work of the elementwise kernels compared with one scalar conversion per element.
+__device__ __forceinline__ void vec_to_f32(const Vec16<float>& q, float* f) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = q.v[i];
+}
+__device__ __forceinline__ void vec_to_f32(const Vec16<__half>& q, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ void vec_to_f32(const Vec16<__nv_bfloat16>& q, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ void vec_from_f32(const float* f, Vec16<float>& q) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q.v[i] = f[i];
+}
+__device__ __forceinline__ void vec_from_f32(const float* f, Vec16<__half>& q) {
+    __half2* h = reinterpret_cast<__half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+}
+__device__ __forceinline__ void vec_from_f32(const float* f, Vec16<__nv_bfloat16>& q) {
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+}
+
 __host__ __device__ inline bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Exact logistic function in fp32 (the torch path of the reference uses F.silu on fp32 values).

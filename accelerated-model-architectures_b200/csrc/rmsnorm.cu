@@ -39,19 +39,17 @@ struct Item {
     static constexpr int N = VEC ? Vec16<T>::N : 1;
     float v[N];
     __device__ __forceinline__ void load(const T* p) {
-        if (VEC) {
+        if constexpr (VEC) {
             const Vec16<T> q = load16(p);
-#pragma unroll
-            for (int j = 0; j < N; ++j) v[j] = to_f32(q.v[j]);
+            vec_to_f32(q, v);
         } else {
             v[0] = to_f32(p[0]);
         }
     }
     __device__ __forceinline__ void store(T* p) const {
-        if (VEC) {
+        if constexpr (VEC) {
             Vec16<T> q;
-#pragma unroll
-            for (int j = 0; j < N; ++j) q.v[j] = from_f32<T>(v[j]);
+            vec_from_f32(v, q);
             store16(p, q);
         } else {
             p[0] = from_f32<T>(v[0]);

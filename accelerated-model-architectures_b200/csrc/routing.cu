@@ -209,17 +209,6 @@ constexpr unsigned long long LB_PREFIX = 2ull << 62;
 constexpr unsigned long long LB_STATE_MASK = 3ull << 62;
 constexpr unsigned LB_MAX_POLLS = 1u << 22;  // bounded wait; on expiry the status word gets the timeout bit
 
-__host__ __device__ inline size_t sort_smem_bytes(int E) {
-    // staged[TILE] u32, warp_cnt[WARPS][E+1] u32, bin_first[E+1] u32, dst_base[E] i32, pad_delta[E] i32,
-    // scan scratch[32] u32 + tile id
-    size_t b = static_cast<size_t>(SORT_TILE) * sizeof(unsigned);
-    b += static_cast<size_t>(SORT_WARPS) * (E + 1) * sizeof(unsigned);
-    b += static_cast<size_t>(E + 1) * sizeof(unsigned);
-    b += 2 * static_cast<size_t>(E) * sizeof(int);
-    b += 40 * sizeof(unsigned);
-    return (b + 15) & ~static_cast<size_t>(15);
-}
-
 // Scratch of one count_sort call (the caller's memory, zeroed by the call before use):
 //   [0, 256)            ticket counter of the scan kernel
 //   tile_counts         [tiles][E] u32   per-tile counts, turned into exclusive prefixes inside the chunk
@@ -387,42 +376,59 @@ tile_scan_kernel(SortScratch sc, int64_t tiles, int E, const int* __restrict__ o
     }
 }
 
-// Pass 2, one tile of SORT_TILE ids per CTA: every warp loads its 512 contiguous ids row by row (coalesced)
-// and ranks them against its own per-bin counters (stable: rows in order, lanes in order); one thread per bin
-// scans the warps and fetches the bin's base for this tile from the scanned tables. The tile is then sorted
-// locally into shared memory (one packed word per id: position in the tile and bin), so that each bin's run
-// leaves the CTA as consecutive addresses: scattering straight from registers would touch one 32-byte
-// sector per id. No CTA waits for another.
-template <typename IdT, int BITS>
+// Pass 2, one tile of SORT_TILE ids per CTA: the tile is sorted by bin inside the CTA, stably, by a
+// least-significant-digit radix sort with 4-bit digits (two passes for up to 256 bins, three up to 1024), and
+// then leaves as runs of consecutive addresses (scattering straight from registers would touch one 32-byte
+// sector per id). Ranking is the counter scheme of block radix sorts: thread t holds 16 consecutive elements of
+// the current sequence and counts its digits in its own byte counters cnt[digit][t]; the exclusive prefix of all
+// counters in (digit, thread) order is the position of a thread's first element of a digit, the count at the
+// moment an element was met its offset behind that - about 20 warp instructions per 32 ids and pass, where
+// the first version (one warp vote per bit of the bin index to find the lanes with equal bins, then per-warp
+// counters) spent about 200 per 32 ids and was bound by instruction issue at 0.2 of the HBM roof.
+// No CTA waits for another: the tile's base in every bin comes from the scanned tables.
+constexpr int RADIX_BITS = 4;
+constexpr int RADIX = 1 << RADIX_BITS;
+constexpr unsigned SORT_INVALID = 0xffffffffu;
+
+__host__ __device__ inline size_t sort_smem_bytes(int E) {
+    // items[TILE] u32, cnt[RADIX][THREADS] u8, pref[RADIX][THREADS] u16, first[E] u32, dst_base[E] i32,
+    // pad_delta[E] i32, scan scratch
+    size_t b = static_cast<size_t>(SORT_TILE) * sizeof(unsigned);
+    b += static_cast<size_t>(RADIX) * SORT_THREADS * (sizeof(unsigned char) + sizeof(unsigned short));
+    b += 3 * static_cast<size_t>(E) * sizeof(int);
+    b += 64 * sizeof(unsigned);
+    return (b + 15) & ~static_cast<size_t>(15);
+}
+
+template <typename IdT>
 __global__ void __launch_bounds__(SORT_THREADS, 3)
-sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __restrict__ offsets_incl,
+sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, int passes, const int* __restrict__ offsets_incl,
                     const int* __restrict__ pad_offsets, int* __restrict__ sorted_expert,
                     int* __restrict__ sorted_scattered, int* __restrict__ row_src, int* __restrict__ row_dst,
                     SortScratch sc, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char s_raw[];
-    unsigned* s_staged = reinterpret_cast<unsigned*>(s_raw);          // [TILE] (index in tile << 16) | bin
-    unsigned* s_warp_cnt = s_staged + SORT_TILE;                      // [WARPS][E+1]
-    unsigned* s_bin_first = s_warp_cnt + SORT_WARPS * (E + 1);        // [E+1] start of each bin inside the tile
-    int* s_dst_base = reinterpret_cast<int*>(s_bin_first + (E + 1));  // [E] global position - position in tile
-    int* s_pad_delta = s_dst_base + E;                                // [E] padded row - sorted row
-    unsigned* s_scan = reinterpret_cast<unsigned*>(s_pad_delta + E);  // [32]
+    unsigned* s_items = reinterpret_cast<unsigned*>(s_raw);                                   // [TILE] (i << 16) | bin
+    unsigned char* s_cnt = reinterpret_cast<unsigned char*>(s_items + SORT_TILE);             // [RADIX][THREADS]
+    unsigned short* s_pref = reinterpret_cast<unsigned short*>(s_cnt + RADIX * SORT_THREADS);  // [RADIX][THREADS]
+    unsigned* s_first = reinterpret_cast<unsigned*>(s_pref + RADIX * SORT_THREADS);           // [E]
+    int* s_dst_base = reinterpret_cast<int*>(s_first + E);                                    // [E]
+    int* s_pad_delta = s_dst_base + E;                                                        // [E]
+    unsigned* s_scan = reinterpret_cast<unsigned*>(s_pad_delta + E);                          // [64]
+    unsigned short* s_inv = reinterpret_cast<unsigned short*>(s_cnt);  // [TILE], after the passes: position of id i
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const int EB = E + 1;  // bin E collects ids that are out of range (dropped)
-
-    for (int i = tid; i < SORT_WARPS * EB; i += SORT_THREADS) s_warp_cnt[i] = 0u;
-    __syncthreads();
     const int64_t tile = blockIdx.x;
     const int64_t base = tile * SORT_TILE;
     if (base >= n) return;  // uniform for the CTA
     const int cnt = static_cast<int>((n - base) < SORT_TILE ? (n - base) : SORT_TILE);
-    // what step 2 needs from global memory, asked for now so that it arrives while the ids are ranked
+
+    // what the output step needs from global memory, asked for now so that it arrives during the sort
     // (E <= 1024 bins over 512 threads: two bins per thread)
     constexpr int BINS_PER_THREAD = SORT_MAX_BINS / SORT_THREADS;
-    unsigned pre_first[BINS_PER_THREAD], pre_gbase[BINS_PER_THREAD];
-    int pre_pad[BINS_PER_THREAD];
+    unsigned pre_first[BINS_PER_THREAD];
+    int pre_delta[BINS_PER_THREAD];
     {
         const unsigned* tile_excl = sc.tile_counts + static_cast<size_t>(tile) * E;
         const unsigned* chunk_base = sc.chunk_base + static_cast<size_t>(tile / SCAN_TILES) * E;
@@ -431,138 +437,178 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int* __
             const int b = tid + j * SORT_THREADS;
             if (b < E) {
                 pre_first[j] = chunk_base[b] + tile_excl[b];  // sorted position of the tile's first id of bin b
-                pre_gbase[j] = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
-                pre_pad[j] = pad_offsets[b];
+                const int gbase = (b == 0) ? 0 : offsets_incl[b - 1];
+                pre_delta[j] = pad_offsets[b] - gbase;        // padded row - sorted row
             }
         }
     }
 
-    // 1. load (16 independent coalesced loads per thread) and rank
-    unsigned my_bin[SORT_ITEMS];
+    // 1. load: thread t takes the 16 consecutive ids [16 t, 16 t + 16) of the tile
+    unsigned item[SORT_ITEMS];
     bool bad = false;
+    {
+        constexpr int V = 16 / sizeof(IdT);
+        const IdT* src = ids + base + tid * SORT_ITEMS;
+        IdT raw[SORT_ITEMS];
+        if (cnt == SORT_TILE && (reinterpret_cast<uintptr_t>(ids) & 15u) == 0) {
 #pragma unroll
-    for (int r = 0; r < SORT_ITEMS; ++r) {
-        const int i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
-        unsigned b = static_cast<unsigned>(E);
-        if (i < cnt) {
-            const IdT id = __ldcs(ids + base + i);
-            if (static_cast<unsigned long long>(id) < static_cast<unsigned long long>(E)) {
-                b = static_cast<unsigned>(id);
-            } else {
-                bad = true;
-                if (row_dst) row_dst[base + i] = -1;  // a dropped id has no grouped row
+            for (int j = 0; j < SORT_ITEMS / V; ++j) {
+                const Vec16<IdT> q = load16_stream(src + j * V);
+#pragma unroll
+                for (int i = 0; i < V; ++i) raw[j * V + i] = q.v[i];
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < SORT_ITEMS; ++k) raw[k] = (tid * SORT_ITEMS + k < cnt) ? src[k] : static_cast<IdT>(0);
+        }
+#pragma unroll
+        for (int k = 0; k < SORT_ITEMS; ++k) {
+            const int i = tid * SORT_ITEMS + k;
+            unsigned w = SORT_INVALID;
+            if (i < cnt) {
+                if (static_cast<unsigned long long>(raw[k]) < static_cast<unsigned long long>(E)) {
+                    w = (static_cast<unsigned>(i) << 16) | static_cast<unsigned>(raw[k]);
+                } else {
+                    bad = true;
+                    if (row_dst) row_dst[base + i] = -1;  // a dropped id has no grouped row
+                }
+            }
+            item[k] = w;
+        }
+    }
+
+    // 2. stable radix passes, least significant digit first
+    unsigned n_valid = 0;
+    for (int pass = 0; pass < passes; ++pass) {
+        const int shift = pass * RADIX_BITS;
+        // zero the counters (16 bytes per thread)
+        reinterpret_cast<uint4*>(s_cnt)[tid] = make_uint4(0u, 0u, 0u, 0u);
+        __syncthreads();
+        // count: old value = how many elements of this digit the thread has met before
+        unsigned long long met = 0ull;  // 16 x 4 bits
+#pragma unroll
+        for (int k = 0; k < SORT_ITEMS; ++k) {
+            if (item[k] != SORT_INVALID) {
+                const unsigned d = (item[k] >> shift) & (RADIX - 1);
+                unsigned char* c = s_cnt + d * SORT_THREADS + tid;
+                const unsigned old = *c;
+                *c = static_cast<unsigned char>(old + 1u);
+                met |= static_cast<unsigned long long>(old) << (4 * k);
             }
         }
-        my_bin[r] = b;
-    }
-    // Rank of every id inside its warp's 512 ids (rows in order, lanes in order: stable). Per row of 32 ids:
-    // the lanes holding the same bin come from one ballot per bit of the bin index (the native match
-    // instruction is several times slower than log2(E) votes); the lowest of them adds the group's size to the
-    // warp's counter of that bin with a shared-memory atomic, whose return value - the count of the rows
-    // before - reaches the group by shuffle (one atomic, one shuffle and one warp barrier per row; the first
-    // version went through a read, two warp barriers and a write).
-    // From here on my_bin[r] holds bin | (rank inside the warp's 512 ids) << 16.
-    // BITS = bits of the bin index for bins 0..E (E = dropped), a template argument so that the votes unroll
-    // without a branch per bit; per bit one vote and one three-input logic operation on the running mask:
-    // m &= ~(vote ^ ones_if_bit_set).
-    unsigned* wc = s_warp_cnt + warp * EB;
-    const unsigned lt_mask = (1u << lane) - 1u;
+        __syncthreads();
+        // scan of all counters in (digit, thread) order: thread t owns the 16 counters [16 t, 16 t + 16)
+        {
+            const uint4 q = reinterpret_cast<const uint4*>(s_cnt)[tid];
+            const unsigned words[4] = {q.x, q.y, q.z, q.w};
+            unsigned run[16];
+            unsigned total = 0;
 #pragma unroll
-    for (int r = 0; r < SORT_ITEMS; ++r) {
-        const unsigned b = my_bin[r];
-        unsigned m = 0xffffffffu;
+            for (int j = 0; j < 16; ++j) {
+                run[j] = total;
+                total += (words[j >> 2] >> (8 * (j & 3))) & 0xffu;
+            }
+            unsigned incl = total;
 #pragma unroll
-        for (int k = 0; k < BITS; ++k) {
-            const unsigned vote = __ballot_sync(0xffffffffu, (b >> k) & 1u);
-            const unsigned ones = 0u - ((b >> k) & 1u);  // all ones when the bit is set
-            m &= ~(vote ^ ones);
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            if (lane == 31) s_scan[warp] = incl;
+            __syncthreads();
+            unsigned wsum = (lane < SORT_WARPS) ? s_scan[lane] : 0u;
+            unsigned winc = wsum;
+#pragma unroll
+            for (int o = 1; o < SORT_WARPS; o <<= 1) {
+                const unsigned t = __shfl_up_sync(0xffffffffu, winc, o);
+                if (lane >= o) winc += t;
+            }
+            const unsigned before_warp = __shfl_sync(0xffffffffu, winc - wsum, warp);
+            n_valid = __shfl_sync(0xffffffffu, winc, SORT_WARPS - 1);
+            const unsigned tbase = before_warp + incl - total;
+            uint4 lo, hi;
+            lo.x = (tbase + run[0]) | ((tbase + run[1]) << 16);
+            lo.y = (tbase + run[2]) | ((tbase + run[3]) << 16);
+            lo.z = (tbase + run[4]) | ((tbase + run[5]) << 16);
+            lo.w = (tbase + run[6]) | ((tbase + run[7]) << 16);
+            hi.x = (tbase + run[8]) | ((tbase + run[9]) << 16);
+            hi.y = (tbase + run[10]) | ((tbase + run[11]) << 16);
+            hi.z = (tbase + run[12]) | ((tbase + run[13]) << 16);
+            hi.w = (tbase + run[14]) | ((tbase + run[15]) << 16);
+            reinterpret_cast<uint4*>(s_pref)[2 * tid] = lo;
+            reinterpret_cast<uint4*>(s_pref)[2 * tid + 1] = hi;
         }
-        const int leader = __ffs(m) - 1;
-        unsigned before = 0;
-        if (lane == leader) before = atomicAdd(&wc[b], static_cast<unsigned>(__popc(m)));
-        before = __shfl_sync(0xffffffffu, before, leader);
-        my_bin[r] = b | ((before + __popc(m & lt_mask)) << 16);
-        __syncwarp();  // orders this row's atomics before the next row's, whichever lanes issue them
+        __syncthreads();
+        // rank and move: position = prefix of (digit, thread) + elements of the digit met before in the thread
+#pragma unroll
+        for (int k = 0; k < SORT_ITEMS; ++k) {
+            if (item[k] != SORT_INVALID) {
+                const unsigned d = (item[k] >> shift) & (RADIX - 1);
+                const unsigned pos = s_pref[d * SORT_THREADS + tid] + (static_cast<unsigned>(met >> (4 * k)) & 15u);
+                s_items[pos] = item[k];
+            }
+        }
+        __syncthreads();
+        if (pass + 1 < passes) {  // next pass: the thread takes 16 consecutive elements of the new sequence
+            const uint4* p = reinterpret_cast<const uint4*>(s_items + tid * SORT_ITEMS);
+#pragma unroll
+            for (int j = 0; j < SORT_ITEMS / 4; ++j) {
+                const uint4 q = p[j];
+                const unsigned w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const unsigned pos = tid * SORT_ITEMS + j * 4 + i;
+                    item[j * 4 + i] = (pos < n_valid) ? w4[i] : SORT_INVALID;
+                }
+            }
+            // (the barrier behind the next pass's counter reset orders these reads before its writes to s_items)
+        }
     }
-    __syncthreads();
 
-    // 2. per bin: exclusive scan over warps; the bin's base for this tile comes from the scanned tables
+    // 3. tables of the output step; s_items[0, n_valid) is the tile sorted by bin
 #pragma unroll
     for (int j = 0; j < BINS_PER_THREAD; ++j) {
         const int b = tid + j * SORT_THREADS;
         if (b < E) {
-            unsigned run = 0;
-#pragma unroll
-            for (int w = 0; w < SORT_WARPS; ++w) {
-                const unsigned t = s_warp_cnt[w * EB + b];
-                s_warp_cnt[w * EB + b] = run;
-                run += t;
-            }
-            s_bin_first[b] = run;                                // tile count for now, scanned below
-            s_dst_base[b] = static_cast<int>(pre_first[j]);      // minus the bin's start in the tile, below
-            s_pad_delta[b] = pre_pad[j] - static_cast<int>(pre_gbase[j]);
+            s_first[b] = pre_first[j];
+            s_pad_delta[b] = pre_delta[j];
         }
     }
-    __syncthreads();
-
-    // 3. exclusive scan of the tile's bin counts -> start of each bin inside the tile
-    {
-        constexpr int PER = SORT_MAX_BINS / SORT_THREADS;
-        unsigned v[PER];
-        unsigned sum = 0;
-#pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            const int b = tid * PER + j;
-            v[j] = (b < E) ? s_bin_first[b] : 0u;
-            sum += v[j];
-        }
-        unsigned incl = sum;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += t;
-        }
-        if (lane == 31) s_scan[warp] = incl;
-        __syncthreads();
-        unsigned run = incl - sum;
-        for (int w = 0; w < warp; ++w) run += s_scan[w];
-#pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            const int b = tid * PER + j;
-            if (b < E) {
-                s_bin_first[b] = run;
-                s_dst_base[b] -= static_cast<int>(run);
-            }
-            run += v[j];
-            if (b == E - 1) s_bin_first[E] = run;  // number of in-range ids in the tile
-        }
+    if (row_dst) {  // 0xffff = "id was dropped"
+        const uint4 ones = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+        reinterpret_cast<uint4*>(s_inv)[2 * tid] = ones;
+        reinterpret_cast<uint4*>(s_inv)[2 * tid + 1] = ones;
     }
     __syncthreads();
-
-    // 4. local stable sort into shared memory; the inverse map row_dst leaves from here, in the order of the
-    //    ids (consecutive lanes, consecutive addresses)
-#pragma unroll
-    for (int r = 0; r < SORT_ITEMS; ++r) {
-        const unsigned b = my_bin[r] & 0xffffu;
-        if (b < static_cast<unsigned>(E)) {
-            const unsigned i = warp * (32 * SORT_ITEMS) + r * 32 + lane;
-            const unsigned j = s_bin_first[b] + wc[b] + (my_bin[r] >> 16);  // position in the sorted tile
-            s_staged[j] = (i << 16) | b;
-            if (row_dst) row_dst[base + i] = s_dst_base[b] + static_cast<int>(j) + s_pad_delta[b];
-        }
-    }
-    __syncthreads();
-
-    // 5. each bin's run goes out as consecutive addresses
-    const int valid = static_cast<int>(s_bin_first[E]);
+    const int valid = static_cast<int>(n_valid);
+    // where a bin's run starts in the tile: dst_base = (first sorted position of the bin for this tile) - start
     for (int j = tid; j < valid; j += SORT_THREADS) {
-        const unsigned word = s_staged[j];
+        const unsigned b = s_items[j] & 0xffffu;
+        if (j == 0 || (s_items[j - 1] & 0xffffu) != b) s_dst_base[b] = static_cast<int>(s_first[b]) - j;
+    }
+    __syncthreads();
+
+    // 4. each bin's run goes out as consecutive addresses
+    for (int j = tid; j < valid; j += SORT_THREADS) {
+        const unsigned word = s_items[j];
         const unsigned b = word & 0xffffu;
-        const int f = static_cast<int>(base) + static_cast<int>(word >> 16);
+        const unsigned i = word >> 16;
+        const int f = static_cast<int>(base) + static_cast<int>(i);
         const int g = s_dst_base[b] + j;
         sorted_scattered[g] = f;
         sorted_expert[g] = static_cast<int>(b);
         if (row_src) row_src[g + s_pad_delta[b]] = f;
+        if (row_dst) s_inv[i] = static_cast<unsigned short>(j);
+    }
+    if (row_dst) {  // the inverse map leaves in the order of the ids
+        __syncthreads();
+        for (int i = tid; i < cnt; i += SORT_THREADS) {
+            const unsigned j = s_inv[i];
+            if (j != 0xffffu) {
+                const unsigned b = s_items[j] & 0xffffu;
+                row_dst[base + i] = s_dst_base[b] + static_cast<int>(j) + s_pad_delta[b];
+            }
+        }
     }
     if (bad && status) atomicOr(status, XMA_DEV_ID_OUT_OF_RANGE);
 }
@@ -767,25 +813,14 @@ int count_sort_impl(const IdT* ids, int64_t n, int E, uint32_t* counts, int* off
     XMA_CUDA_TRY(cudaGetLastError());
     const size_t smem = xma::sort_smem_bytes(E);
     int bits = 1;
-    while ((1 << bits) <= E) ++bits;  // bins 0..E (E = dropped ids) need this many bits: 1..11
+    while ((1 << bits) < E) ++bits;  // bits of the largest bin index E - 1
+    const int passes = (bits + xma::RADIX_BITS - 1) / xma::RADIX_BITS;
     (void)scratch_bytes;
-#define XMA_SORT_CASE(B)                                                                                          \
-    case B: {                                                                                                     \
-        auto kernel = xma::sort_scatter_kernel<IdT, B>;                                                           \
-        if (smem > 48 * 1024)                                                                                     \
-            XMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
-                                              static_cast<int>(smem)));                                          \
-        kernel<<<static_cast<int>(tiles), xma::SORT_THREADS, smem, stream>>>(                                     \
-            ids, n, E, offsets_incl, pad_offsets, sorted_expert, sorted_scattered, row_src, row_dst, sc,          \
-            device_status);                                                                                       \
-        break;                                                                                                    \
-    }
-    switch (bits) {
-        XMA_SORT_CASE(1) XMA_SORT_CASE(2) XMA_SORT_CASE(3) XMA_SORT_CASE(4) XMA_SORT_CASE(5) XMA_SORT_CASE(6)
-        XMA_SORT_CASE(7) XMA_SORT_CASE(8) XMA_SORT_CASE(9) XMA_SORT_CASE(10) XMA_SORT_CASE(11)
-        default: return XMA_ERR_BAD_SHAPE;
-    }
-#undef XMA_SORT_CASE
+    auto kernel = xma::sort_scatter_kernel<IdT>;
+    XMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    kernel<<<static_cast<int>(tiles), xma::SORT_THREADS, smem, stream>>>(
+        ids, n, E, passes, offsets_incl, pad_offsets, sorted_expert, sorted_scattered, row_src, row_dst, sc,
+        device_status);
     return static_cast<int>(cudaGetLastError());
 }
 }  // namespace
@@ -909,20 +944,11 @@ constexpr int kMaxDevices = 64;
 std::mutex g_static_scratch_mutex;
 void* g_static_scratch_addr[kMaxDevices] = {nullptr};
 
-template <typename IdT, int B>
-cudaError_t preload_scatter() {
-    cudaFuncAttributes a;
-    cudaError_t rc = cudaFuncGetAttributes(&a, xma::sort_scatter_kernel<IdT, B>);
-    if (rc != cudaSuccess) return rc;
-    if constexpr (B < 11) return preload_scatter<IdT, B + 1>();
-    return cudaSuccess;
-}
-
 cudaError_t preload_sort_kernels() {
     cudaFuncAttributes a;
     cudaError_t rc;
-    if ((rc = preload_scatter<int, 1>()) != cudaSuccess) return rc;
-    if ((rc = preload_scatter<long long, 1>()) != cudaSuccess) return rc;
+    if ((rc = cudaFuncGetAttributes(&a, xma::sort_scatter_kernel<int>)) != cudaSuccess) return rc;
+    if ((rc = cudaFuncGetAttributes(&a, xma::sort_scatter_kernel<long long>)) != cudaSuccess) return rc;
     if ((rc = cudaFuncGetAttributes(&a, xma::tile_histogram_kernel<int>)) != cudaSuccess) return rc;
     if ((rc = cudaFuncGetAttributes(&a, xma::tile_histogram_kernel<long long>)) != cudaSuccess) return rc;
     if ((rc = cudaFuncGetAttributes(&a, xma::tile_scan_kernel)) != cudaSuccess) return rc;
@@ -963,8 +989,8 @@ int xma_b200_count_sort_static(const void* ids, int id_dtype, int64_t n, int num
         if (!g_static_scratch_addr[dev]) {
             void* p = nullptr;
             XMA_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_sort_scratch));
-            // every kernel a later call may launch is loaded now (the scatter kernel has one instance per width
-            // of the bin index), so that lazy loading cannot allocate behind a later call
+            // every kernel a later call may launch is loaded now, so that lazy loading cannot allocate behind a
+            // later call
             XMA_CUDA_TRY(preload_sort_kernels());
             g_static_scratch_addr[dev] = p;
         }

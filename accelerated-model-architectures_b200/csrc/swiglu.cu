@@ -85,10 +85,14 @@ swiglu_fwd_kernel(const T* __restrict__ g, int64_t g_stride, const T* __restrict
 #pragma unroll
         for (int k = 0; k < EW_UNROLL; ++k)
             if (on[k]) {
-                Vec16<T> o;
+                constexpr int N = Vec16<T>::N;
+                float af[N], bf[N], of[N];
+                vec_to_f32(a[k], af);
+                vec_to_f32(b[k], bf);
 #pragma unroll
-                for (int j = 0; j < Vec16<T>::N; ++j)
-                    o.v[j] = from_f32<T>(swiglu_f<T>(to_f32(a[k].v[j]), to_f32(b[k].v[j])));
+                for (int j = 0; j < N; ++j) of[j] = swiglu_f<T>(af[j], bf[j]);
+                Vec16<T> o;
+                vec_from_f32(of, o);
                 store16_stream(y + r[k] * y_stride + c[k], o);
             }
     } else {
@@ -119,14 +123,16 @@ swiglu_bwd_kernel(const T* __restrict__ g, int64_t g_stride, const T* __restrict
 #pragma unroll
         for (int k = 0; k < EW_UNROLL; ++k)
             if (on[k]) {
-                Vec16<T> og, ou;
+                constexpr int N = Vec16<T>::N;
+                float af[N], bf[N], df[N], gf[N], uf[N];
+                vec_to_f32(a[k], af);
+                vec_to_f32(b[k], bf);
+                vec_to_f32(d[k], df);
 #pragma unroll
-                for (int j = 0; j < Vec16<T>::N; ++j) {
-                    float x, z;
-                    swiglu_b<T>(to_f32(a[k].v[j]), to_f32(b[k].v[j]), to_f32(d[k].v[j]), x, z);
-                    og.v[j] = from_f32<T>(x);
-                    ou.v[j] = from_f32<T>(z);
-                }
+                for (int j = 0; j < N; ++j) swiglu_b<T>(af[j], bf[j], df[j], gf[j], uf[j]);
+                Vec16<T> og, ou;
+                vec_from_f32(gf, og);
+                vec_from_f32(uf, ou);
                 store16_stream(dg + r[k] * dg_stride + c[k], og);
                 store16_stream(du + r[k] * du_stride + c[k], ou);
             }
@@ -162,12 +168,16 @@ swiglu_packed_fwd_kernel(const T* __restrict__ x, int64_t x_stride, T* __restric
 #pragma unroll
         for (int k = 0; k < EW_UNROLL; ++k)
             if (on[k]) {
-                Vec16<T> o;
+                float af[N], bf[N], of[N];
+                vec_to_f32(a[k], af);
+                vec_to_f32(b[k], bf);
 #pragma unroll
                 for (int j = 0; j < N / 2; ++j) {
-                    o.v[j] = from_f32<T>(swiglu_f<T>(to_f32(a[k].v[2 * j]), to_f32(a[k].v[2 * j + 1])));
-                    o.v[j + N / 2] = from_f32<T>(swiglu_f<T>(to_f32(b[k].v[2 * j]), to_f32(b[k].v[2 * j + 1])));
+                    of[j] = swiglu_f<T>(af[2 * j], af[2 * j + 1]);
+                    of[j + N / 2] = swiglu_f<T>(bf[2 * j], bf[2 * j + 1]);
                 }
+                Vec16<T> o;
+                vec_from_f32(of, o);
                 store16_stream(y + r[k] * y_stride + c[k], o);
             }
     } else {
@@ -198,17 +208,18 @@ swiglu_packed_bwd_kernel(const T* __restrict__ x, int64_t x_stride, const T* __r
 #pragma unroll
         for (int k = 0; k < EW_UNROLL; ++k)
             if (on[k]) {
-                Vec16<T> oa, ob;
+                float af[N], bf[N], df[N], pa[N], pb[N];
+                vec_to_f32(a[k], af);
+                vec_to_f32(b[k], bf);
+                vec_to_f32(d[k], df);
 #pragma unroll
                 for (int j = 0; j < N / 2; ++j) {
-                    float p, q;
-                    swiglu_b<T>(to_f32(a[k].v[2 * j]), to_f32(a[k].v[2 * j + 1]), to_f32(d[k].v[j]), p, q);
-                    oa.v[2 * j] = from_f32<T>(p);
-                    oa.v[2 * j + 1] = from_f32<T>(q);
-                    swiglu_b<T>(to_f32(b[k].v[2 * j]), to_f32(b[k].v[2 * j + 1]), to_f32(d[k].v[j + N / 2]), p, q);
-                    ob.v[2 * j] = from_f32<T>(p);
-                    ob.v[2 * j + 1] = from_f32<T>(q);
+                    swiglu_b<T>(af[2 * j], af[2 * j + 1], df[j], pa[2 * j], pa[2 * j + 1]);
+                    swiglu_b<T>(bf[2 * j], bf[2 * j + 1], df[j + N / 2], pb[2 * j], pb[2 * j + 1]);
                 }
+                Vec16<T> oa, ob;
+                vec_from_f32(pa, oa);
+                vec_from_f32(pb, ob);
                 store16_stream(dx + r[k] * dx_stride + 2 * c[k], oa);
                 store16_stream(dx + r[k] * dx_stride + 2 * c[k] + N, ob);
             }

@@ -691,7 +691,8 @@ def build_workload(b: Bench, name: str):
                     print(f"peer transport unavailable ({exc}); using NCCL all-to-all", file=sys.stderr)
                 b.transport = "nccl"
         layer = ExpertParallelMoE(moe, gate, world_group=b.dist.group.WORLD, overlap_chunks=args.ep_chunks,
-                                  transport=b.transport, fused_return=args.fused_return)
+                                  transport=b.transport, fused_return=args.fused_return,
+                                  private_copies=args.private_copies)
     else:
         with torch.no_grad():
             moe.gate.weight.copy_(gate)
@@ -792,6 +793,7 @@ def time_end_to_end(b: Bench, name: str, layer, x_dev, dy_dev, steps: int) -> di
     uploaded = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
     copy_events: list = []
+    step_ticks: list = []
 
     def upload(s: int) -> None:
         k = s & 1
@@ -816,6 +818,9 @@ def time_end_to_end(b: Bench, name: str, layer, x_dev, dy_dev, steps: int) -> di
             main_stream.wait_event(uploaded[k])
             y, dx, _ = step(x_buf[k], dy_buf[k])
             consumed[k].record(main_stream)
+            tick = torch.cuda.Event(enable_timing=True)
+            tick.record(main_stream)
+            step_ticks.append(tick)
             d2h.wait_event(consumed[k])
             with torch.cuda.stream(d2h):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -831,6 +836,7 @@ def time_end_to_end(b: Bench, name: str, layer, x_dev, dy_dev, steps: int) -> di
     run(4)  # the caching allocator settles (tensors held for the downloads change its working set)
     b.barrier()
     copy_events.clear()
+    step_ticks.clear()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
     run(steps)
@@ -845,7 +851,9 @@ def time_end_to_end(b: Bench, name: str, layer, x_dev, dy_dev, steps: int) -> di
         # slowest rank decides: report the minimum rate over the ranks
         gbs = nbytes / (statistics.median(ms) * 1e-3) / 1e9 if ms else 0.0
         rate[kind] = -b.max_over_ranks(-gbs)
+    ends = [e_start.elapsed_time(t) for t in step_ticks]
     return {"value": w["tokens"] * b.world / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+            "step_end_ms_rank0": [round(t, 2) for t in ends],
             "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out,
             "h2d_gb_per_s_per_rank_min": rate["h2d"], "d2h_gb_per_s_per_rank_min": rate["d2h"],
             "copy_overlap": "upload of step s+1 and download of step s-1 run on their own streams under step s"}
@@ -945,6 +953,8 @@ def main() -> None:
                     help="skip the secondary workloads (configs2 / configs3) and the parity check")
     ap.add_argument("--transport", choices=["peer", "nccl"], default="peer",
                     help="row exchange of the expert-parallel layer: stores into peer memory, or NCCL all-to-all")
+    ap.add_argument("--private-copies", action="store_true",
+                    help="peer transport: copy the rows the backward needs out of the exchange buffers")
     ap.add_argument("--unfused-return", dest="fused_return", action="store_false",
                     help="peer transport: return rows with a separate row kernel instead of the GEMM epilogues")
     ap.add_argument("--ep-chunks", type=int, default=None,
