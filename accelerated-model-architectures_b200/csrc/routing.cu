@@ -124,11 +124,40 @@ static int launch_histogram(const IdT* ids, int64_t n, int bins, unsigned* out, 
 //   tile_prefix[e]  : number of 128-row tiles in front of expert e; tile_prefix[E] = tiles in use
 //   tile_expert[t]  : expert that owns padded tile t
 // ------------------------------------------------------------------------------------------------
+// tile_expert[t] for every tile in use and -1 in every pad row of row_src, by `nthreads` threads of which this is
+// number `thread` (consecutive threads, consecutive addresses). Needs tile_prefix[0..E] from plan_kernel. The single
+// plan CTA does this only when nothing is sorted afterwards; otherwise the CTAs of the scan kernel share it (one
+// thread per expert walking its own tiles and pad rows, a store per 128-byte line, cost 0.3 ms at 64 Mi ids).
+__device__ __forceinline__ void fill_tile_tables(int64_t thread, int64_t nthreads, const unsigned* __restrict__ counts,
+                                                 int E, const int* __restrict__ tile_prefix,
+                                                 int* __restrict__ tile_expert, int tile_cap,
+                                                 int* __restrict__ row_src) {
+    const int total = tile_prefix[E];
+    for (int64_t t = thread; t < total; t += nthreads) {
+        int lo = 0, hi = E;  // largest e with tile_prefix[e] <= t
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (tile_prefix[mid] <= t) lo = mid;
+            else hi = mid;
+        }
+        tile_expert[t] = lo;
+    }
+    if (!row_src) return;
+    const int64_t rows_cap = static_cast<int64_t>(tile_cap) * XMA_ROW_PAD;
+    for (int64_t i = thread; i < static_cast<int64_t>(E) * XMA_ROW_PAD; i += nthreads) {  // pad rows of each expert
+        const int e = static_cast<int>(i / XMA_ROW_PAD);
+        const int t1 = min(tile_prefix[e + 1], total);
+        const int64_t r = static_cast<int64_t>(tile_prefix[e]) * XMA_ROW_PAD + counts[e] + (i % XMA_ROW_PAD);
+        if (r < static_cast<int64_t>(t1) * XMA_ROW_PAD && r < rows_cap) row_src[r] = -1;
+    }
+    // allocated rows behind the last expert's block
+    for (int64_t r = static_cast<int64_t>(total) * XMA_ROW_PAD + thread; r < rows_cap; r += nthreads) row_src[r] = -1;
+}
+
 __global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __restrict__ offsets_incl,
                             int* __restrict__ pad_offsets, int* __restrict__ tile_prefix,
                             int* __restrict__ tile_expert, int tile_cap, int* __restrict__ row_src,
-                            int* __restrict__ status) {
-    __shared__ int s_tiles_total;
+                            int fill_tables, int* __restrict__ status) {
     __shared__ int s_cnt[1024];  // E <= 1024 (checked by the callers)
     // counts are read in parallel (one dependent global load per expert in a serial loop cost ~0.3 us each)
     for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = static_cast<int>(counts[e]);
@@ -151,36 +180,11 @@ __global__ void plan_kernel(const unsigned* __restrict__ counts, int E, int* __r
             tiles = tile_cap;
         }
         tile_prefix[E] = tiles;
-        s_tiles_total = tiles;
+        __threadfence_block();
     }
     __syncthreads();
-    const int total = s_tiles_total;
-    // tile_expert[t] and the pad rows of row_src, written with consecutive threads on consecutive addresses
-    // (one thread per expert walking its own tiles and pad rows issued a store per 128-byte line: with
-    // 2048 tiles per expert the single CTA spent 0.3 ms there)
-    __shared__ int s_tile0[1025];
-    for (int e = threadIdx.x; e <= E; e += blockDim.x) s_tile0[e] = tile_prefix[e];
-    __syncthreads();
-    for (int t = threadIdx.x; t < total; t += blockDim.x) {
-        int lo = 0, hi = E;  // largest e with s_tile0[e] <= t
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (s_tile0[mid] <= t) lo = mid;
-            else hi = mid;
-        }
-        tile_expert[t] = lo;
-    }
-    if (row_src) {
-        const int rows_cap = tile_cap * XMA_ROW_PAD;
-        for (int i = threadIdx.x; i < E * XMA_ROW_PAD; i += blockDim.x) {  // pad rows at the end of each expert's block
-            const int e = i / XMA_ROW_PAD;
-            const int t1 = min(s_tile0[e + 1], total);
-            const int r = s_tile0[e] * XMA_ROW_PAD + s_cnt[e] + (i % XMA_ROW_PAD);
-            if (r < t1 * XMA_ROW_PAD && r < rows_cap) row_src[r] = -1;
-        }
-        // allocated rows behind the last expert's block
-        for (int r = total * XMA_ROW_PAD + threadIdx.x; r < rows_cap; r += blockDim.x) row_src[r] = -1;
-    }
+    if (fill_tables)
+        fill_tile_tables(threadIdx.x, blockDim.x, counts, E, tile_prefix, tile_expert, tile_cap, row_src);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -317,7 +321,8 @@ __device__ __forceinline__ unsigned scan_chunk_bin(unsigned* __restrict__ tile_c
 // The wait is bounded: after LB_MAX_POLLS empty rounds the chunk sets status bit 2 and goes on with prefix 0.
 __global__ void __launch_bounds__(SCAN_THREADS)
 tile_scan_kernel(SortScratch sc, int64_t tiles, int E, const int* __restrict__ offsets_incl,
-                 int* __restrict__ status) {
+                 const unsigned* __restrict__ counts, const int* __restrict__ tile_prefix,
+                 int* __restrict__ tile_expert, int tile_cap, int* __restrict__ row_src, int* __restrict__ status) {
     __shared__ unsigned s_chunk;
     if (threadIdx.x == 0) s_chunk = atomicAdd(sc.ticket, 1u);
     __syncthreads();
@@ -374,6 +379,10 @@ tile_scan_kernel(SortScratch sc, int64_t tiles, int E, const int* __restrict__ o
         const unsigned gbase = (b == 0) ? 0u : static_cast<unsigned>(offsets_incl[b - 1]);
         sc.chunk_base[static_cast<size_t>(chunk) * E + b] = gbase + excl;
     }
+    // the tile -> expert table and the pad rows of row_src, shared by all CTAs of this launch
+    fill_tile_tables(static_cast<int64_t>(blockIdx.x) * SCAN_THREADS + threadIdx.x,
+                     static_cast<int64_t>(gridDim.x) * SCAN_THREADS, counts, E, tile_prefix, tile_expert, tile_cap,
+                     row_src);
 }
 
 // Pass 2, one tile of SORT_TILE ids per CTA: the tile is sorted by bin inside the CTA, stably, by a
@@ -803,13 +812,14 @@ int count_sort_impl(const IdT* ids, int64_t n, int E, uint32_t* counts, int* off
         XMA_CUDA_TRY(cudaGetLastError());
     }
     xma::plan_kernel<<<1, 1024, 0, stream>>>(counts, E, offsets_incl, pad_offsets, tile_prefix, tile_expert,
-                                            static_cast<int>(tile_cap), row_src, device_status);
+                                            static_cast<int>(tile_cap), row_src, n == 0 ? 1 : 0, device_status);
     XMA_CUDA_TRY(cudaGetLastError());
     (void)row_cap;
     if (n == 0) return XMA_OK;
     const int64_t chunks = xma::ceil_div(tiles, static_cast<int64_t>(xma::SCAN_TILES));
-    xma::tile_scan_kernel<<<static_cast<int>(chunks), xma::SCAN_THREADS, 0, stream>>>(sc, tiles, E, offsets_incl,
-                                                                                      device_status);
+    xma::tile_scan_kernel<<<static_cast<int>(chunks), xma::SCAN_THREADS, 0, stream>>>(
+        sc, tiles, E, offsets_incl, counts, tile_prefix, tile_expert, static_cast<int>(tile_cap), row_src,
+        device_status);
     XMA_CUDA_TRY(cudaGetLastError());
     const size_t smem = xma::sort_smem_bytes(E);
     int bits = 1;
