@@ -109,9 +109,9 @@ template <typename T, bool HAS_COEFF>
 __global__ void __launch_bounds__(EP_ROW_THREADS)
 ep_dispatch_kernel(const T* __restrict__ src, int64_t src_stride, const int* __restrict__ sorted_expert,
                    const int* __restrict__ sorted_scattered, const T* __restrict__ coeff, int fan_out,
-                   const int* __restrict__ send_delta, int num_experts, int e_local, int rank, int64_t rows,
-                   int64_t width, void* const* __restrict__ peer_rows, int* const* __restrict__ peer_meta,
-                   int64_t peer_rows_cap, int* __restrict__ status) {
+                   const int* __restrict__ send_delta, int num_experts, int e_local, int local_lo, int local_hi,
+                   int rank, int64_t rows, int64_t width, void* const* __restrict__ peer_rows,
+                   int* const* __restrict__ peer_meta, int64_t peer_rows_cap, int* __restrict__ status) {
     constexpr int V = Vec16<T>::N;
     const int64_t nvec = width / V;
     for (int64_t p0 = static_cast<int64_t>(blockIdx.x) * EP_ROWS; p0 < rows;
@@ -133,6 +133,8 @@ ep_dispatch_kernel(const T* __restrict__ src, int64_t src_stride, const int* __r
                     continue;  // never store outside the owner's buffer
                 }
                 const int owner = e / e_local;
+                const int local = e - owner * e_local;
+                if (local < local_lo || local >= local_hi) continue;  // another part of the pipelined exchange
                 q[j] = qq;
                 dst[j] = static_cast<T*>(peer_rows[owner]) + row * width;
                 if (HAS_COEFF) cf[j] = to_f32(coeff[qq]);
@@ -243,18 +245,19 @@ static int ep_grid(int64_t rows) {
 template <typename T>
 static int ep_dispatch_t(const void* src, int64_t src_stride, const int* sorted_expert, const int* sorted_scattered,
                          const void* coeff, int fan_out, const int* send_delta, int num_experts, int e_local,
-                         int rank, int64_t rows, int64_t width, void* const* peer_rows, int* const* peer_meta,
-                         int64_t peer_rows_cap, int* status, cudaStream_t stream) {
+                         int local_lo, int local_hi, int rank, int64_t rows, int64_t width, void* const* peer_rows,
+                         int* const* peer_meta, int64_t peer_rows_cap, int* status, cudaStream_t stream) {
     if (width % Vec16<T>::N || src_stride % Vec16<T>::N || !is_aligned16(src)) return XMA_ERR_MISALIGNED;
     const int grid = ep_grid(rows);
     if (coeff)
         ep_dispatch_kernel<T, true><<<grid, EP_ROW_THREADS, 0, stream>>>(
             static_cast<const T*>(src), src_stride, sorted_expert, sorted_scattered, static_cast<const T*>(coeff),
-            fan_out, send_delta, num_experts, e_local, rank, rows, width, peer_rows, peer_meta, peer_rows_cap, status);
+            fan_out, send_delta, num_experts, e_local, local_lo, local_hi, rank, rows, width, peer_rows, peer_meta,
+            peer_rows_cap, status);
     else
         ep_dispatch_kernel<T, false><<<grid, EP_ROW_THREADS, 0, stream>>>(
             static_cast<const T*>(src), src_stride, sorted_expert, sorted_scattered, nullptr, fan_out, send_delta,
-            num_experts, e_local, rank, rows, width, peer_rows, peer_meta, peer_rows_cap, status);
+            num_experts, e_local, local_lo, local_hi, rank, rows, width, peer_rows, peer_meta, peer_rows_cap, status);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -304,11 +307,12 @@ int xma_b200_ep_plan(const int32_t* count_matrix, int world, int num_experts, in
     return static_cast<int>(cudaGetLastError());
 }
 
-int xma_b200_ep_dispatch(const void* src, int dtype, int64_t src_row_stride, const int32_t* sorted_expert_idxs,
-                         const int32_t* sorted_scattered_idxs, const void* coeff, int fan_out,
-                         const int32_t* send_delta, int num_experts, int world, int rank, int64_t rows, int64_t width,
-                         void* const* peer_rows, int32_t* const* peer_meta, int64_t peer_rows_cap,
-                         int* device_status, cudaStream_t stream) {
+int xma_b200_ep_dispatch_part(const void* src, int dtype, int64_t src_row_stride, const int32_t* sorted_expert_idxs,
+                              const int32_t* sorted_scattered_idxs, const void* coeff, int fan_out,
+                              const int32_t* send_delta, int num_experts, int world, int rank, int local_lo,
+                              int local_hi, int64_t rows, int64_t width, void* const* peer_rows,
+                              int32_t* const* peer_meta, int64_t peer_rows_cap, int* device_status,
+                              cudaStream_t stream) {
     if (rows == 0) return XMA_OK;
     if (!src || !sorted_expert_idxs || !sorted_scattered_idxs || !send_delta || !peer_rows)
         return XMA_ERR_NULL_POINTER;
@@ -317,10 +321,12 @@ int xma_b200_ep_dispatch(const void* src, int dtype, int64_t src_row_stride, con
         return XMA_ERR_BAD_SHAPE;
     if (rows > xma::PEER_ROW_MASK + 1LL) return XMA_ERR_TOO_LARGE;
     const int e_local = num_experts / world;
+    if (local_lo < 0 || local_hi > e_local || local_lo > local_hi) return XMA_ERR_BAD_SHAPE;
+    if (local_lo == local_hi) return XMA_OK;
 #define XMA_EP_DISPATCH(T)                                                                                         \
     return xma::ep_dispatch_t<T>(src, src_row_stride, sorted_expert_idxs, sorted_scattered_idxs, coeff, fan_out,   \
-                                 send_delta, num_experts, e_local, rank, rows, width, peer_rows, peer_meta,        \
-                                 peer_rows_cap, device_status, stream)
+                                 send_delta, num_experts, e_local, local_lo, local_hi, rank, rows, width,          \
+                                 peer_rows, peer_meta, peer_rows_cap, device_status, stream)
     switch (dtype) {
         case XMA_F32: XMA_EP_DISPATCH(float);
         case XMA_F16: XMA_EP_DISPATCH(__half);
@@ -328,6 +334,17 @@ int xma_b200_ep_dispatch(const void* src, int dtype, int64_t src_row_stride, con
     }
 #undef XMA_EP_DISPATCH
     return XMA_ERR_BAD_DTYPE;
+}
+
+int xma_b200_ep_dispatch(const void* src, int dtype, int64_t src_row_stride, const int32_t* sorted_expert_idxs,
+                         const int32_t* sorted_scattered_idxs, const void* coeff, int fan_out,
+                         const int32_t* send_delta, int num_experts, int world, int rank, int64_t rows, int64_t width,
+                         void* const* peer_rows, int32_t* const* peer_meta, int64_t peer_rows_cap,
+                         int* device_status, cudaStream_t stream) {
+    const int e_local = (world > 0 && num_experts > 0) ? num_experts / world : 0;
+    return xma_b200_ep_dispatch_part(src, dtype, src_row_stride, sorted_expert_idxs, sorted_scattered_idxs, coeff,
+                                     fan_out, send_delta, num_experts, world, rank, 0, e_local, rows, width, peer_rows,
+                                     peer_meta, peer_rows_cap, device_status, stream);
 }
 
 int xma_b200_ep_copy_rows(const void* rows, int dtype, const int32_t* meta, int64_t n_rows, int64_t width, void* out,

@@ -108,17 +108,20 @@ struct RowsWork {
     int m_tile, n_tile, e;
 };
 
+// `tile_prefix` may be a slice of a longer table (experts [a, b) of a layer: the expert-parallel layer runs its
+// experts group by group), so its first entry is not necessarily 0: work items count from tile_prefix[0].
 __device__ __forceinline__ RowsWork decode_rows(const int* tile_prefix, int E, int n_tiles, int64_t w) {
-    // largest e with tile_prefix[e] * n_tiles <= w
-    int lo = 0, hi = E;  // invariant: prefix[lo]*n_tiles <= w < prefix[hi]*n_tiles
+    const int base = tile_prefix[0];
+    // largest e with (tile_prefix[e] - base) * n_tiles <= w
+    int lo = 0, hi = E;  // invariant: (prefix[lo] - base) * n_tiles <= w < (prefix[hi] - base) * n_tiles
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (static_cast<int64_t>(tile_prefix[mid]) * n_tiles <= w) lo = mid;
+        if (static_cast<int64_t>(tile_prefix[mid] - base) * n_tiles <= w) lo = mid;
         else hi = mid;
     }
     RowsWork r;
     r.e = lo;
-    const int64_t local = w - static_cast<int64_t>(tile_prefix[lo]) * n_tiles;
+    const int64_t local = w - static_cast<int64_t>(tile_prefix[lo] - base) * n_tiles;
     const int mt = tile_prefix[lo + 1] - tile_prefix[lo];
     int m;
     raster_tile(local, mt, n_tiles, ROWS_RASTER_GROUP, m, r.n_tile);
@@ -144,7 +147,7 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int half_n = n / 2;  // SwiGLU: width of the activation
     const int n_tiles = (EPI == EPI_SWIGLU) ? (half_n + 127) / 128 : (n + BN - 1) / BN;
     const int k_blocks = (kd + BK - 1) / BK;
-    const int64_t total = static_cast<int64_t>(s.tile_prefix[E]) * n_tiles;
+    const int64_t total = static_cast<int64_t>(s.tile_prefix[E] - s.tile_prefix[0]) * n_tiles;
 
     if (warp == 0) {
         if (lane == 0) {

@@ -85,6 +85,9 @@ _SIGNATURES = {
                          c_void_p, c_int64, c_void_p, c_void_p],
     "xma_b200_ep_dispatch": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                              c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
+    "xma_b200_ep_dispatch_part": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                  c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
+                                  c_void_p],
     "xma_b200_ep_copy_rows": [c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p, c_void_p],
     "xma_b200_ep_publish": [c_void_p, c_int64, c_void_p, c_void_p],
     "xma_b200_ep_return": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p,

@@ -34,8 +34,12 @@ ranks of one node map each other's exchange buffers once, CUDA IPC over NVLink):
 Backward mirrors it (dY rows dispatched with the routing weight applied, dX rows returned the same
 way). No kernel waits on another GPU: the phases are separated by a stream-ordered
 barrier (a one-element NCCL all-reduce), so a rank that stops costs a collective timeout, never a
-spinning kernel. Tensors kept for backward are private copies; the exchange buffers are reused by
-every call.
+spinning kernel. What the backward needs of the exchanged rows stays in the exchange buffers (a second
+pair of buffers serves the backward's exchange; `private_copies=True` copies instead), so a forward must
+be followed by its backward before the next forward of the same layer.
+
+Eager only: the exchange kernels write through raw addresses of other ranks' buffers (int64 tables), which
+a tracing compiler cannot see as outputs of the ops; do not wrap this layer in `torch.compile`.
 """
 
 from __future__ import annotations
@@ -284,6 +288,13 @@ class _Exchange:
         self.recv_rows_bwd = self.home_rows_bwd = None
         self.recv_table_bwd = self.home_table_bwd = None
         self._in_use = None  # weak reference to the forward whose tensors live in the buffers
+        self._side = None
+
+    def side_stream(self, device: torch.device) -> torch.cuda.Stream:
+        """The stream the dispatches of the pipelined exchange are queued on."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=device)
+        return self._side
 
     def claim(self, owner) -> None:
         """The forward `owner` is about to fill the forward buffers. An earlier forward whose backward has not
@@ -338,9 +349,11 @@ class _Exchange:
 
 
 class _PeerRoute:
-    """Device tables of one routing decision under the peer transport (all from `ep_plan`)."""
+    """Device tables of one routing decision under the peer transport (all from `ep_plan`), and the host's view
+    of how this rank's experts are cut into the parts of the pipelined exchange."""
 
-    def __init__(self, count_matrix: torch.Tensor, rank: int, rows: int, exchange: _Exchange) -> None:
+    def __init__(self, count_matrix: torch.Tensor, rank: int, rows: int, exchange: _Exchange,
+                 local_padded=None, parts: int = 1) -> None:
         world, num_experts = count_matrix.shape
         e_local = num_experts // world
         dev = count_matrix.device
@@ -350,6 +363,15 @@ class _PeerRoute:
          self.tile_expert) = torch.empty(sum(sizes), dtype=torch.int32, device=dev).split(sizes)
         ops.ep_plan_(count_matrix, rank, self.send_delta, self.counts, self.pad_offsets, self.tile_prefix,
                      self.tile_expert, exchange.recv_meta)
+        # parts: (first local expert, one past the last, first padded row, one past the last) - contiguous groups
+        # of this rank's experts; `local_padded` = padded rows of each local expert, known to the host
+        parts = max(1, min(int(parts), e_local))
+        if local_padded is None or parts == 1:
+            self.parts = [(0, e_local, 0, rows)]
+        else:
+            ends = np.concatenate([[0], np.cumsum(np.asarray(local_padded, dtype=np.int64))])
+            cuts = [round(i * e_local / parts) for i in range(parts + 1)]
+            self.parts = [(cuts[i], cuts[i + 1], int(ends[cuts[i]]), int(ends[cuts[i + 1]])) for i in range(parts)]
 
 
 class _KeptRows:
@@ -365,7 +387,34 @@ class _KeptRows:
 
 class _PeerSwiGLUExperts(torch.autograd.Function):
     """The fused SwiGLU expert block with the experts sharded over the ranks: dispatch and combine are
-    stores into the other ranks' exchange buffers (see the module docstring)."""
+    stores into the other ranks' exchange buffers (see the module docstring).
+
+    The exchange is pipelined by expert: this rank's experts are cut into `route.parts` contiguous groups, every
+    rank dispatches the rows of group 0, then of group 1, ... on a side stream (each followed by a barrier over
+    the ranks), and the main stream runs the grouped GEMMs of a group as soon as its rows have landed - the
+    dispatch of group i + 1 travels under the GEMMs of group i. The GEMMs are whole experts either way, so
+    nothing is computed twice (cutting the tokens instead would add every weight gradient up once per cut)."""
+
+    @staticmethod
+    def _dispatch_parts(src, coeff, K, sorted_expert_idxs, sorted_scattered_idxs, route, exchange, recv_table,
+                        meta_table):
+        """Queues every part's dispatch + barrier on the exchange's side stream; -> one event per part."""
+        main = torch.cuda.current_stream(src.device)
+        side = exchange.side_stream(src.device)
+        side.wait_stream(main)
+        events = []
+        with torch.cuda.stream(side):
+            for lo, hi, _, _ in route.parts:
+                ops.ep_dispatch_(src, sorted_expert_idxs, sorted_scattered_idxs, coeff, K, route.send_delta,
+                                 route.world, route.rank, recv_table, meta_table, exchange.recv_cap, lo, hi)
+                exchange.link.barrier()
+                ev = torch.cuda.Event()
+                ev.record(side)
+                events.append(ev)
+        for t in (src, coeff):
+            if t is not None:
+                t.record_stream(side)
+        return events
 
     @staticmethod
     def forward(ctx, x, router_weights, w1, w2, sorted_expert_idxs, sorted_scattered_idxs, route, exchange):
@@ -378,32 +427,36 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
         impl = ops.GEMM_IMPL
         rows = route.rows                              # padded rows of this rank's experts in use
         alloc = route.tile_expert.numel() * ROW_PAD    # grouped buffers span the whole tile table
+        main = torch.cuda.current_stream(x.device)
 
         kept = _KeptRows() if any(ctx.needs_input_grad) else None
         exchange.claim(kept)
-        ops.ep_dispatch_(x, sorted_expert_idxs, sorted_scattered_idxs, None, K, route.send_delta, route.world,
-                         route.rank, exchange.recv_table, exchange.meta_table, exchange.recv_cap)
-        link.barrier()
+        arrived = _PeerSwiGLUExperts._dispatch_parts(x, None, K, sorted_expert_idxs, sorted_scattered_idxs, route,
+                                                     exchange, exchange.recv_table, exchange.meta_table)
 
-        meta = exchange.recv_meta[:alloc].clone()
-        if exchange.private_copies:
-            xs = torch.empty(alloc, H, **opts)
-            ops.ep_copy_rows_(exchange.recv_rows, meta, xs[:rows])
-        else:
-            xs = exchange.recv_rows[:alloc]
-            ops.ep_copy_rows_(xs, meta, xs[:rows])  # in place: zero the pad rows (nobody else writes them)
+        meta = torch.full((alloc,), -1, dtype=torch.int32, device=x.device)
+        xs = torch.empty(alloc, H, **opts) if exchange.private_copies else exchange.recv_rows[:alloc]
         gu = torch.empty(alloc, two_i, **opts)
         act = torch.empty(alloc, I, **opts)
-        ops.grouped_gemm_rows_(xs, w1, W_NK, act, gu, None, route.tile_expert, route.tile_prefix, H, two_i,
-                               EPI_SWIGLU, impl, tag="gemm_up_swiglu")
-        if exchange.fused_return:
-            ops.grouped_gemm_rows_(act, w2, W_NK, exchange.home_rows, None, meta, route.tile_expert,
-                                   route.tile_prefix, I, H, EPI_PLAIN, impl, exchange.home_table, exchange.home_cap,
-                                   tag="gemm_down")
-        else:
-            out = torch.empty(alloc, H, **opts)
-            ops.grouped_gemm_rows_(act, w2, W_NK, out, None, None, route.tile_expert, route.tile_prefix, I, H,
-                                   EPI_PLAIN, impl, tag="gemm_down")
+        out = None if exchange.fused_return else torch.empty(alloc, H, **opts)
+        for (lo, hi, r0, r1), ev in zip(route.parts, arrived):
+            main.wait_event(ev)
+            meta[r0:r1].copy_(exchange.recv_meta[r0:r1])
+            if exchange.private_copies:
+                ops.ep_copy_rows_(exchange.recv_rows[r0:r1], meta[r0:r1], xs[r0:r1])
+            else:
+                ops.ep_copy_rows_(xs[r0:r1], meta[r0:r1], xs[r0:r1])  # in place: zero the pad rows
+            tiles = route.tile_prefix[lo:hi + 1]
+            ops.grouped_gemm_rows_(xs, w1[lo:hi], W_NK, act, gu, None, route.tile_expert, tiles, H, two_i,
+                                   EPI_SWIGLU, impl, tag="gemm_up_swiglu")
+            if exchange.fused_return:
+                ops.grouped_gemm_rows_(act, w2[lo:hi], W_NK, exchange.home_rows, None, meta, route.tile_expert,
+                                       tiles, I, H, EPI_PLAIN, impl, exchange.home_table, exchange.home_cap,
+                                       tag="gemm_down")
+            else:
+                ops.grouped_gemm_rows_(act, w2[lo:hi], W_NK, out, None, None, route.tile_expert, tiles, I, H,
+                                       EPI_PLAIN, impl, tag="gemm_down")
+        if not exchange.fused_return:
             ops.ep_return_(out[:rows], meta, route.world, exchange.home_table, exchange.home_cap)
         link.barrier()
 
@@ -433,36 +486,39 @@ class _PeerSwiGLUExperts(torch.autograd.Function):
         opts = dict(dtype=xs.dtype, device=xs.device)
         impl = ops.GEMM_IMPL
         grad_out = grad_out.contiguous()
+        main = torch.cuda.current_stream(xs.device)
 
+        # dY rows, scaled by their routing weight, to the owners (same slots as the forward rows), part by part
+        arrived = _PeerSwiGLUExperts._dispatch_parts(grad_out, router_weights.view(-1), K, sorted_expert_idxs,
+                                                     sorted_scattered_idxs, route, exchange,
+                                                     exchange.recv_table_bwd, None)
         d_rw = None
         if ctx.needs_input_grad[1]:
             d_rw = torch.empty_like(router_weights)
             if T > 0:
                 ops.combine_bwd_(ys, grad_out, K, d_rw)
 
-        # dY rows, scaled by their routing weight, to the owners (same slots as the forward rows)
-        ops.ep_dispatch_(grad_out, sorted_expert_idxs, sorted_scattered_idxs, router_weights.view(-1), K,
-                         route.send_delta, route.world, route.rank, exchange.recv_table_bwd, None, exchange.recv_cap)
         dys = exchange.recv_rows_bwd[:alloc]
-        ops.ep_copy_rows_(dys, meta, dys[:rows])  # in place: zero the pad rows (nobody else writes them)
-        link.barrier()
-
-        d_w2 = torch.empty_like(w2)
-        ops.grouped_gemm_dw_(dys, act, route.counts, route.pad_offsets, d_w2, impl, tag="gemm_dw2")
+        d_w1, d_w2 = torch.empty_like(w1), torch.empty_like(w2)
         dgu = torch.empty(alloc, two_i, **opts)
-        ops.grouped_gemm_rows_(dys, w2, W_KN, dgu, gu, None, route.tile_expert, route.tile_prefix, H, I,
-                               EPI_DSWIGLU, impl, tag="gemm_dact_dswiglu")
-        d_w1 = torch.empty_like(w1)
-        ops.grouped_gemm_dw_(dgu, xs, route.counts, route.pad_offsets, d_w1, impl, tag="gemm_dw1")
-        # dX rows straight back to the token's home rank
-        if exchange.fused_return:
-            ops.grouped_gemm_rows_(dgu, w1, W_KN, exchange.home_rows_bwd, None, meta, route.tile_expert,
-                                   route.tile_prefix, two_i, H, EPI_PLAIN, impl, exchange.home_table_bwd,
-                                   exchange.home_cap, tag="gemm_dx")
-        else:
-            dxs = torch.empty(alloc, H, **opts)
-            ops.grouped_gemm_rows_(dgu, w1, W_KN, dxs, None, None, route.tile_expert, route.tile_prefix, two_i, H,
-                                   EPI_PLAIN, impl, tag="gemm_dx")
+        dxs = None if exchange.fused_return else torch.empty(alloc, H, **opts)
+        for (lo, hi, r0, r1), ev in zip(route.parts, arrived):
+            main.wait_event(ev)
+            ops.ep_copy_rows_(dys[r0:r1], meta[r0:r1], dys[r0:r1])  # in place: zero the pad rows
+            tiles, counts, pads = route.tile_prefix[lo:hi + 1], route.counts[lo:hi], route.pad_offsets[lo:hi + 1]
+            ops.grouped_gemm_dw_(dys, act, counts, pads, d_w2[lo:hi], impl, tag="gemm_dw2")
+            ops.grouped_gemm_rows_(dys, w2[lo:hi], W_KN, dgu, gu, None, route.tile_expert, tiles, H, I, EPI_DSWIGLU,
+                                   impl, tag="gemm_dact_dswiglu")
+            ops.grouped_gemm_dw_(dgu, xs, counts, pads, d_w1[lo:hi], impl, tag="gemm_dw1")
+            # dX rows straight back to the token's home rank
+            if exchange.fused_return:
+                ops.grouped_gemm_rows_(dgu, w1[lo:hi], W_KN, exchange.home_rows_bwd, None, meta, route.tile_expert,
+                                       tiles, two_i, H, EPI_PLAIN, impl, exchange.home_table_bwd, exchange.home_cap,
+                                       tag="gemm_dx")
+            else:
+                ops.grouped_gemm_rows_(dgu, w1[lo:hi], W_KN, dxs, None, None, route.tile_expert, tiles, two_i, H,
+                                       EPI_PLAIN, impl, tag="gemm_dx")
+        if not exchange.fused_return:
             ops.ep_return_(dxs[:rows], meta, route.world, exchange.home_table_bwd, exchange.home_cap)
         # every read of the forward's rows (xs for dW1, ys for d_router_weights) is queued in front of this
         # barrier, so the buffers are free for the next forward once it has passed
@@ -481,7 +537,7 @@ class ExpertParallelMoE(nn.Module):
 
     def __init__(self, local_moe: MoE, gate_weight: torch.Tensor, world_group=None,
                  overlap_chunks: int | None = None, transport: str = "nccl", link=None,
-                 fused_return: bool = True, private_copies: bool = False) -> None:
+                 fused_return: bool = True, private_copies: bool = False, pipeline_parts: int | None = None) -> None:
         """`transport`: "nccl" (all-to-all collectives; any process group) or "peer" (stores into the
         other ranks' memory; the ranks must be GPUs of one node with peer access). `link` replaces the
         `PeerLink` built from the process group (the tests run several ranks on one GPU with it).
@@ -490,7 +546,9 @@ class ExpertParallelMoE(nn.Module):
         shared memory so that each row leaves in 128-byte pieces); False runs a separate row kernel.
         `private_copies` (peer transport): False keeps what the backward needs of the exchanged rows in the
         exchange buffers themselves (the backward exchanges through a second pair of buffers), which saves two
-        passes over `[rows, hidden]` per step but allows one forward per backward at a time; True copies them."""
+        passes over `[rows, hidden]` per step but allows one forward per backward at a time; True copies them.
+        `pipeline_parts` (peer transport): this rank's experts are cut into that many groups and the rows of one
+        group are dispatched while the GEMMs of the previous one run (default 1: the exchange in one piece)."""
         super().__init__()
         if not (getattr(local_moe.act, "xma_fused_activation", None) == "swiglu" and local_moe.is_glu):
             raise ValueError("ExpertParallelMoE runs the fused SwiGLU expert block")
@@ -500,6 +558,7 @@ class ExpertParallelMoE(nn.Module):
         self.transport = transport
         self.fused_return = fused_return
         self.private_copies = private_copies
+        self.pipeline_parts = pipeline_parts
         if link is not None:
             self.link, self.group = link, None
             self.world, self.rank = link.world, link.rank
@@ -575,7 +634,12 @@ class ExpertParallelMoE(nn.Module):
             exchange = self._exchange(slot, x)
             # (grouped buffers are allocated for rows // 128 + e_local tiles, the received rows included)
             exchange.ensure(int(padded.max()) + e_local * ROW_PAD, int(host.sum(1).max()))
-            route = _PeerRoute(count_matrix, self.rank, int(padded[self.rank]), exchange)
+            local_padded = ((host.sum(0) + ROW_PAD - 1) // ROW_PAD * ROW_PAD)[self.rank * e_local:
+                                                                                (self.rank + 1) * e_local]
+            parts = self.pipeline_parts if self.pipeline_parts is not None else 1
+            if not self.local._tensor_cores(x):
+                parts = 1  # the CUDA-core GEMMs take whole tile tables only
+            route = _PeerRoute(count_matrix, self.rank, int(padded[self.rank]), exchange, local_padded, parts)
         y = _PeerSwiGLUExperts.apply(x, router_weights, self.local.c_fc.weight, self.local.c_proj.weight,
                                      plan.sorted_expert_idxs, plan.sorted_scattered_idxs, route, exchange)
         return y, router_logits

@@ -227,15 +227,18 @@ def _ep_plan_op(count_matrix: Tensor, rank: int, send_delta: Tensor, counts: Ten
 @torch.library.custom_op(f"{_NS}::ep_dispatch", mutates_args=(), device_types="cuda")
 def _ep_dispatch_op(src: Tensor, sorted_expert_idxs: Tensor, sorted_scattered_idxs: Tensor, coeff: Optional[Tensor],
                     fan_out: int, send_delta: Tensor, world: int, rank: int, peer_rows: Tensor,
-                    peer_meta: Optional[Tensor], peer_rows_cap: int) -> None:
-    """Writes into the exchange buffers whose addresses `peer_rows` / `peer_meta` (int64 [world]) hold."""
+                    peer_meta: Optional[Tensor], peer_rows_cap: int, local_lo: int = 0, local_hi: int = -1) -> None:
+    """Writes into the exchange buffers whose addresses `peer_rows` / `peer_meta` (int64 [world]) hold; only the rows
+    for the owners' local experts [local_lo, local_hi) (all of them by default)."""
     require_cuda(src, sorted_expert_idxs, sorted_scattered_idxs, send_delta, peer_rows)
+    if local_hi < 0:
+        local_hi = send_delta.numel() // world
     check(
-        lib.xma_b200_ep_dispatch(
+        lib.xma_b200_ep_dispatch_part(
             ptr(src), dtype_code(src.dtype), _row_stride(src), ptr(sorted_expert_idxs), ptr(sorted_scattered_idxs),
-            ptr(coeff), fan_out, ptr(send_delta), send_delta.numel(), world, rank, sorted_expert_idxs.numel(),
-            src.size(1), ptr(peer_rows), ptr(peer_meta), peer_rows_cap, ptr(status_word(src.device)),
-            current_stream(src.device)
+            ptr(coeff), fan_out, ptr(send_delta), send_delta.numel(), world, rank, local_lo, local_hi,
+            sorted_expert_idxs.numel(), src.size(1), ptr(peer_rows), ptr(peer_meta), peer_rows_cap,
+            ptr(status_word(src.device)), current_stream(src.device)
         ),
         "xma_b200_ep_dispatch",
     )

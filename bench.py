@@ -692,7 +692,7 @@ def build_workload(b: Bench, name: str):
                 b.transport = "nccl"
         layer = ExpertParallelMoE(moe, gate, world_group=b.dist.group.WORLD, overlap_chunks=args.ep_chunks,
                                   transport=b.transport, fused_return=args.fused_return,
-                                  private_copies=args.private_copies)
+                                  private_copies=args.private_copies, pipeline_parts=args.ep_parts)
     else:
         with torch.no_grad():
             moe.gate.weight.copy_(gate)
@@ -953,6 +953,8 @@ def main() -> None:
                     help="skip the secondary workloads (configs2 / configs3) and the parity check")
     ap.add_argument("--transport", choices=["peer", "nccl"], default="peer",
                     help="row exchange of the expert-parallel layer: stores into peer memory, or NCCL all-to-all")
+    ap.add_argument("--ep-parts", type=int, default=None,
+                    help="peer transport: expert groups of the pipelined exchange (default: the layer's choice)")
     ap.add_argument("--private-copies", action="store_true",
                     help="peer transport: copy the rows the backward needs out of the exchange buffers")
     ap.add_argument("--unfused-return", dest="fused_return", action="store_false",

@@ -284,6 +284,16 @@ int xma_b200_ep_dispatch(const void* src, int dtype, int64_t src_row_stride, con
                          void* const* peer_rows, int32_t* const* peer_meta, int64_t peer_rows_cap,
                          int* device_status, cudaStream_t stream);
 
+/* The same for the rows of this rank whose expert is one of the owners' local experts [local_lo, local_hi) only
+ * (local index = e mod (E / world)): the exchange cut into parts by expert, so that the owners can start on the
+ * experts of one part while the rows of the next are still on their way. */
+int xma_b200_ep_dispatch_part(const void* src, int dtype, int64_t src_row_stride, const int32_t* sorted_expert_idxs,
+                              const int32_t* sorted_scattered_idxs, const void* coeff, int fan_out,
+                              const int32_t* send_delta, int num_experts, int world, int rank, int local_lo,
+                              int local_hi, int64_t rows, int64_t width, void* const* peer_rows,
+                              int32_t* const* peer_meta, int64_t peer_rows_cap, int* device_status,
+                              cudaStream_t stream);
+
 /* out[r, :] = meta[r] >= 0 ? rows[r, :] : 0 for r < n_rows (dense rows of `width` elements);
  * out == rows zero-fills the pad rows in place. */
 int xma_b200_ep_copy_rows(const void* rows, int dtype, const int32_t* meta, int64_t n_rows, int64_t width, void* out,

@@ -78,7 +78,8 @@ def run_rank(rank: int, world: int, port: int, results, cfg: dict) -> None:
         link = HostSyncLink(dist.group.WORLD) if (shared_gpu and transport == "peer") else None
         layer = ExpertParallelMoE(moe, g0["gate"].to(dev), overlap_chunks=cfg["chunks"], transport=transport,
                                   link=link, fused_return=cfg.get("fused_return", True),
-                                  private_copies=cfg.get("private_copies", False))
+                                  private_copies=cfg.get("private_copies", False),
+                                  pipeline_parts=cfg.get("parts"))
 
         errs = {}
         for step in range(cfg["steps"]):

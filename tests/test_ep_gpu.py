@@ -43,11 +43,13 @@ def _run(world: int, cfg: dict):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("transport,chunks,fused", [("nccl", 1, False), ("nccl", 2, False), ("peer", 1, False),
-                                                    ("peer", 2, False), ("peer", 1, True)])
-def test_expert_parallel_matches_single_device_oracle(transport, chunks, fused):
+@pytest.mark.parametrize("transport,chunks,fused,parts", [("nccl", 1, False, None), ("nccl", 2, False, None),
+                                                          ("peer", 1, False, 1), ("peer", 2, False, 1),
+                                                          ("peer", 1, True, 1), ("peer", 1, True, 2),
+                                                          ("peer", 1, False, 4)])
+def test_expert_parallel_matches_single_device_oracle(transport, chunks, fused, parts):
     _run(2, dict(shared_gpu=False, transport=transport, chunks=chunks, dtype="bfloat16", tokens=150, steps=2,
-                 fused_return=fused))
+                 fused_return=fused, parts=parts))
 
 
 @pytest.mark.parametrize("world,dtype,chunks,fused", [(2, "bfloat16", 1, False), (4, "bfloat16", 1, True),
@@ -56,6 +58,14 @@ def test_expert_parallel_matches_single_device_oracle(transport, chunks, fused):
 def test_peer_transport_with_ranks_sharing_one_gpu(world, dtype, chunks, fused):
     _run(world, dict(shared_gpu=True, transport="peer", chunks=chunks, dtype=dtype, tokens=300, steps=2,
                      fused_return=fused))
+
+
+@pytest.mark.parametrize("world,parts,fused", [(2, 2, True), (2, 4, False), (4, 2, True), (4, 3, True)])
+def test_peer_transport_pipelined_by_expert_groups(world, parts, fused):
+    """`pipeline_parts`: the rows of one group of experts are dispatched while the GEMMs of the previous group
+    run (side stream, one barrier per group); same results as the exchange in one piece."""
+    _run(world, dict(shared_gpu=True, transport="peer", chunks=1, dtype="bfloat16", tokens=300, steps=2,
+                     fused_return=fused, parts=parts))
 
 
 def test_peer_transport_with_private_copies():
