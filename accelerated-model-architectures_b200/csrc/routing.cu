@@ -490,20 +490,31 @@ sort_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int E, int passes, c
     unsigned n_valid = 0;
     for (int pass = 0; pass < passes; ++pass) {
         const int shift = pass * RADIX_BITS;
-        // zero the counters (16 bytes per thread)
-        reinterpret_cast<uint4*>(s_cnt)[tid] = make_uint4(0u, 0u, 0u, 0u);
-        __syncthreads();
-        // count: old value = how many elements of this digit the thread has met before
-        unsigned long long met = 0ull;  // 16 x 4 bits
+        // count in registers: sixteen 8-bit counters in two 64-bit words (a thread holds at most 16 elements);
+        // the value before the increment = how many elements of this digit the thread has met before. (Counting
+        // straight in the shared byte counters made every element wait for the read-modify-write of the one
+        // before it: the pass was bound by shared-memory latency.)
+        unsigned long long c_lo = 0ull, c_hi = 0ull;  // digits 0-7, 8-15
+        unsigned long long met = 0ull;                // 16 x 4 bits
 #pragma unroll
         for (int k = 0; k < SORT_ITEMS; ++k) {
             if (item[k] != SORT_INVALID) {
                 const unsigned d = (item[k] >> shift) & (RADIX - 1);
-                unsigned char* c = s_cnt + d * SORT_THREADS + tid;
-                const unsigned old = *c;
-                *c = static_cast<unsigned char>(old + 1u);
+                const unsigned sh = (d & 7u) << 3;
+                const bool high = (d & 8u) != 0u;
+                const unsigned long long word = high ? c_hi : c_lo;
+                const unsigned old = static_cast<unsigned>(word >> sh) & 0xffu;
+                const unsigned long long inc = 1ull << sh;
+                c_hi += high ? inc : 0ull;
+                c_lo += high ? 0ull : inc;
                 met |= static_cast<unsigned long long>(old) << (4 * k);
             }
+        }
+        // every thread writes all sixteen of its counters cnt[digit][t]: nothing to zero beforehand
+#pragma unroll
+        for (int d = 0; d < RADIX; ++d) {
+            const unsigned long long word = (d & 8) ? c_hi : c_lo;
+            s_cnt[d * SORT_THREADS + tid] = static_cast<unsigned char>(word >> ((d & 7) << 3));
         }
         __syncthreads();
         // scan of all counters in (digit, thread) order: thread t owns the 16 counters [16 t, 16 t + 16)

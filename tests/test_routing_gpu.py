@@ -207,3 +207,19 @@ def test_count_sort_full_size_properties(dist):
     ref = orc.count_sort(ids, 256)
     assert np.array_equal(ss[: 1 << 20].cpu().numpy(), ref.sorted_scattered_idxs[: 1 << 20])
     assert int(ss.sum(dtype=torch.int64)) == n * (n - 1) // 2
+
+
+def test_check_device_status_raises_once_and_clears():
+    """`xma.check_device_status()` surfaces what the kernels flagged asynchronously: an id outside the bins is
+    skipped by the kernel (the counts are those of the valid ids) and reported by the next check, which also clears
+    the word."""
+    import xma
+    from xma.functional import continuous_count
+
+    xma.check_device_status()  # clean slate
+    ids = torch.tensor([0, 1, 7, 3, 1], dtype=torch.int32, device="cuda")
+    counts = continuous_count(ids, 4)
+    assert counts.cpu().tolist() == [1, 2, 0, 1]
+    with pytest.raises(RuntimeError, match="out of range"):
+        xma.check_device_status()
+    xma.check_device_status()  # cleared by the check that raised
