@@ -324,3 +324,37 @@ def test_rows_gemm_peer_output_matches_scattered_output(impl, dtype, counts, kd,
         assert torch.equal(got, want), (b, layout)
         untouched = np.setdiff1d(np.arange(cap), slot[idx])
         assert torch.isnan(outs[b][torch.from_numpy(untouched).cuda()]).all()
+
+
+@pytest.mark.parametrize("impl", [TC, TC_PAIR])
+def test_gemms_on_expert_slices_match_the_whole(impl):
+    """The expert-parallel layer runs its experts group by group: weights `w[a:b]`, `tile_prefix[a:b+1]`,
+    `counts[a:b]`, `pad_offsets[a:b+1]` are slices of the layer's tables, the row buffers stay whole. Two calls
+    on two slices must write exactly what one call on all experts writes."""
+    from xma import _lib, ops
+
+    counts = [700, 0, 129, 2100, 64, 300]
+    E, R, kd, n, dtype = len(counts), int(sum(counts)), 192, 512, torch.bfloat16
+    plan, _ = _plan(counts, E)
+    a, _ = _grouped(plan, R, kd, dtype, seed=11)
+    y, _ = _grouped(plan, R, n, dtype, seed=12)
+    rng = np.random.RandomState(13)
+    w = torch.from_numpy((rng.standard_normal((E, n, kd)) * 0.05).astype(np.float32)).to(dtype).cuda()
+
+    whole = torch.full((plan.row_cap, n), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_rows_(a, w, _lib.W_NK, whole, None, None, plan.tile_expert, plan.tile_prefix, kd, n,
+                           _lib.EPI_PLAIN, impl)
+    dw_whole = torch.full((E, kd, n), float("nan"), dtype=dtype, device="cuda")
+    ops.grouped_gemm_dw_(a, y, plan.counts, plan.pad_offsets, dw_whole, impl)
+
+    parts = torch.full((plan.row_cap, n), float("nan"), dtype=dtype, device="cuda")
+    dw_parts = torch.full((E, kd, n), float("nan"), dtype=dtype, device="cuda")
+    for lo, hi in ((0, 2), (2, 4), (4, 6)):
+        ops.grouped_gemm_rows_(a, w[lo:hi], _lib.W_NK, parts, None, None, plan.tile_expert,
+                               plan.tile_prefix[lo:hi + 1], kd, n, _lib.EPI_PLAIN, impl)
+        ops.grouped_gemm_dw_(a, y, plan.counts[lo:hi], plan.pad_offsets[lo:hi + 1], dw_parts[lo:hi], impl)
+    torch.cuda.synchronize()
+    assert _lib.read_and_clear_device_status() == 0
+    used = int(plan.pad_offsets[-1])
+    assert torch.equal(parts[:used], whole[:used])
+    assert torch.equal(dw_parts, dw_whole)
