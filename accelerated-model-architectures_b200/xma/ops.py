@@ -348,6 +348,30 @@ def _rmsnorm_bwd_op(xr: Tensor, weight: Optional[Tensor], dy: Tensor, dxr: Optio
     )
 
 
+@torch.library.custom_op(f"{_NS}::router_prob_sums", mutates_args={"partial"}, device_types="cuda")
+def _router_prob_sums_op(logits: Tensor, partial: Tensor) -> None:
+    require_cuda(logits, partial)
+    check(
+        lib.xma_b200_router_prob_sums(
+            ptr(logits), dtype_code(logits.dtype), _row_stride(logits), logits.size(0), logits.size(1), ptr(partial),
+            partial.size(0), current_stream(logits.device)
+        ),
+        "xma_b200_router_prob_sums",
+    )
+
+
+@torch.library.custom_op(f"{_NS}::load_balancing_loss_bwd", mutates_args={"d_logits"}, device_types="cuda")
+def _load_balancing_loss_bwd_op(logits: Tensor, coef: Tensor, d_logits: Tensor) -> None:
+    require_cuda(logits, coef, d_logits)
+    check(
+        lib.xma_b200_load_balancing_loss_bwd(
+            ptr(logits), dtype_code(logits.dtype), _row_stride(logits), logits.size(0), logits.size(1), ptr(coef),
+            ptr(d_logits), current_stream(logits.device)
+        ),
+        "xma_b200_load_balancing_loss_bwd",
+    )
+
+
 # ---- launch accounting and per-kernel timing ------------------------------------------------------
 class KernelStats:
     """Counts the kernels this library launches and, when `timing` is on, brackets every op with
@@ -408,6 +432,8 @@ swiglu_packed_fwd_ = _wrap(_swiglu_packed_fwd_op, "swiglu_packed_fwd", 1)
 swiglu_packed_bwd_ = _wrap(_swiglu_packed_bwd_op, "swiglu_packed_bwd", 1)
 rmsnorm_fwd_ = _wrap(_rmsnorm_fwd_op, "rmsnorm_fwd", 1)
 rmsnorm_bwd_ = _wrap(_rmsnorm_bwd_op, "rmsnorm_bwd", 1)
+router_prob_sums_ = _wrap(_router_prob_sums_op, "router_prob_sums", 1)
+load_balancing_loss_bwd_ = _wrap(_load_balancing_loss_bwd_op, "load_balancing_loss_bwd", 1)
 
 
 # Kernel-family override for the grouped GEMMs (tests, tuning): 0 automatic, 1 CUDA cores,

@@ -258,6 +258,20 @@ int xma_b200_rmsnorm_bwd(const void* xr, int64_t xr_row_stride, const void* weig
                          int partial_rows, int dtype, int64_t rows, int64_t cols, float eps, float multiplier,
                          cudaStream_t stream);
 
+/* ---- auxiliary load-balancing loss on the router logits --------------------------------------- */
+/* No counterpart in the reference, which returns router_logits unused (xma/layers/moe/__init__.py:180); this is the
+ * usual consumer: loss = E * sum_e f_e * P_e with P_e = mean over tokens of softmax(logits)[t, e] (fp32) and
+ * f_e = (routed slots of expert e) / tokens, a count without gradient (Switch Transformer, eq. 4-6).
+ * _sums: partial[b, e] = sum over the tokens CTA b handled of softmax(logits[t, :])[e], b < partial_rows =
+ * xma_b200_router_prob_partial_rows(tokens) (fp32 [partial_rows, E]; the caller adds the rows up, a fixed order).
+ * _bwd: d_logits[t, j] = p[t, j] * (coef[j] - sum_e coef[e] * p[t, e]) with coef[e] = d loss * E * f_e / tokens
+ * (fp32 [E], device); d_logits is dense [tokens, E] in the dtype of the logits. num_experts <= 1024. */
+int xma_b200_router_prob_partial_rows(int64_t tokens);
+int xma_b200_router_prob_sums(const void* logits, int dtype, int64_t logits_row_stride, int64_t tokens,
+                              int num_experts, float* partial, int partial_rows, cudaStream_t stream);
+int xma_b200_load_balancing_loss_bwd(const void* logits, int dtype, int64_t logits_row_stride, int64_t tokens,
+                                     int num_experts, const float* coef, void* d_logits, cudaStream_t stream);
+
 /* ---- expert parallelism over peer memory ------------------------------------------------------ */
 /* None of these has a counterpart in the reference (single-device MoE, xma/layers/moe/__init__.py:144-160).
  * Rank r of `world` owns experts [r * E / world, (r + 1) * E / world). An owner keeps the rows it receives
