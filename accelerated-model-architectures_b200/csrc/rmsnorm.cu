@@ -12,6 +12,7 @@
 // The normalisation uses the value that is stored as `xr` (rounded to the storage type), so the backward,
 // which only sees `xr`, differentiates exactly what the forward computed.
 #include "common.cuh"
+#include "sm100_common.cuh"
 
 #include <initializer_list>
 
@@ -19,6 +20,7 @@ namespace xma {
 
 constexpr int RN_THREADS = 256;
 
+template <int NT = RN_THREADS>
 __device__ __forceinline__ float block_sum(float v, float* smem) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -26,7 +28,7 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
     __syncthreads();  // smem may still be read by the previous reduction
     if (lane == 0) smem[warp] = v;
     __syncthreads();
-    float t = (lane < RN_THREADS / 32) ? smem[lane] : 0.0f;
+    float t = (lane < NT / 32) ? smem[lane] : 0.0f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
     return t;
@@ -293,6 +295,235 @@ rmsnorm_bwd_kernel(const T* __restrict__ xr, int64_t xr_stride, const T* __restr
     }
 }
 
+// ---- backward, rows staged in shared memory by bulk asynchronous copies ----------------------------------------
+// The register-cached kernel above keeps at most one row per CTA in flight and stalls on it at every row boundary
+// (request, reduce, emit, request ...): 0.54-0.70 of the copy bandwidth. Here one thread asks the copy engine for
+// whole rows (cp.async.bulk, one copy per stream of the row, completion counted in bytes on an mbarrier) STAGES - 1
+// rows ahead, so that (STAGES - 1) * streams * row bytes per CTA are on their way while the CTA works on a row
+// that is already in shared memory. Requirements (checked by the launcher): 128-bit rows, a row of at most 16 KiB,
+// at most 1024 packets per row. Weight packets and the weight-gradient sums of a thread's columns stay in
+// registers for the whole kernel.
+// A wait that runs out of time (1 s) does not end the kernel and leaves no result undefined: from then on the CTA
+// fills its stage with ordinary loads instead of waiting for the copy engine.
+constexpr int RNB_MAX_STAGES = 4;
+constexpr int RNB_CTAS_PER_SM = 2;
+constexpr int RNB_MAX_ROW_BYTES = 16384;
+constexpr unsigned long long RNB_WAIT_NS = 1000000000ull;
+
+__device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :
+                 : "r"(tc::smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(tc::smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ bool rnb_wait(uint64_t* bar, uint32_t parity, volatile int* gave_up) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = tc::globaltimer_ns();
+    uint32_t spins = 0;
+    while (!tc::mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3ffu) == 0u) {
+            if (*gave_up) return false;
+            if (tc::globaltimer_ns() - t0 > RNB_WAIT_NS) {
+                *gave_up = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+template <typename T, int IPT, int NT>
+__global__ void __launch_bounds__(NT, RNB_CTAS_PER_SM)
+rmsnorm_bwd_bulk_kernel(const T* __restrict__ xr, int64_t xr_stride, const T* __restrict__ w,
+                        const T* __restrict__ dy, int64_t dy_stride, const T* __restrict__ dxr, int64_t dxr_stride,
+                        const float* __restrict__ s, T* __restrict__ dx, int64_t dx_stride, T* __restrict__ dr,
+                        int64_t dr_stride, float* __restrict__ dw_partial, int64_t rows, int cols, int stages,
+                        float eps, float multiplier) {
+    using V = Vec16<T>;
+    constexpr int N = V::N;
+    extern __shared__ __align__(128) unsigned char rnb_smem[];
+    __shared__ float red[NT / 32];
+    __shared__ int gave_up;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rnb_smem);  // [RNB_MAX_STAGES], 128 bytes reserved
+    const int items = cols / N;
+    const uint32_t row_bytes = static_cast<uint32_t>(cols) * sizeof(T);
+    const int streams = dxr ? 3 : 2;
+    unsigned char* stage0 = rnb_smem + 128;
+    const uint32_t stage_bytes = streams * row_bytes;
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    const int tid = threadIdx.x;
+
+    if (tid == 0) {
+        gave_up = 0;
+        for (int i = 0; i < stages; ++i) tc::mbar_init(&bars[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    uint32_t pending = 0, pending_parity = 0;  // thread 0: stages with a copy requested and not yet waited for
+    auto request = [&](int64_t row, int j) {   // thread 0 only; j = the CTA's running row number
+        const int st = j % stages;
+        unsigned char* dst = stage0 + static_cast<size_t>(st) * stage_bytes;
+        tc::mbar_expect_tx(&bars[st], stage_bytes);
+        bulk_load_row(dst, xr + row * xr_stride, row_bytes, &bars[st]);
+        bulk_load_row(dst + row_bytes, dy + row * dy_stride, row_bytes, &bars[st]);
+        if (dxr) bulk_load_row(dst + 2 * row_bytes, dxr + row * dxr_stride, row_bytes, &bars[st]);
+        pending |= 1u << st;
+        pending_parity = (pending_parity & ~(1u << st)) | (static_cast<uint32_t>((j / stages) & 1) << st);
+    };
+    if (tid == 0) {
+        int j = 0;
+        for (int64_t row = blockIdx.x; row < rows && j < stages - 1; row += gridDim.x, ++j) request(row, j);
+    }
+
+    V cw[IPT];
+    float acc[IPT][N];
+#pragma unroll
+    for (int k = 0; k < IPT; ++k) {
+        const int i = tid + k * NT;
+        if (w && i < items) cw[k] = load16(w + i * N);
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[k][e] = 0.0f;
+    }
+
+    // the stored 1/rms of the rows two and one step ahead: read directly it would put one DRAM latency under load
+    // (microseconds, with every SM streaming) into each row's chain of dependent steps
+    const int64_t step = gridDim.x;
+    float s_now = 0.0f, s_next = 0.0f;
+    if (s) {
+        if (blockIdx.x < rows) s_now = s[blockIdx.x];
+        if (blockIdx.x + step < rows) s_next = s[blockIdx.x + step];
+    }
+    bool bulk = true;  // the same in every thread of the CTA
+    int j = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++j) {
+        const float s_row = s_now;
+        s_now = s_next;
+        if (s && row + 2 * step < rows) s_next = s[row + 2 * step];
+        const int st = j % stages;
+        unsigned char* base = stage0 + static_cast<size_t>(st) * stage_bytes;
+        if (bulk && rnb_wait(&bars[st], (j / stages) & 1, &gave_up)) pending &= ~(1u << st);
+        __syncthreads();  // every thread is done with the previous row (its stage is free), `gave_up` is settled
+        if (bulk && gave_up) bulk = false;
+        if (!bulk) {
+            for (int i = tid; i < items; i += NT) {
+                reinterpret_cast<V*>(base)[i] = load16(xr + row * xr_stride + i * N);
+                reinterpret_cast<V*>(base + row_bytes)[i] = load16(dy + row * dy_stride + i * N);
+                if (dxr) reinterpret_cast<V*>(base + 2 * row_bytes)[i] = load16(dxr + row * dxr_stride + i * N);
+            }
+            __syncthreads();
+        } else if (tid == 0) {
+            const int64_t ahead = row + static_cast<int64_t>(stages - 1) * gridDim.x;
+            if (ahead < rows) request(ahead, j + stages - 1);
+        }
+        const V* sx = reinterpret_cast<const V*>(base);
+        const V* sg = reinterpret_cast<const V*>(base + row_bytes);
+        const V* se = reinterpret_cast<const V*>(base + 2 * row_bytes);
+
+        float rstd;
+        if (s) {
+            rstd = s_row;
+        } else {
+            float sumsq = 0.0f;
+#pragma unroll
+            for (int k = 0; k < IPT; ++k) {
+                const int i = tid + k * NT;
+                if (i < items) {
+                    float xv[N];
+                    vec_to_f32(sx[i], xv);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) sumsq += xv[e] * xv[e];
+                }
+            }
+            rstd = rsqrtf(block_sum<NT>(sumsq, red) * inv_cols + eps);
+        }
+        // pass 1: dot = sum g * z with z = xr * rstd, g = dy * weight; d weight += dy * z. With at most 16 elements
+        // per thread z and g stay in registers for pass 2 (a third of the kernel's instructions are conversions
+        // and the 16-bit variants run close to the issue limit of the SM, not only to that of HBM).
+        constexpr bool KEEP = sizeof(T) == 2 && IPT * N <= 16;  // fp32 has no conversions to save and measured slower with it
+        float zk[KEEP ? IPT : 1][N], gk[KEEP ? IPT : 1][N];
+        float dot = 0.0f;
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) {
+            const int i = tid + k * NT;
+            if (i < items) {
+                float xv[N], gv[N], wv[N];
+                vec_to_f32(sx[i], xv);
+                vec_to_f32(sg[i], gv);
+                if (w) vec_to_f32(cw[k], wv);
+#pragma unroll
+                for (int e = 0; e < N; ++e) {
+                    const float z = xv[e] * rstd;
+                    acc[k][e] = fmaf(gv[e], z, acc[k][e]);
+                    const float g = w ? gv[e] * wv[e] : gv[e];
+                    dot = fmaf(g, z, dot);
+                    if (KEEP) {
+                        zk[k][e] = z;
+                        gk[k][e] = g;
+                    }
+                }
+            }
+        }
+        const float c = block_sum<NT>(dot, red) * inv_cols;
+        const float neg_c = -c;
+        const bool scaled = multiplier != 1.0f;
+        // pass 2: d = (g - z * c) * rstd + d(xr)
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) {
+            const int i = tid + k * NT;
+            if (i < items) {
+                float ev[N], d[N];
+                if (dxr) vec_to_f32(se[i], ev);
+                if (KEEP) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) d[e] = fmaf(zk[k][e], neg_c, gk[k][e]);
+                } else {
+                    float xv[N], gv[N], wv[N];
+                    vec_to_f32(sx[i], xv);
+                    vec_to_f32(sg[i], gv);
+                    if (w) vec_to_f32(cw[k], wv);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) d[e] = fmaf(xv[e] * rstd, neg_c, w ? gv[e] * wv[e] : gv[e]);
+                }
+#pragma unroll
+                for (int e = 0; e < N; ++e) d[e] = dxr ? fmaf(d[e], rstd, ev[e]) : d[e] * rstd;
+                V q;
+                vec_from_f32(d, q);
+                if (dr) store16(dr + row * dr_stride + i * N, q);
+                if (scaled) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) d[e] *= multiplier;
+                    vec_from_f32(d, q);
+                }
+                store16(dx + row * dx_stride + i * N, q);
+            }
+        }
+    }
+    if (dw_partial) {
+        float* my_dw = dw_partial + static_cast<int64_t>(blockIdx.x) * cols;
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) {
+            const int i = tid + k * NT;
+            if (i < items) {
+#pragma unroll
+                for (int e = 0; e < N; e += 4)
+                    *reinterpret_cast<float4*>(my_dw + i * N + e) =
+                        make_float4(acc[k][e], acc[k][e + 1], acc[k][e + 2], acc[k][e + 3]);
+            }
+        }
+    }
+    // copies that were requested and never waited for (only after a wait gave up): one more bounded wait each, so
+    // that the CTA does not leave while the copy engine may still write into its shared memory
+    if (tid == 0 && pending) {
+        for (int st = 0; st < stages; ++st)
+            if (pending & (1u << st)) {
+                int fresh = 0;
+                rnb_wait(&bars[st], (pending_parity >> st) & 1u, &fresh);
+            }
+    }
+}
+
 static int rn_grid(int64_t rows) {
     const int64_t cap = static_cast<int64_t>(num_sms()) * 4;
     return static_cast<int>(rows < 1 ? 1 : (rows > cap ? cap : rows));
@@ -348,6 +579,44 @@ static int rmsnorm_fwd_impl(const void* x, int64_t xs, const void* r, int64_t rs
     return static_cast<int>(cudaGetLastError());
 }
 
+// Shared memory of the bulk-copy backward: as many CTAs per SM (at most RNB_CTAS_PER_SM) as still keep 64 KiB of
+// copies in flight per SM; with fewer bytes than that whatever keeps the most.
+struct BulkPlan {
+    int stages = 0, ctas_per_sm = 0, smem_bytes = 0;
+};
+
+static BulkPlan rn_bulk_plan(int64_t row_bytes, int streams) {
+    BulkPlan best;
+    if (row_bytes <= 0 || row_bytes > RNB_MAX_ROW_BYTES || row_bytes % 16) return best;
+    const int64_t stage = streams * row_bytes;
+    int64_t best_flight = -1;
+    for (int ctas = RNB_CTAS_PER_SM; ctas >= 1; --ctas) {
+        const int64_t room = (227 * 1024) / ctas - 1024 /*reserved per CTA*/ - 128 /*barriers*/ - 64 /*static*/;
+        int64_t stages = room / stage;
+        if (stages > RNB_MAX_STAGES) stages = RNB_MAX_STAGES;
+        if (stages < 2) continue;
+        const int64_t flight = ctas * (stages - 1) * stage;
+        const bool enough = flight >= 64 * 1024;
+        if (flight > best_flight) {
+            best_flight = flight;
+            best.stages = static_cast<int>(stages);
+            best.ctas_per_sm = ctas;
+            best.smem_bytes = static_cast<int>(128 + stages * stage);
+        }
+        if (enough) break;
+    }
+    return best;
+}
+
+// XMA_B200_RMSNORM_BULK=0 keeps the backward on the register-cached kernel (for comparisons).
+static bool rn_bulk_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("XMA_B200_RMSNORM_BULK");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 template <typename T>
 static int rmsnorm_bwd_impl(const void* xr, int64_t xrs, const void* w, const void* dy, int64_t dys, const void* dxr,
                             int64_t dxrs, const float* s, void* dx, int64_t dxs, void* dr, int64_t drs,
@@ -359,7 +628,36 @@ static int rmsnorm_bwd_impl(const void* xr, int64_t xrs, const void* w, const vo
     const T* dxrp = static_cast<const T*>(dxr);
     T* dxp = static_cast<T*>(dx);
     T* drp = static_cast<T*>(dr);
-    if (rn_vec_ok<T>(cols, {xrs, dys, dxr ? dxrs : 0, dxs, dr ? drs : 0}, {xr, w, dy, dxr, dx, dr})) {
+    const bool vec = rn_vec_ok<T>(cols, {xrs, dys, dxr ? dxrs : 0, dxs, dr ? drs : 0}, {xr, w, dy, dxr, dx, dr});
+    if (vec && rn_bulk_enabled() && is_aligned16(dw_partial)) {
+        const int64_t items = cols / Vec16<T>::N;
+        const BulkPlan plan = rn_bulk_plan(cols * static_cast<int64_t>(sizeof(T)), dxr ? 3 : 2);
+        if (plan.stages >= 2 && items <= 1024) {
+            int g = static_cast<int>(rows < static_cast<int64_t>(num_sms()) * plan.ctas_per_sm
+                                         ? rows
+                                         : static_cast<int64_t>(num_sms()) * plan.ctas_per_sm);
+            if (dw_partial) {
+                // `grid` is the number of partial rows the caller sums; the CTAs of this kernel fill the first g
+                if (g > grid) g = grid;
+                if (g < grid)
+                    XMA_CUDA_TRY(cudaMemsetAsync(dw_partial + static_cast<int64_t>(g) * cols, 0,
+                                                 sizeof(float) * static_cast<size_t>(grid - g) * cols, st));
+            }
+#define XMA_RNB_LAUNCH(IPT, NT)                                                                                     \
+    do {                                                                                                            \
+        auto kernel = rmsnorm_bwd_bulk_kernel<T, IPT, NT>;                                                          \
+        XMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));   \
+        kernel<<<g, NT, plan.smem_bytes, st>>>(xp, xrs, wp, dyp, dys, dxrp, dxrs, s, dxp, dxs, drp, drs, dw_partial, \
+                                               rows, static_cast<int>(cols), plan.stages, eps, multiplier);         \
+    } while (0)
+            if (items <= 256) XMA_RNB_LAUNCH(1, 256);
+            else if (items <= 512) XMA_RNB_LAUNCH(2, 256);
+            else XMA_RNB_LAUNCH(4, 256);
+#undef XMA_RNB_LAUNCH
+            return static_cast<int>(cudaGetLastError());
+        }
+    }
+    if (vec) {
         XMA_RN_DISPATCH(rmsnorm_bwd_kernel, true, cols / Vec16<T>::N, grid,
                         (dw_partial ? RN_THREADS * Vec16<T>::N * sizeof(float) : 0), st, xp, xrs, wp, dyp, dys, dxrp, dxrs, s,
                         dxp, dxs, drp, drs, dw_partial, rows, cols, eps, multiplier)

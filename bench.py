@@ -441,8 +441,10 @@ def run_swiglu_microbench(args) -> None:
     torch.cuda.set_device(device)
     peaks, peak_kind = measured_peaks()
     hbm = float(peaks.get("hbm_gbs", PEAK_FALLBACK["hbm_gbs"]))
-    B, H = 16 * 4096, 4096
-    steps, warm = max(args.steps, 20), max(args.warmup, 5)
+    B, H = int(args.rmsnorm_rows), 4096
+    full = B == 16 * 4096
+    steps, warm = (max(args.steps, 20), max(args.warmup, 5)) if full else (args.steps, args.warmup)
+    wanted = [t.strip() for t in args.rmsnorm_dtypes.split(",") if t.strip()]
 
     def timed(fn) -> float:
         for _ in range(warm):
@@ -513,8 +515,10 @@ def run_rmsnorm_microbench(args) -> None:
     torch.cuda.set_device(device)
     peaks, peak_kind = measured_peaks()
     hbm = float(peaks.get("hbm_gbs", PEAK_FALLBACK["hbm_gbs"]))
-    B, H = 16 * 4096, 4096
-    steps, warm = max(args.steps, 20), max(args.warmup, 5)
+    B, H = int(args.rmsnorm_rows), 4096
+    full = B == 16 * 4096
+    steps, warm = (max(args.steps, 20), max(args.warmup, 5)) if full else (args.steps, args.warmup)
+    wanted = [t.strip() for t in args.rmsnorm_dtypes.split(",") if t.strip()]
 
     def timed(fn) -> float:
         for _ in range(warm):
@@ -530,6 +534,8 @@ def run_rmsnorm_microbench(args) -> None:
 
     out = {}
     for dtype, tag in ((torch.float32, "f32"), (torch.float16, "f16"), (torch.bfloat16, "bf16")):
+        if tag not in wanted:
+            continue
         item = torch.empty((), dtype=dtype).element_size()
         x = torch.randn(B, H, device=device, dtype=dtype, requires_grad=True)
         r = torch.randn(B, H, device=device, dtype=dtype, requires_grad=True)
@@ -544,7 +550,8 @@ def run_rmsnorm_microbench(args) -> None:
     for v in out.values():
         v["frac"] = v["gbs"] / hbm
     worst = min(out, key=lambda k: out[k]["frac"])
-    head = out["rmsnorm_fwd_bf16"]
+    head_name = "rmsnorm_fwd_bf16" if "rmsnorm_fwd_bf16" in out else sorted(out)[0]
+    head = out[head_name]
     print(json.dumps({
         "metric": "rmsnorm_hbm_gb_per_s", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
         "warmup": warm, "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -552,7 +559,7 @@ def run_rmsnorm_microbench(args) -> None:
         "config": {"workload": f"rmsnorm: fused_residual_add_rmsnorm, {B} x {H}, fp32/fp16/bf16, forward and backward "
                                "(backward includes the sum of the weight-gradient partial rows)",
                    "l2_policy": "inputs_exceed_l2"},
-        "roofline": {"bound": "hbm", "kernel": "rmsnorm_fwd_kernel<bf16>", "achieved": head["gbs"], "peak": hbm,
+        "roofline": {"bound": "hbm", "kernel": head_name, "achieved": head["gbs"], "peak": hbm,
                      "unit": "GB/s", "frac": head["frac"], "peak_source": f"{peak_kind} copy bandwidth",
                      "traffic": None},
         "lowest": {"kernel": worst, **out[worst]},
@@ -946,6 +953,10 @@ def main() -> None:
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "ep", "swiglu", "rmsnorm"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--ids-log2", type=int, default=26, help="workload c5: log2 of the number of ids (default 64 Mi)")
+    ap.add_argument("--rmsnorm-rows", type=int, default=16 * 4096,
+                    help="workload rmsnorm: rows of the [rows, 4096] activation (default 65536; a profiler capture "
+                         "takes fewer)")
+    ap.add_argument("--rmsnorm-dtypes", default="f32,f16,bf16", help="workload rmsnorm: which of f32,f16,bf16 to run")
     ap.add_argument("--ids-only", action="store_true",
                     help="workload c5: histogram and counting sort only, no row permute (small profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -100,6 +100,45 @@ def test_rmsnorm_size_grid(dtype, memory_efficient, has_weight, multiplier):
             _close(wd.grad, dw, dtype, f"dw cols={cols}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cols", [64, 520, 2048, 4096, 8192])
+@pytest.mark.parametrize("has_residual,has_weight,memory_efficient", [(True, True, False), (False, True, True),
+                                                                      (True, False, False)])
+def test_rmsnorm_many_rows(dtype, cols, has_residual, has_weight, memory_efficient):
+    """More rows than CTAs of the backward kernel, so that each CTA walks several rows through its staged
+    pipeline (rows requested ahead, stages reused); random gradients for both outputs."""
+    from xma.functional import fused_residual_add_rmsnorm
+
+    rows = 3001
+    rng = np.random.RandomState(cols + rows)
+    mk = lambda *s: torch.from_numpy(rng.standard_normal(s).astype(np.float32)).to(dtype)
+    x = mk(rows, cols)
+    r = mk(rows, cols) if has_residual else None
+    w = (1.0 + 0.1 * mk(cols).float()).to(dtype) if has_weight else None
+    dy = mk(rows, cols)
+    dxr = mk(rows, cols) if has_residual else None
+    dev = lambda t: None if t is None else t.cuda().requires_grad_()
+    xd, rd, wd = dev(x), dev(r), dev(w)
+    y, xr = fused_residual_add_rmsnorm(xd, rd, wd, EPS, None, memory_efficient)
+    loss = (y * dy.cuda()).sum()
+    if has_residual:
+        loss = loss + (xr * dxr.cuda()).sum()
+    loss.backward()
+    torch.cuda.synchronize()
+
+    np_ = lambda t: None if t is None else t.double().numpy()
+    stream = np_(xr.detach().cpu()) if has_residual else np_(x)
+    ref_y, _, _ = rn.forward(stream, None, np_(w), EPS, None)
+    _close(y, ref_y, dtype, "y")
+    dv, _, dw = rn.backward(stream, None, np_(w), EPS, None, np_(dy), np_(dxr))
+    _close(xd.grad, dv, dtype, "dx")
+    if has_residual:
+        _close(rd.grad, dv, dtype, "dr")
+    if has_weight:
+        # a sum over 3001 rows of products rounded to the storage type only at the end: fp32 accumulation
+        _close(wd.grad, dw, dtype, "dw")
+
+
 def test_rmsnorm_without_residual_and_unused_outputs():
     """No residual: the second result is None; with a multiplier the gradient is that of the function computed.
     A residual stream nobody reads contributes no gradient (d(xr) absent, not zeros read from memory)."""
