@@ -20,7 +20,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libxma_b200.so")
 OBJ_DIR = os.path.join(_HERE, "build")
 
 SOURCES = ["routing.cu", "permute.cu", "swiglu.cu", "gemm_simt.cu", "grouped_gemm_sm100.cu", "grouped_gemm_sm100_2cta.cu",
-           "gemm_api.cu", "expert_parallel.cu", "rmsnorm.cu", "aux_loss.cu"]
+           "gemm_api.cu", "expert_parallel.cu", "rmsnorm.cu", "aux_loss.cu", "sequence_packing.cu"]
 HEADERS = ["common.cuh", "gemm_internal.h", "sm100_common.cuh"]
 
 NVCC_FLAGS = [

@@ -84,6 +84,10 @@ _SIGNATURES = {
     "xma_b200_router_prob_partial_rows": [c_int64],
     "xma_b200_router_prob_sums": [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p],
     "xma_b200_load_balancing_loss_bwd": [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p],
+    "xma_b200_pack_sequence": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int,
+                               c_void_p, c_void_p],
+    "xma_b200_unpack_sequence": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int,
+                                 c_void_p, c_void_p],
     "xma_b200_ep_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                          c_void_p, c_int64, c_void_p, c_void_p],
     "xma_b200_ep_dispatch": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,

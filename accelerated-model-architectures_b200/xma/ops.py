@@ -372,6 +372,45 @@ def _load_balancing_loss_bwd_op(logits: Tensor, coef: Tensor, d_logits: Tensor) 
     )
 
 
+def _offsets_code(cu_seqlens: Tensor) -> int:
+    # uint32 offsets (the reference's tests pass them) read as int32 below 2^31
+    if cu_seqlens.dtype in (torch.int32, torch.uint32):
+        return _lib.I32
+    if cu_seqlens.dtype == torch.int64:
+        return _lib.I64
+    raise TypeError(f"cu_seqlens must be int32, uint32 or int64, not {cu_seqlens.dtype}")
+
+
+def _sequence_packing(fn_name: str, src: Tensor, dst: Tensor, padded: Tensor, packed: Tensor, cu_seqlens: Tensor,
+                      left: bool) -> None:
+    require_cuda(src, dst, cu_seqlens)
+    if not (src.is_contiguous() and dst.is_contiguous() and cu_seqlens.is_contiguous()):
+        raise ValueError("pack/unpack_sequence kernels take contiguous buffers")
+    batch, seq_len = padded.size(0), padded.size(1)
+    row = 1
+    for d in packed.shape[1:]:
+        row *= d
+    if tuple(padded.shape[2:]) != tuple(packed.shape[1:]) or cu_seqlens.numel() != batch + 1:
+        raise ValueError("padded must be [B, S, ...], packed [T, ...] with the same trailing shape, cu_seqlens [B + 1]")
+    check(
+        getattr(lib, fn_name)(
+            ptr(src), ptr(dst), ptr(cu_seqlens), _offsets_code(cu_seqlens), batch, seq_len, packed.size(0),
+            row * packed.element_size(), 1 if left else 0, ptr(status_word(src.device)), current_stream(src.device)
+        ),
+        fn_name,
+    )
+
+
+@torch.library.custom_op(f"{_NS}::pack_sequence", mutates_args={"packed"}, device_types="cuda")
+def _pack_sequence_op(padded: Tensor, cu_seqlens: Tensor, packed: Tensor, left: bool) -> None:
+    _sequence_packing("xma_b200_pack_sequence", padded, packed, padded, packed, cu_seqlens, left)
+
+
+@torch.library.custom_op(f"{_NS}::unpack_sequence", mutates_args={"padded"}, device_types="cuda")
+def _unpack_sequence_op(packed: Tensor, cu_seqlens: Tensor, padded: Tensor, left: bool) -> None:
+    _sequence_packing("xma_b200_unpack_sequence", packed, padded, padded, packed, cu_seqlens, left)
+
+
 # ---- launch accounting and per-kernel timing ------------------------------------------------------
 class KernelStats:
     """Counts the kernels this library launches and, when `timing` is on, brackets every op with
@@ -434,6 +473,8 @@ rmsnorm_fwd_ = _wrap(_rmsnorm_fwd_op, "rmsnorm_fwd", 1)
 rmsnorm_bwd_ = _wrap(_rmsnorm_bwd_op, "rmsnorm_bwd", 1)
 router_prob_sums_ = _wrap(_router_prob_sums_op, "router_prob_sums", 1)
 load_balancing_loss_bwd_ = _wrap(_load_balancing_loss_bwd_op, "load_balancing_loss_bwd", 1)
+pack_sequence_ = _wrap(_pack_sequence_op, "pack_sequence", 1)
+unpack_sequence_ = _wrap(_unpack_sequence_op, "unpack_sequence", 1)
 
 
 # Kernel-family override for the grouped GEMMs (tests, tuning): 0 automatic, 1 CUDA cores,

@@ -568,6 +568,69 @@ def run_rmsnorm_microbench(args) -> None:
 
 
 # ---------------------------------------------------------------------------------------------------
+# pack_sequence / unpack_sequence (HBM-bound)
+# ---------------------------------------------------------------------------------------------------
+def run_packing_microbench(args) -> None:
+    """`pack_sequence` and `unpack_sequence` on a ragged training batch: 16 sequences padded to 4096 tokens of
+    4096 bf16 values (512 MiB padded), seeded lengths uniform in [1024, 4096], both padding sides. Algorithmic bytes:
+    pack reads and writes the valid tokens (2 * T * row bytes); unpack reads the valid tokens and writes the whole
+    padded batch ((T + B * S) * row bytes)."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    from xma.functional import pack_sequence, unpack_sequence
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks.get("hbm_gbs", PEAK_FALLBACK["hbm_gbs"]))
+    B, S, H = 16, 4096, 4096
+    steps, warm = max(args.steps, 20), max(args.warmup, 5)
+    rng = np.random.RandomState(0)
+    lens = rng.randint(1024, S + 1, size=B)
+    cu_list = [0] + np.cumsum(lens).tolist()
+    T = cu_list[-1]
+    cu = torch.tensor(cu_list, device=device, dtype=torch.int32)
+    x = torch.randn(B, S, H, device=device, dtype=torch.bfloat16)
+    p = torch.randn(T, H, device=device, dtype=torch.bfloat16)
+    row = H * 2
+
+    def timed(fn) -> float:
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    out = {}
+    for side in ("left", "right"):
+        ms = timed(lambda: pack_sequence([x], cu, T, side))
+        out[f"pack_{side}"] = {"ms": ms, "gbs": 2 * T * row / ms / 1e6}
+        ms = timed(lambda: unpack_sequence([p], cu, B, S, side))
+        out[f"unpack_{side}"] = {"ms": ms, "gbs": (T + B * S) * row / ms / 1e6}
+    for v in out.values():
+        v["frac"] = v["gbs"] / hbm
+    worst = min(out, key=lambda k: out[k]["frac"])
+    head = out["pack_left"]
+    print(json.dumps({
+        "metric": "pack_sequence_hbm_gb_per_s", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
+        "warmup": warm, "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bytes", "data": "synthetic",
+        "config": {"workload": f"packing: pack_sequence / unpack_sequence, {B} x {S} x {H} bf16 padded, {T} valid "
+                               "tokens, both padding sides", "l2_policy": "inputs_exceed_l2"},
+        "roofline": {"bound": "hbm", "kernel": "sequence_packing_kernel<uint4, int, pack>", "achieved": head["gbs"],
+                     "peak": hbm, "unit": "GB/s", "frac": head["frac"], "peak_source": f"{peak_kind} copy bandwidth",
+                     "traffic": None},
+        "lowest": {"kernel": worst, **out[worst]},
+        "kernels": out,
+    }), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
 # DRAM traffic table (ncu) and kernel names
 # ---------------------------------------------------------------------------------------------------
 KERNEL_SOURCES = ("grouped_gemm_sm100.cu", "grouped_gemm_sm100_2cta.cu", "sm100_common.cuh", "gemm_api.cu")
@@ -950,7 +1013,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "ep", "swiglu", "rmsnorm"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "ep", "swiglu", "rmsnorm", "packing"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--ids-log2", type=int, default=26, help="workload c5: log2 of the number of ids (default 64 Mi)")
     ap.add_argument("--rmsnorm-rows", type=int, default=16 * 4096,
@@ -981,6 +1044,8 @@ def main() -> None:
         return
     if args.workload == "rmsnorm":
         return run_rmsnorm_microbench(args)
+    if args.workload == "packing":
+        return run_packing_microbench(args)
     if args.workload == "swiglu":
         run_swiglu_microbench(args)
         return

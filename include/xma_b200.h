@@ -272,6 +272,27 @@ int xma_b200_router_prob_sums(const void* logits, int dtype, int64_t logits_row_
 int xma_b200_load_balancing_loss_bwd(const void* logits, int dtype, int64_t logits_row_stride, int64_t tokens,
                                      int num_experts, const float* coef, void* d_logits, cudaStream_t stream);
 
+/* ---- pack_sequence / unpack_sequence ----------------------------------------------------------- */
+/* Replace the kernels behind xma.functional.pack_sequence / unpack_sequence
+ * (xma/functional/sequence_packing/__init__.py:39-132; cuda_implementation.py:17-98, launched from :101-134;
+ * semantics of torch_implementation.py:9-48).
+ *   padded [batch, seq_len, row]   packed [total_tokens, row]   cu_seqlens [batch + 1] (device; cu_dtype XMA_I32 -
+ *   which also takes uint32 offsets below 2^31 - or XMA_I64), row given in BYTES (product of the trailing
+ *   dimensions x itemsize): the kernels copy bytes and do not care about the element type.
+ * Sequence b holds tokens cu_seqlens[b] .. cu_seqlens[b + 1] - 1 of the packed buffer; in the padded buffer they
+ * are the LAST len_b positions of row b (left_padding != 0) or the first (left_padding == 0).
+ * _pack: writes every row of `packed`: the tokens of the sequences (cu_seqlens[0] = 0) and zeros in rows behind
+ * cu_seqlens[batch], if total_tokens is larger.
+ * _unpack: writes ALL of `padded`, the tokens and zeros in the padding (no zero-fill by the caller).
+ * A sequence whose offsets leave [0, total_tokens] or whose length exceeds seq_len is skipped (zeros on unpack) and
+ * sets bit 1 of *device_status (may be NULL). Both buffers contiguous; any alignment (the copy unit adapts). */
+int xma_b200_pack_sequence(const void* padded, void* packed, const void* cu_seqlens, int cu_dtype, int64_t batch,
+                           int64_t seq_len, int64_t total_tokens, int64_t row_bytes, int left_padding,
+                           int* device_status, cudaStream_t stream);
+int xma_b200_unpack_sequence(const void* packed, void* padded, const void* cu_seqlens, int cu_dtype, int64_t batch,
+                             int64_t seq_len, int64_t total_tokens, int64_t row_bytes, int left_padding,
+                             int* device_status, cudaStream_t stream);
+
 /* ---- expert parallelism over peer memory ------------------------------------------------------ */
 /* None of these has a counterpart in the reference (single-device MoE, xma/layers/moe/__init__.py:144-160).
  * Rank r of `world` owns experts [r * E / world, (r + 1) * E / world). An owner keeps the rows it receives

@@ -32,6 +32,15 @@ RMSNORM_CASES = {
 }
 RMSNORM_EPS = 1e-5
 
+# pack_sequence / unpack_sequence: name -> (cumulative sequence lengths, padded length S, trailing shape).
+# The first is the reference test's own cu_seqlens (tests/functional/pack_sequence_test.py:28) at a reduced S.
+PACK_CASES = {
+    "ref_cu_3x4": ([0, 70, 170, 295, 393, 412, 515, 691], 180, (3, 4)),
+    "ragged_9x7": ([0, 5, 5, 17, 18, 40], 23, (9, 7)),
+    "scalar_rows": ([0, 3, 11, 12], 9, (1, 1)),
+    "full_and_empty": ([0, 6, 6, 12], 6, (3,)),
+}
+
 
 def moe_inputs(name: str, dtype: torch.dtype = torch.float32, seed: int = 0):
     """x ~ N(0,1); gate and expert weights ~ N(0, 0.02); dy ~ N(0,1). Values are rounded to `dtype`
@@ -78,6 +87,17 @@ def rmsnorm_inputs(name: str, seed: int = 11):
     dy = f(rng.standard_normal((rows, cols)))
     dxr = f(rng.standard_normal((rows, cols))) if has_r else None
     return dict(x=x, residual=r, weight=w, dy=dy, dxr=dxr, multiplier=multiplier)
+
+
+def pack_inputs(name: str, seed: int = 0):
+    """Padded batch x [B, S, ...] and packed batch p [T, ...] of fp32 N(0,1) values, with upstream gradients for the
+    packed (`dpacked`) and the padded (`dpadded`) results."""
+    cu, S, trailing = PACK_CASES[name]
+    rng = np.random.RandomState(seed)
+    f = lambda *s: torch.from_numpy(rng.standard_normal(s).astype(np.float32))
+    B, T = len(cu) - 1, cu[-1]
+    return dict(cu_seqlens=cu, seq_len=S, x=f(B, S, *trailing), p=f(T, *trailing), dpacked=f(T, *trailing),
+                dpadded=f(B, S, *trailing))
 
 
 def sample(t: torch.Tensor, limit: int = 4096) -> np.ndarray:

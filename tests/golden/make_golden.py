@@ -80,27 +80,49 @@ def main(root: str, only: str | None = None) -> None:
     KB = ref.KernelBackend.torch
     torch.set_num_threads(max(1, (os.cpu_count() or 2) // 2))
 
-    # ---- fused_residual_add_rmsnorm (forward and gradients for given upstream gradients) ----------
-    from xma_ref.functional import fused_residual_add_rmsnorm
+    if only in (None, "rmsnorm"):
+        # ---- fused_residual_add_rmsnorm (forward and gradients for given upstream gradients) ----------
+        from xma_ref.functional import fused_residual_add_rmsnorm
+
+        out = {}
+        for name in gi.RMSNORM_CASES:
+            inp = gi.rmsnorm_inputs(name)
+            x = inp["x"].clone().requires_grad_()
+            r = None if inp["residual"] is None else inp["residual"].clone().requires_grad_()
+            w = None if inp["weight"] is None else inp["weight"].clone().requires_grad_()
+            y, xr = fused_residual_add_rmsnorm(x, r, w, gi.RMSNORM_EPS, inp["multiplier"], kernel_backend=KB)
+            loss = (y * inp["dy"]).sum()
+            if xr is not None:
+                loss = loss + (xr * inp["dxr"]).sum()
+            loss.backward()
+            out[name + ".y"], out[name + ".dx"] = y.detach().numpy(), x.grad.numpy()
+            if xr is not None:
+                out[name + ".xr"], out[name + ".dr"] = xr.detach().numpy(), r.grad.numpy()
+            if w is not None:
+                out[name + ".dw"] = w.grad.numpy()
+        np.savez_compressed(os.path.join(HERE, "rmsnorm.npz"), **out)
+    if only == "rmsnorm":
+        return
+
+    # ---- pack_sequence / unpack_sequence (outputs and gradients, both padding sides) ----------
+    from xma_ref.functional import pack_sequence, unpack_sequence
 
     out = {}
-    for name in gi.RMSNORM_CASES:
-        inp = gi.rmsnorm_inputs(name)
-        x = inp["x"].clone().requires_grad_()
-        r = None if inp["residual"] is None else inp["residual"].clone().requires_grad_()
-        w = None if inp["weight"] is None else inp["weight"].clone().requires_grad_()
-        y, xr = fused_residual_add_rmsnorm(x, r, w, gi.RMSNORM_EPS, inp["multiplier"], kernel_backend=KB)
-        loss = (y * inp["dy"]).sum()
-        if xr is not None:
-            loss = loss + (xr * inp["dxr"]).sum()
-        loss.backward()
-        out[name + ".y"], out[name + ".dx"] = y.detach().numpy(), x.grad.numpy()
-        if xr is not None:
-            out[name + ".xr"], out[name + ".dr"] = xr.detach().numpy(), r.grad.numpy()
-        if w is not None:
-            out[name + ".dw"] = w.grad.numpy()
-    np.savez_compressed(os.path.join(HERE, "rmsnorm.npz"), **out)
-    if only == "rmsnorm":
+    for name in gi.PACK_CASES:
+        inp = gi.pack_inputs(name)
+        cu = torch.tensor(inp["cu_seqlens"], dtype=torch.int32)
+        B, S = len(inp["cu_seqlens"]) - 1, inp["seq_len"]
+        for side in ("left", "right"):
+            x = inp["x"].clone().requires_grad_()
+            (y,) = pack_sequence([x], cu, inp["cu_seqlens"][-1], side, kernel_backend=KB)
+            (y * inp["dpacked"]).sum().backward()
+            out[f"{name}.{side}.pack"], out[f"{name}.{side}.pack_dx"] = y.detach().numpy(), x.grad.numpy()
+            p = inp["p"].clone().requires_grad_()
+            (z,) = unpack_sequence([p], cu, B, S, side, kernel_backend=KB)
+            (z * inp["dpadded"]).sum().backward()
+            out[f"{name}.{side}.unpack"], out[f"{name}.{side}.unpack_dx"] = z.detach().numpy(), p.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "sequence_packing.npz"), **out)
+    if only == "sequence_packing":
         return
 
     # ---- continuous_count -------------------------------------------------------------------
@@ -169,5 +191,5 @@ def main(root: str, only: str | None = None) -> None:
 
 if __name__ == "__main__":
     if len(sys.argv) not in (2, 3):
-        sys.exit("usage: make_golden.py <path-to-reference-checkout> [rmsnorm]")
+        sys.exit("usage: make_golden.py <path-to-reference-checkout> [rmsnorm | sequence_packing]")
     main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

@@ -134,3 +134,19 @@ def test_rmsnorm_oracle_matches_reference(name):
         np.testing.assert_allclose(dr, gold[name + ".dr"], rtol=2e-5, atol=5e-6)
     if w is not None:
         np.testing.assert_allclose(dw, gold[name + ".dw"], rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("side", ["left", "right"])
+@pytest.mark.parametrize("name", list(gi.PACK_CASES))
+def test_sequence_packing_oracle_matches_reference(name, side):
+    """pack_sequence / unpack_sequence and their gradients: bit for bit against the reference's torch path."""
+    from oracle import sequence_packing_oracle as sp
+
+    gold = np.load(os.path.join(GOLDEN, "sequence_packing.npz"))
+    inp = gi.pack_inputs(name)
+    cu, S = inp["cu_seqlens"], inp["seq_len"]
+    key = f"{name}.{side}."
+    assert np.array_equal(sp.pack(inp["x"].numpy(), cu, side), gold[key + "pack"])
+    assert np.array_equal(sp.pack_backward(inp["dpacked"].numpy(), cu, S, side), gold[key + "pack_dx"])
+    assert np.array_equal(sp.unpack(inp["p"].numpy(), cu, S, side), gold[key + "unpack"])
+    assert np.array_equal(sp.unpack_backward(inp["dpadded"].numpy(), cu, side), gold[key + "unpack_dx"])
