@@ -24,6 +24,7 @@ Tuning& tuning() {
         env("XMA_B200_EPI_WARPS", t.epi_warps);
         env("XMA_B200_PLAIN_PAIRS", t.plain_pairs);
         env("XMA_B200_DW_DYNAMIC", t.dw_dynamic);
+        env("XMA_B200_DSWIGLU_STAGED", t.dswiglu_staged);
     });
     return t;
 }
@@ -226,6 +227,7 @@ int xma_b200_tuning_set(int key, int value) {
         case 3: field = &t.epi_warps; break;
         case 4: field = &t.plain_pairs; break;
         case 5: field = &t.dw_dynamic; break;
+        case 6: field = &t.dswiglu_staged; break;
         default: return XMA_ERR_BAD_SHAPE;
     }
     const int previous = *field;

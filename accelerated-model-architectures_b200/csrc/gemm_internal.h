@@ -20,10 +20,13 @@ enum WeightLayout { W_NK = 0, W_KN = 1 };
 //                 where acc is the gradient of the activation output.
 //   EPI_SWIGLU_PACKED / EPI_DSWIGLU_PACKED : the same with gate/up interleaved along the columns
 //                 (g, u, g, u, ...) in aux and in the weight rows, as swiglu_packed expects.
+//   EPI_DSWIGLU_STAGED : internal (CTA-pair kernel): EPI_DSWIGLU with gate|up fetched and d gate|d up stored by TMA
+//                    through shared memory, 32 columns at a time
 //   EPI_PLAIN_PEER : internal (chosen when out_peers is set): plain store of each row into the buffer of
 //                 the rank that row_map names.
 enum Epilogue {
-    EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2, EPI_SWIGLU_PACKED = 3, EPI_DSWIGLU_PACKED = 4, EPI_PLAIN_PEER = 5
+    EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2, EPI_SWIGLU_PACKED = 3, EPI_DSWIGLU_PACKED = 4, EPI_PLAIN_PEER = 5,
+    EPI_DSWIGLU_STAGED = 6
 };
 
 struct RowsGemmArgs {
@@ -79,6 +82,8 @@ struct Tuning {
     int epi_warps = 0;          // 4 or 8 epilogue warps; 0 = per-kernel default
     int plain_pairs = 1;        // automatic choice: CTA pairs also for the plain epilogues of large experts
     int dw_dynamic = 1;         // weight-gradient pair kernel: tiles by atomic ticket, heaviest experts first
+    int dswiglu_staged = 1;     // SwiGLU-backward epilogue of the pair kernel: gate|up and d gate|d up through
+                                // shared memory by TMA (when the shapes allow) instead of row-per-thread accesses
 };
 Tuning& tuning();
 uint32_t tune_word();  // the switches the kernels read, packed (see sm100_common.cuh)

@@ -27,6 +27,21 @@ constexpr int STAGE2_BYTES = A2_BYTES + B2_BYTES;
 constexpr size_t SMEM2_BYTES = 1024 + static_cast<size_t>(STAGES2) * STAGE2_BYTES +
                                2 * (MAX_EXPERTS + 1) * sizeof(int) + 256 + PEER_STAGE_BYTES;
 
+// Staged SwiGLU-backward epilogue (EPI_DSWIGLU_STAGED): every epilogue warp owns two 4 KiB buffers, each holding
+// the gate and the up values of its 32 rows x 32 columns (two TMA boxes, 64-byte swizzle). The room comes from the
+// staging of the peer epilogue, which this variant does not use, and from expert tables sized for at most
+// STAGED_MAX_EXPERTS experts.
+constexpr int STAGED_MAX_EXPERTS = 192;
+constexpr int GU_BOX_COLS = 32;
+constexpr int GU_HALF_BYTES = 32 * GU_BOX_COLS * 2;  // 32 rows x 32 columns of 16-bit values: 2 KiB
+constexpr int GU_BUF_BYTES = 2 * GU_HALF_BYTES;      // gate | up
+constexpr int GU_WARP_BYTES = 2 * GU_BUF_BYTES;      // two buffers per epilogue warp
+constexpr int GU_STAGE_BYTES = 4 * GU_WARP_BYTES;    // four epilogue warps: 32 KiB
+constexpr int GU_PREFETCH_CHUNKS = 3;                // chunks asked for in L2 ahead of the chunk being loaded
+constexpr size_t SMEM2_STAGED_BYTES = 1024 + GU_STAGE_BYTES + static_cast<size_t>(STAGES2) * STAGE2_BYTES +
+                                      2 * (STAGED_MAX_EXPERTS + 1) * sizeof(int) + 256 + 64;
+static_assert(SMEM2_STAGED_BYTES <= 227 * 1024, "staged epilogue: shared memory");
+
 // ---- cluster / pair PTX ---------------------------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -121,19 +136,25 @@ struct Shared2 {
     uint64_t* acc_empty;
     uint32_t* tmem_ptr;
     volatile int* abort_flag;
-    uint8_t* peer_stage;  // [PEER_STAGE_BYTES], 16-byte aligned
+    uint8_t* peer_stage;  // [PEER_STAGE_BYTES], 16-byte aligned (null in the staged SwiGLU-backward variant)
+    uint8_t* gu_stage;    // [GU_STAGE_BYTES], 1024-byte aligned (staged SwiGLU-backward variant only)
+    uint64_t* gu_full;    // [4 warps][2 buffers] (staged SwiGLU-backward variant only)
 };
 
+template <bool STAGED = false>
 __device__ __forceinline__ Shared2 carve_smem2(uint8_t* raw) {
     Shared2 s;
     const uint32_t a = smem_u32(raw);
     uint8_t* base = raw + ((1024u - (a & 1023u)) & 1023u);
+    constexpr int TABLE = (STAGED ? STAGED_MAX_EXPERTS : MAX_EXPERTS) + 1;
+    s.gu_stage = STAGED ? base : nullptr;
+    if (STAGED) base += GU_STAGE_BYTES;
     s.stage_base = base;
     uint8_t* p = base + static_cast<size_t>(STAGES2) * STAGE2_BYTES;
     s.tile_prefix = reinterpret_cast<int*>(p);
-    p += (MAX_EXPERTS + 1) * sizeof(int);
+    p += TABLE * sizeof(int);
     s.pair_prefix = reinterpret_cast<int*>(p);
-    p += (MAX_EXPERTS + 1) * sizeof(int);
+    p += TABLE * sizeof(int);
     p = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 7) & ~static_cast<uintptr_t>(7));
     s.full = reinterpret_cast<uint64_t*>(p);
     s.empty = s.full + STAGES2;
@@ -141,8 +162,10 @@ __device__ __forceinline__ Shared2 carve_smem2(uint8_t* raw) {
     s.acc_empty = s.acc_full + 2;
     s.tmem_ptr = reinterpret_cast<uint32_t*>(s.acc_empty + 2);
     s.abort_flag = reinterpret_cast<volatile int*>(s.tmem_ptr + 1);
-    s.peer_stage =
-        reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(s.tmem_ptr + 2) + 15) & ~static_cast<uintptr_t>(15));
+    uint8_t* tail = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(s.tmem_ptr + 2) + 15) &
+                                               ~static_cast<uintptr_t>(15));
+    s.peer_stage = STAGED ? nullptr : tail;
+    s.gu_full = STAGED ? reinterpret_cast<uint64_t*>(tail) : nullptr;
     return s;
 }
 
@@ -158,6 +181,8 @@ __device__ __forceinline__ uint32_t prologue2(const Shared2& s, int warp) {
             mbar_init(&s.acc_full[i], 1);
             mbar_init(&s.acc_empty[i], 2 * epi_warps);  // one arrival per epilogue warp of both CTAs
         }
+        if (s.gu_full)
+            for (int i = 0; i < 8; ++i) mbar_init(&s.gu_full[i], 1);  // lane 0 of the owning warp; bytes of two boxes
         *s.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -217,12 +242,14 @@ __device__ __forceinline__ PairWork decode_pair(const Shared2& s, int E, int n_t
 template <typename T, int WL, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     const __grid_constant__ CUtensorMap tm_gu, const __grid_constant__ CUtensorMap tm_dgu,
                      T* __restrict__ out, int64_t out_stride, T* __restrict__ aux, int64_t aux_stride,
                      const int* __restrict__ row_map, void* const* __restrict__ out_peers, int peer_world,
                      int64_t peer_rows_cap, const int* __restrict__ g_tile_prefix, int E, int kd, int n,
                      uint32_t idesc, uint32_t tune, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    const Shared2 s = carve_smem2(smem_raw);
+    constexpr bool STAGED = (EPI == EPI_DSWIGLU_STAGED);
+    const Shared2 s = carve_smem2<STAGED>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = static_cast<int>(cluster_ctarank());
     const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -330,6 +357,118 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 umma_commit_pair(&s.acc_full[buf]);
             }
         }
+    } else if constexpr (STAGED) {
+        // SwiGLU backward with gate|up and d gate|d up moved by TMA, 32 columns at a time. A thread owns one
+        // accumulator row, so reading gate|up of that row straight from global memory costs a warp 32 rows x 16
+        // bytes per instruction (32 L1 wavefronts, and a DRAM latency per 32-column chunk whenever the L2 prefetch
+        // of a whole tile ahead had been evicted again: 0.76 PFLOP/s where the other GEMMs of the 64-expert layer
+        // reach 1.15-1.37). Here lane 0 of each warp asks the TMA unit for the warp's 32 x 32 gate and up boxes of
+        // the next two chunks (and, in L2, of the chunks behind them) while the warp works on the current one out
+        // of shared memory (64-byte swizzle: a row's four 16-byte pieces sit at piece ^ ((row >> 1) & 3), conflict-free
+        // for one row per lane); the results overwrite the chunk in place and leave by a TMA store.
+        // Four epilogue warps; the activation width is a multiple of 32.
+        const int quarter = warp & 3;
+        uint8_t* wst = s.gu_stage + (warp - 2) * GU_WARP_BYTES;
+        uint64_t* wbar = s.gu_full + (warp - 2) * 2;
+        auto chunk_boxes = [&](bool load, uint32_t qi, int64_t row, int col) {  // lane 0
+            if (load) {
+                uint8_t* dst = wst + (qi & 1u) * GU_BUF_BYTES;
+                mbar_expect_tx(&wbar[qi & 1u], GU_BUF_BYTES);
+                tma_load_2d(dst, &tm_gu, &wbar[qi & 1u], col, static_cast<int>(row));
+                tma_load_2d(dst + GU_HALF_BYTES, &tm_gu, &wbar[qi & 1u], n + col, static_cast<int>(row));
+            } else {
+                tma_prefetch_2d(&tm_gu, col, static_cast<int>(row));
+                tma_prefetch_2d(&tm_gu, n + col, static_cast<int>(row));
+            }
+        };
+        auto chunks_of = [&](const PairWork& t) { return min(BN / GU_BOX_COLS, (n - t.n_tile * BN) / GU_BOX_COLS); };
+        uint32_t q = 0;  // chunks this warp has taken: buffer q & 1, barrier phase (q >> 1) & 1
+        int ahead = 0;   // lane 0: chunks q, q + 1, ... already requested (at most 2: one per buffer)
+        uint32_t lt = 0;
+        for (int64_t w = pair; w < total; w += num_pairs, ++lt) {
+            const PairWork wk = decode_pair(s, E, n_tiles, w, rank);
+            const uint32_t buf = lt & 1u;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            const int64_t row0 = static_cast<int64_t>(wk.m_tile) * BM + quarter * 32;
+            const int n0 = wk.n_tile * BN;
+            const int nch = chunks_of(wk);
+            bool ok = true;
+            if (wk.active) {
+                PairWork nx = wk;
+                bool has_next = w + num_pairs < total;
+                if (has_next) {
+                    nx = decode_pair(s, E, n_tiles, w + num_pairs, rank);
+                    has_next = nx.active;
+                }
+                const int64_t nx_row0 = static_cast<int64_t>(nx.m_tile) * BM + quarter * 32;
+                const int nx_nch = has_next ? chunks_of(nx) : 0;
+                // chunk `cc` of the stream that starts at this tile's chunk 0 and runs on into the next tile
+                auto stream_chunk = [&](bool load, uint32_t qi, int cc) -> bool {
+                    if (cc < nch) chunk_boxes(load, qi, row0, n0 + cc * GU_BOX_COLS);
+                    else if (cc - nch < nx_nch) chunk_boxes(load, qi, nx_row0, nx.n_tile * BN + (cc - nch) * GU_BOX_COLS);
+                    else return false;
+                    return true;
+                };
+                if (lane == 0) {
+                    if (ahead == 0) tma_store_wait_read();  // (both buffers may still feed stores of an earlier tile)
+                    while (ahead < 2 && stream_chunk(true, q + ahead, ahead)) ++ahead;
+                    for (int cc = 2; cc < 2 + GU_PREFETCH_CHUNKS; ++cc) stream_chunk(false, 0u, cc);
+                }
+                ok = mbar_wait_epilogue(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag);
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; ok && c < nch; ++c, ++q) {
+                    ok = mbar_wait(&wbar[q & 1u], (q >> 1) & 1u, s.abort_flag);
+                    if (!ok) break;
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c * 32, v);
+                    uint8_t* bp = wst + (q & 1u) * GU_BUF_BYTES + lane * (GU_BOX_COLS * 2);
+                    const int sw = (lane >> 1) & 3;
+                    uint4 gq[4], uq[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        gq[i] = *reinterpret_cast<const uint4*>(bp + ((i ^ sw) << 4));
+                        uq[i] = *reinterpret_cast<const uint4*>(bp + GU_HALF_BYTES + ((i ^ sw) << 4));
+                    }
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float gg[8], uu[8], dg[8], du[8];
+                        unpack8<T>(gq[i], gg);
+                        unpack8<T>(uq[i], uu);
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            const float d = __uint_as_float(v[8 * i + t]);
+                            const float sg = fast_sigmoid(gg[t]);
+                            dg[t] = d * uu[t] * sg * (1.0f + gg[t] * (1.0f - sg));
+                            du[t] = d * gg[t] * sg;
+                        }
+                        *reinterpret_cast<uint4*>(bp + ((i ^ sw) << 4)) = pack8<T>(dg);
+                        *reinterpret_cast<uint4*>(bp + GU_HALF_BYTES + ((i ^ sw) << 4)) = pack8<T>(du);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint8_t* src = wst + (q & 1u) * GU_BUF_BYTES;
+                        tma_store_2d(&tm_dgu, src, n0 + c * GU_BOX_COLS, static_cast<int>(row0));
+                        tma_store_2d(&tm_dgu, src + GU_HALF_BYTES, n + n0 + c * GU_BOX_COLS, static_cast<int>(row0));
+                        tma_store_commit();
+                        // this buffer takes the chunk after next as soon as the store has read it
+                        --ahead;
+                        tma_store_wait_read();
+                        while (ahead < 2 && stream_chunk(true, q + 1 + ahead, c + 1 + ahead)) ++ahead;
+                        stream_chunk(false, 0u, c + 3 + GU_PREFETCH_CHUNKS - 1);
+                    }
+                }
+            } else {
+                ok = mbar_wait_epilogue(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag);
+            }
+            if (!ok) break;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s.acc_empty[buf]), 0));
+        }
+        if (lane == 0) tma_store_wait_all();
     } else {
         const int quarter = warp & 3;
         const int parts = (static_cast<int>(blockDim.x) - 64) >> 7;
@@ -675,33 +814,53 @@ dw_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 static int pair_grid() { return num_sms() & ~1; }
 
 template <typename K>
-static int set_smem2(K kernel) {
+static int set_smem2(K kernel, size_t bytes = SMEM2_BYTES) {
     apply_epilogue_tuning();
-    return set_dynamic_smem_once(kernel, SMEM2_BYTES);
+    return set_dynamic_smem_once(kernel, bytes);
 }
 
+// `tgu` / `tdgu`: maps over aux / out with 32 x 32 boxes for the staged SwiGLU-backward epilogue (any valid map
+// for the other variants, which do not touch them).
 template <typename T, int WL, int EPI>
-static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb) {
+static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu,
+                        const CUtensorMap& tdgu) {
+    constexpr bool STAGED = (EPI == EPI_DSWIGLU_STAGED);
+    constexpr size_t SMEM = STAGED ? SMEM2_STAGED_BYTES : SMEM2_BYTES;
     auto kernel = rows_gemm_tc2_kernel<T, WL, EPI>;
-    int rc = set_smem2(kernel);
+    int rc = set_smem2(kernel, SMEM);
     if (rc) return rc;
     const uint32_t idesc = make_idesc_mn(g.dtype, false, WL == W_KN, 2 * BM, BN);
-    // (rows bound for other ranks are staged per epilogue warp: always four warps then)
-    const int threads = (EPI == EPI_PLAIN_PEER)
+    // (rows bound for other ranks, and the staged SwiGLU backward, are staged per epilogue warp: always four
+    // warps then)
+    const int threads = (EPI == EPI_PLAIN_PEER || STAGED)
                             ? 64 + 32 * 4
                             : block_threads(4);  // (the SwiGLU-backward epilogue measured 3.6 % faster with 4 warps
                                                  // than with 8 on the dense-expert layer, the others equal)
-    kernel<<<pair_grid(), threads, SMEM2_BYTES, g.stream>>>(
-        ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map, g.out_peers,
-        g.peer_world, g.peer_rows_cap, g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n),
-        idesc, tune_word(), g.device_status);
+    kernel<<<pair_grid(), threads, SMEM, g.stream>>>(
+        ta, tb, tgu, tdgu, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
+        g.out_peers, g.peer_world, g.peer_rows_cap, g.tile_prefix, g.num_experts, static_cast<int>(g.kd),
+        static_cast<int>(g.n), idesc, tune_word(), g.device_status);
     return static_cast<int>(cudaGetLastError());
+}
+
+// Whether the SwiGLU backward of these arguments can take the staged epilogue (and builds its two maps).
+static bool staged_dswiglu_maps(const RowsGemmArgs& g, CUtensorMap* tgu, CUtensorMap* tdgu) {
+    if (g.epilogue != EPI_DSWIGLU || g.w_layout != W_KN || !tuning().dswiglu_staged) return false;
+    if (g.n % GU_BOX_COLS || g.num_experts > STAGED_MAX_EXPERTS) return false;
+    if (g.aux_stride % 8 || g.out_stride % 8 || !is_aligned16(g.aux) || !is_aligned16(g.out)) return false;
+    const uint64_t rows_cap = static_cast<uint64_t>(g.tile_cap) * XMA_ROW_PAD;
+    return cached_map(tgu, g.dtype, g.aux, 2 * g.n, rows_cap, g.aux_stride, 32, GU_BOX_COLS) &&
+           cached_map(tdgu, g.dtype, g.out, 2 * g.n, rows_cap, g.out_stride, 32, GU_BOX_COLS);
 }
 
 template <typename T>
 static int rows_dispatch2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb) {
+    {
+        CUtensorMap tgu, tdgu;
+        if (staged_dswiglu_maps(g, &tgu, &tdgu)) return launch_rows2<T, W_KN, EPI_DSWIGLU_STAGED>(g, ta, tb, tgu, tdgu);
+    }
 #define XMA_ROWS2_CASE(WL, EPI) \
-    if (g.w_layout == WL && g.epilogue == EPI) return launch_rows2<T, WL, EPI>(g, ta, tb)
+    if (g.w_layout == WL && g.epilogue == EPI) return launch_rows2<T, WL, EPI>(g, ta, tb, ta, ta)
     XMA_ROWS2_CASE(W_NK, EPI_PLAIN);
     XMA_ROWS2_CASE(W_NK, EPI_SWIGLU);
     XMA_ROWS2_CASE(W_KN, EPI_PLAIN);

@@ -135,6 +135,24 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, 
                  : "memory");
 }
 
+// Shared memory -> global through a tensor map (bulk group of the issuing thread).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :
+                 : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// The issuing thread's earlier bulk stores have read their shared-memory source / have completed.
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders this thread's shared-memory writes before later accesses of the asynchronous (TMA) proxy.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // One 128-byte line into L2.
 __device__ __forceinline__ void prefetch_l2(const void* p) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
@@ -631,21 +649,22 @@ inline EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Row-major 2-D tensor [outer, inner] of 16-bit elements, box [box_outer, 64], 128-byte swizzle,
-// out-of-range elements read as zero.
+// Row-major 2-D tensor [outer, inner] of 16-bit elements, box [box_outer, box_inner], out-of-range elements
+// read as zero. box_inner = 64 elements (the GEMM operands): 128-byte swizzle; 32 elements (the staged
+// SwiGLU-backward epilogue): 64-byte swizzle.
 inline bool make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-                     uint64_t row_stride_elems, uint32_t box_outer) {
+                     uint64_t row_stride_elems, uint32_t box_outer, uint32_t box_inner = 64) {
     EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
+    if (!fn || (box_inner != 64 && box_inner != 32)) return false;
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {row_stride_elems * 2};
-    const cuuint32_t box[2] = {64, box_outer};
+    const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt =
         (dtype == XMA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    box_inner == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return false;
     // Drivers up to 13.1 mis-handle tensors below 128 KiB unless this descriptor bit is cleared
     // (the same adjustment CUTLASS applies after encoding).
@@ -680,15 +699,15 @@ constexpr uint32_t TUNE_PREFETCH_B = 1u << 17;
 // Tensor-map cache: encoding a map is a driver call per operand per launch; the same (address, shape) pairs
 // come back every step, so the last encodings are kept (mutex-guarded, a few dozen entries, oldest replaced).
 inline bool cached_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-                       uint64_t row_stride_elems, uint32_t box_outer) {
+                       uint64_t row_stride_elems, uint32_t box_outer, uint32_t box_inner = 64) {
     struct Key {
         const void* base;
         uint64_t inner, outer, stride;
-        uint32_t box;
+        uint32_t box, box_inner;
         int dtype;
         bool operator==(const Key& o) const {
             return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride && box == o.box &&
-                   dtype == o.dtype;
+                   box_inner == o.box_inner && dtype == o.dtype;
         }
     };
     struct Entry {
@@ -700,7 +719,7 @@ inline bool cached_map(CUtensorMap* map, int dtype, const void* base, uint64_t i
     static Entry entries[N];
     static int next = 0;
     static std::mutex mu;
-    const Key key{base, inner, outer, row_stride_elems, box_outer, dtype};
+    const Key key{base, inner, outer, row_stride_elems, box_outer, box_inner, dtype};
     {
         std::lock_guard<std::mutex> lock(mu);
         for (int i = 0; i < N; ++i)
@@ -709,7 +728,7 @@ inline bool cached_map(CUtensorMap* map, int dtype, const void* base, uint64_t i
                 return true;
             }
     }
-    if (!make_map(map, dtype, base, inner, outer, row_stride_elems, box_outer)) return false;
+    if (!make_map(map, dtype, base, inner, outer, row_stride_elems, box_outer, box_inner)) return false;
     std::lock_guard<std::mutex> lock(mu);
     entries[next] = Entry{key, *map, true};
     next = (next + 1) % N;
