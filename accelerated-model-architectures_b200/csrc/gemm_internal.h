@@ -22,11 +22,13 @@ enum WeightLayout { W_NK = 0, W_KN = 1 };
 //                 (g, u, g, u, ...) in aux and in the weight rows, as swiglu_packed expects.
 //   EPI_DSWIGLU_STAGED : internal (CTA-pair kernel): EPI_DSWIGLU with gate|up fetched and d gate|d up stored by TMA
 //                    through shared memory, 32 columns at a time
+//   EPI_SWIGLU_STAGED : internal (CTA-pair kernel): EPI_SWIGLU with gate|up and the activation stored by TMA
+//                    through shared memory, 32 columns at a time
 //   EPI_PLAIN_PEER : internal (chosen when out_peers is set): plain store of each row into the buffer of
 //                 the rank that row_map names.
 enum Epilogue {
     EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2, EPI_SWIGLU_PACKED = 3, EPI_DSWIGLU_PACKED = 4, EPI_PLAIN_PEER = 5,
-    EPI_DSWIGLU_STAGED = 6
+    EPI_DSWIGLU_STAGED = 6, EPI_SWIGLU_STAGED = 7
 };
 
 struct RowsGemmArgs {
@@ -82,8 +84,9 @@ struct Tuning {
     int epi_warps = 0;          // 4 or 8 epilogue warps; 0 = per-kernel default
     int plain_pairs = 1;        // automatic choice: CTA pairs also for the plain epilogues of large experts
     int dw_dynamic = 1;         // weight-gradient pair kernel: tiles by atomic ticket, heaviest experts first
-    int dswiglu_staged = 1;     // SwiGLU-backward epilogue of the pair kernel: gate|up and d gate|d up through
-                                // shared memory by TMA (when the shapes allow) instead of row-per-thread accesses
+    int dswiglu_staged = 3;     // SwiGLU epilogues of the pair kernel (bit 0: backward, bit 1: forward): their
+                                // tiles of gate|up, d gate|d up and the activation go through shared memory by
+                                // TMA (when the shapes allow) instead of row-per-thread accesses
 };
 Tuning& tuning();
 uint32_t tune_word();  // the switches the kernels read, packed (see sm100_common.cuh)

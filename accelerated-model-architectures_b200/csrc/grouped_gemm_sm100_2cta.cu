@@ -248,7 +248,8 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                      int64_t peer_rows_cap, const int* __restrict__ g_tile_prefix, int E, int kd, int n,
                      uint32_t idesc, uint32_t tune, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    constexpr bool STAGED = (EPI == EPI_DSWIGLU_STAGED);
+    constexpr bool STAGED = (EPI == EPI_DSWIGLU_STAGED || EPI == EPI_SWIGLU_STAGED);
+    constexpr bool IS_SWIGLU = (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_STAGED);
     const Shared2 s = carve_smem2<STAGED>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = static_cast<int>(cluster_ctarank());
@@ -268,7 +269,7 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 
     constexpr bool B_MN = (WL == W_KN);
     const int half_n = n / 2;
-    const int n_tiles = (EPI == EPI_SWIGLU) ? (half_n + 127) / 128 : (n + BN - 1) / BN;
+    const int n_tiles = IS_SWIGLU ? (half_n + 127) / 128 : (n + BN - 1) / BN;
     const int k_blocks = (kd + BK - 1) / BK;
     const int64_t total = static_cast<int64_t>(s.pair_prefix[E]) * n_tiles;
 
@@ -286,7 +287,7 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 if (!B_MN) {
                     // weight stored [E * n, kd]: this CTA's 128 rows of the 256-row B tile
                     int r0;
-                    if (EPI == EPI_SWIGLU) r0 = wk.e * n + wk.n_tile * 128 + rank * half_n;  // gate | up rows
+                    if (IS_SWIGLU) r0 = wk.e * n + wk.n_tile * 128 + rank * half_n;  // gate | up rows
                     else r0 = wk.e * n + wk.n_tile * BN + rank * 128;
                     if (load) tma_load_2d_pair(sb, &tm_b, full0, kb * BK, r0);
                     else tma_prefetch_2d(&tm_b, kb * BK, r0);
@@ -357,6 +358,72 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 umma_commit_pair(&s.acc_full[buf]);
             }
         }
+    } else if constexpr (EPI == EPI_SWIGLU_STAGED) {
+        // SwiGLU forward with its three outputs (gate and up, rounded to the storage type, and the activation) leaving
+        // by TMA stores: a thread owns an accumulator row, so direct stores are 32 rows x 16 bytes per instruction,
+        // twelve of them per 32 gate columns. The warp writes its 32 x 32 boxes into shared memory instead (64-byte
+        // swizzle, 6 KiB per warp) and lane 0 hands them to the TMA unit; the buffer is reused once that store has
+        // read it, which it has normally done while the next chunk was computed.
+        // Four epilogue warps; the activation width is a multiple of 32.
+        const int quarter = warp & 3;
+        uint8_t* wst = s.gu_stage + (warp - 2) * GU_WARP_BYTES;
+        uint32_t lt = 0;
+        for (int64_t w = pair; w < total; w += num_pairs, ++lt) {
+            const PairWork wk = decode_pair(s, E, n_tiles, w, rank);
+            const uint32_t buf = lt & 1u;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            const int row0 = wk.m_tile * BM + quarter * 32;
+            const int j0 = wk.n_tile * 128;
+            const int nch = min(4, (half_n - j0) / GU_BOX_COLS);
+            if (!mbar_wait_epilogue(&s.acc_full[buf], (lt >> 1) & 1u, s.abort_flag)) break;
+            tc_fence_after();
+            if (wk.active) {
+#pragma unroll 1
+                for (int c = 0; c < nch; ++c) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(taddr + c * 32, g);
+                    tmem_ld32(taddr + 128 + c * 32, u);
+                    tmem_ld_wait();
+                    uint4 qg[4], qu[4], qa[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float gr[8], ur[8], ac[8];
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            gr[t] = round_to<T>(__uint_as_float(g[8 * i + t]));
+                            ur[t] = round_to<T>(__uint_as_float(u[8 * i + t]));
+                            ac[t] = ur[t] * gr[t] * fast_sigmoid(gr[t]);
+                        }
+                        qg[i] = pack8<T>(gr);
+                        qu[i] = pack8<T>(ur);
+                        qa[i] = pack8<T>(ac);
+                    }
+                    if (lane == 0) tma_store_wait_read();  // the previous chunk's store has read the buffer
+                    __syncwarp();
+                    uint8_t* bp = wst + lane * (GU_BOX_COLS * 2);
+                    const int sw = (lane >> 1) & 3;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        *reinterpret_cast<uint4*>(bp + ((i ^ sw) << 4)) = qg[i];
+                        *reinterpret_cast<uint4*>(bp + GU_HALF_BYTES + ((i ^ sw) << 4)) = qu[i];
+                        *reinterpret_cast<uint4*>(bp + 2 * GU_HALF_BYTES + ((i ^ sw) << 4)) = qa[i];
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int col = j0 + c * GU_BOX_COLS;
+                        tma_store_2d(&tm_gu, wst, col, row0);
+                        tma_store_2d(&tm_gu, wst + GU_HALF_BYTES, half_n + col, row0);
+                        tma_store_2d(&tm_dgu, wst + 2 * GU_HALF_BYTES, col, row0);
+                        tma_store_commit();
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s.acc_empty[buf]), 0));
+        }
+        if (lane == 0) tma_store_wait_all();
     } else if constexpr (STAGED) {
         // SwiGLU backward with gate|up and d gate|d up moved by TMA, 32 columns at a time. A thread owns one
         // accumulator row, so reading gate|up of that row straight from global memory costs a warp 32 rows x 16
@@ -824,7 +891,7 @@ static int set_smem2(K kernel, size_t bytes = SMEM2_BYTES) {
 template <typename T, int WL, int EPI>
 static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu,
                         const CUtensorMap& tdgu) {
-    constexpr bool STAGED = (EPI == EPI_DSWIGLU_STAGED);
+    constexpr bool STAGED = (EPI == EPI_DSWIGLU_STAGED || EPI == EPI_SWIGLU_STAGED);
     constexpr size_t SMEM = STAGED ? SMEM2_STAGED_BYTES : SMEM2_BYTES;
     auto kernel = rows_gemm_tc2_kernel<T, WL, EPI>;
     int rc = set_smem2(kernel, SMEM);
@@ -843,9 +910,10 @@ static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUte
     return static_cast<int>(cudaGetLastError());
 }
 
-// Whether the SwiGLU backward of these arguments can take the staged epilogue (and builds its two maps).
+// Whether the SwiGLU backward of these arguments can take the staged epilogue (and builds its two maps: gate|up
+// to read, d gate|d up to write).
 static bool staged_dswiglu_maps(const RowsGemmArgs& g, CUtensorMap* tgu, CUtensorMap* tdgu) {
-    if (g.epilogue != EPI_DSWIGLU || g.w_layout != W_KN || !tuning().dswiglu_staged) return false;
+    if (g.epilogue != EPI_DSWIGLU || g.w_layout != W_KN || !(tuning().dswiglu_staged & 1)) return false;
     if (g.n % GU_BOX_COLS || g.num_experts > STAGED_MAX_EXPERTS) return false;
     if (g.aux_stride % 8 || g.out_stride % 8 || !is_aligned16(g.aux) || !is_aligned16(g.out)) return false;
     const uint64_t rows_cap = static_cast<uint64_t>(g.tile_cap) * XMA_ROW_PAD;
@@ -853,11 +921,27 @@ static bool staged_dswiglu_maps(const RowsGemmArgs& g, CUtensorMap* tgu, CUtenso
            cached_map(tdgu, g.dtype, g.out, 2 * g.n, rows_cap, g.out_stride, 32, GU_BOX_COLS);
 }
 
+// The same for the SwiGLU forward (maps: gate|up [rows, n] and the activation [rows, n / 2], both written).
+static bool staged_swiglu_maps(const RowsGemmArgs& g, CUtensorMap* tgu, CUtensorMap* tact) {
+    if (g.epilogue != EPI_SWIGLU || g.w_layout != W_NK || !(tuning().dswiglu_staged & 2)) return false;
+    // Measured against the GEMM of equal work beside it: with a 2048-deep reduction the staged stores make the up
+    // projection 7 % faster (the epilogue is then as long as the main loop of a tile); with 4096 they cost 0-5 %
+    // (the epilogue hides behind the main loop anyway and its TMA stores queue with the operand loads). Bit 2 of
+    // the switch forces the staged stores for any depth.
+    if (g.kd >= 4096 && !(tuning().dswiglu_staged & 4)) return false;
+    if ((g.n / 2) % GU_BOX_COLS || g.num_experts > STAGED_MAX_EXPERTS) return false;
+    if (g.aux_stride % 8 || g.out_stride % 8 || !is_aligned16(g.aux) || !is_aligned16(g.out)) return false;
+    const uint64_t rows_cap = static_cast<uint64_t>(g.tile_cap) * XMA_ROW_PAD;
+    return cached_map(tgu, g.dtype, g.aux, g.n, rows_cap, g.aux_stride, 32, GU_BOX_COLS) &&
+           cached_map(tact, g.dtype, g.out, g.n / 2, rows_cap, g.out_stride, 32, GU_BOX_COLS);
+}
+
 template <typename T>
 static int rows_dispatch2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb) {
     {
         CUtensorMap tgu, tdgu;
         if (staged_dswiglu_maps(g, &tgu, &tdgu)) return launch_rows2<T, W_KN, EPI_DSWIGLU_STAGED>(g, ta, tb, tgu, tdgu);
+        if (staged_swiglu_maps(g, &tgu, &tdgu)) return launch_rows2<T, W_NK, EPI_SWIGLU_STAGED>(g, ta, tb, tgu, tdgu);
     }
 #define XMA_ROWS2_CASE(WL, EPI) \
     if (g.w_layout == WL && g.epilogue == EPI) return launch_rows2<T, WL, EPI>(g, ta, tb, ta, ta)

@@ -210,9 +210,10 @@ int xma_b200_grouped_gemm_choice(int kind, int dtype, int num_experts, int64_t t
  * default, 4, 8); key 4: CTA pairs also for plain epilogues in the automatic choice (0/1, default 1);
  * key 5: the CTA-pair weight-gradient kernel hands its tiles out by an atomic ticket, heaviest experts first,
  * instead of a fixed stride (0/1, default 1);
- * key 6: the CTA-pair SwiGLU-backward epilogue moves gate|up and d gate|d up through shared memory by TMA, 32
- * columns at a time, when the activation width is a multiple of 32 and there are at most 192 experts (1, the
- * default), or reads and writes them with one row per thread (0).
+ * key 6: the SwiGLU epilogues of the CTA-pair kernel move their tiles through shared memory by TMA, 32 columns at a
+ * time, instead of reading and writing them with one row per thread, when the activation width is a multiple of 32
+ * and there are at most 192 experts: bit 0 = backward (gate|up read, d gate|d up written), bit 1 = forward
+ * (gate|up and the activation written; only for reductions shorter than 4096 unless bit 2 is set); default 3.
  * The environment variables XMA_B200_GU_PREFETCH, XMA_B200_TMA_PREFETCH, XMA_B200_TMA_PREFETCH_MASK,
  * XMA_B200_EPI_WARPS, XMA_B200_PLAIN_PAIRS, XMA_B200_DW_DYNAMIC and XMA_B200_DSWIGLU_STAGED set the initial values.
  * Stands where the reference has its autotune configurations (scatter_kernel.py:12-52). */

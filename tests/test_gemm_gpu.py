@@ -209,6 +209,49 @@ def test_dw_gemm_ticket_order_matches_fixed_stride():
         assert_close_rel(out[1][e].cpu(), exp, REL_TOL[dtype], f"dW[{e}]")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("counts,kd,inter", [([700, 0, 100, 1], 512, 1024), ([4097, 2049], 4096, 96),
+                                             ([300, 129], 192, 288)])
+def test_staged_swiglu_epilogues_match_row_per_thread_epilogues(dtype, counts, kd, inter):
+    """The CTA-pair kernel moves the tiles of its SwiGLU epilogues through shared memory by TMA (activation width a
+    multiple of 32); the arithmetic is that of the epilogues that read and write one row per thread, so the results
+    are the same bit for bit - forward (gate|up and activation), backward into a separate buffer and backward in
+    place over gate|up. Switch values: 0 = one row per thread, 7 = staged, the forward also for long reductions."""
+    from xma import _lib, ops
+
+    E, R = len(counts), int(sum(counts))
+    plan, _ = _plan(counts, E)
+    used = int(plan.pad_offsets[-1])
+    a, _ = _grouped(plan, R, kd, dtype, seed=3)
+    dys, _ = _grouped(plan, R, kd, dtype, seed=5)
+    rng = np.random.RandomState(4)
+    w1 = torch.from_numpy((rng.standard_normal((E, 2 * inter, kd)) * 0.05).astype(np.float32)).to(dtype).cuda()
+    w2 = torch.from_numpy((rng.standard_normal((E, kd, inter)) * 0.05).astype(np.float32)).to(dtype).cuda()
+    got = {}
+    for staged in (7, 0):
+        previous = _lib.lib.xma_b200_tuning_set(_lib.TUNE_DSWIGLU_STAGED, staged)
+        try:
+            gu = torch.full((plan.row_cap, 2 * inter), float("nan"), dtype=dtype, device="cuda")
+            act = torch.full((plan.row_cap, inter), float("nan"), dtype=dtype, device="cuda")
+            ops.grouped_gemm_rows_(a, w1, _lib.W_NK, act, gu, None, plan.tile_expert, plan.tile_prefix, kd, 2 * inter,
+                                   _lib.EPI_SWIGLU, TC_PAIR)
+            dgu = torch.full((plan.row_cap, 2 * inter), float("nan"), dtype=dtype, device="cuda")
+            ops.grouped_gemm_rows_(dys, w2, _lib.W_KN, dgu, gu, None, plan.tile_expert, plan.tile_prefix, kd, inter,
+                                   _lib.EPI_DSWIGLU, TC_PAIR)
+            in_place = gu.clone()
+            ops.grouped_gemm_rows_(dys, w2, _lib.W_KN, in_place, in_place, None, plan.tile_expert, plan.tile_prefix,
+                                   kd, inter, _lib.EPI_DSWIGLU, TC_PAIR)
+            torch.cuda.synchronize()
+        finally:
+            _lib.lib.xma_b200_tuning_set(_lib.TUNE_DSWIGLU_STAGED, previous)
+        assert _lib.read_and_clear_device_status() == 0
+        got[staged] = (gu[:used], act[:used], dgu[:used], in_place[:used])
+    for x, y, what in zip(got[7], got[0], ("gate|up", "activation", "d gate|d up", "d gate|d up in place")):
+        assert torch.isfinite(x.float()).all(), what
+        assert torch.equal(x, y), what
+    assert torch.equal(got[7][2], got[7][3])
+
+
 @pytest.mark.parametrize("impl,dtype", [pytest.param(TC, torch.bfloat16, id="tcgen05-bf16"),
                                         pytest.param(TC_PAIR, torch.bfloat16, id="pair-bf16"),
                                         pytest.param(TC_PAIR, torch.float16, id="pair-f16")])
