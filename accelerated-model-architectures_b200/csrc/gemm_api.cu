@@ -25,6 +25,7 @@ Tuning& tuning() {
         env("XMA_B200_PLAIN_PAIRS", t.plain_pairs);
         env("XMA_B200_DW_DYNAMIC", t.dw_dynamic);
         env("XMA_B200_DSWIGLU_STAGED", t.dswiglu_staged);
+        env("XMA_B200_ODD_TAIL", t.odd_tail);
     });
     return t;
 }
@@ -120,7 +121,22 @@ int xma_b200_grouped_gemm_rows_peer(const void* a, int64_t a_row_stride, const v
     if (impl == 3) return xma::rows_gemm_tc2(g);
     if (impl != 0) return XMA_ERR_BAD_SHAPE;
     switch (xma::choose_rows_impl(g)) {
-        case 3: return xma::rows_gemm_tc2(g);
+        case 3: {
+            // An expert with an odd number of 128-row tiles costs the pair kernel a whole 256-row tile for its last
+            // 128 rows. The pairs can go to the pair kernel and the odd last tiles to the one-CTA kernel behind it
+            // (which ends at once when there are none); that second launch reads every odd expert's weights once
+            // more for 128 rows, so it pays only with few, large experts. Measured on B200, whole layer, switch
+            // on against off: 8 experts of about 4100 rows -1.3 % (28.7 against 29.1 ms), 128 experts of about
+            // 1024 rows no difference, 64 experts with a Zipf load +2.5 %. Hence: up to 16 experts (switch 1);
+            // switch 2 splits for any number of experts.
+            const int split = xma::tuning().odd_tail;
+            if (out_peers || split == 0 || (split == 1 && g.num_experts > 16)) return xma::rows_gemm_tc2(g);
+            g.tune_extra = xma::tc::TUNE_WHOLE_PAIRS_ONLY;
+            rc = xma::rows_gemm_tc2(g);
+            if (rc) return rc;
+            g.tune_extra = xma::tc::TUNE_ODD_LAST_TILE_ONLY;
+            return xma::rows_gemm_tc(g);
+        }
         case 2: return xma::rows_gemm_tc(g);
         default: return xma::rows_gemm_simt(g);
     }
@@ -228,6 +244,7 @@ int xma_b200_tuning_set(int key, int value) {
         case 4: field = &t.plain_pairs; break;
         case 5: field = &t.dw_dynamic; break;
         case 6: field = &t.dswiglu_staged; break;
+        case 7: field = &t.odd_tail; break;
         default: return XMA_ERR_BAD_SHAPE;
     }
     const int previous = *field;

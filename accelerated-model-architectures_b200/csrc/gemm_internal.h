@@ -56,6 +56,7 @@ struct RowsGemmArgs {
     int dtype;
     int* device_status;
     cudaStream_t stream;
+    uint32_t tune_extra = 0;   // per-launch bits OR-ed into the tuning word (TUNE_WHOLE_PAIRS_ONLY, ...)
 };
 
 struct DwGemmArgs {
@@ -87,8 +88,20 @@ struct Tuning {
     int dswiglu_staged = 3;     // SwiGLU epilogues of the pair kernel (bit 0: backward, bit 1: forward): their
                                 // tiles of gate|up, d gate|d up and the activation go through shared memory by
                                 // TMA (when the shapes allow) instead of row-per-thread accesses
+    int odd_tail = 1;           // automatic choice: the CTA-pair kernel leaves the odd last 128-row tile of an
+                                // expert to a second launch of the one-CTA kernel instead of computing a pair
+                                // tile whose second half is empty (1: with up to 16 experts, 2: always, 0: never)
 };
 Tuning& tuning();
+
+namespace tc {
+// Per-launch bits (set by the launcher, not by the tuning switches): the automatic choice may split one rows GEMM
+// over two launches, the CTA-pair kernel on the whole pairs of 128-row tiles of every expert and the one-CTA kernel
+// on the last tile of the experts that have an odd number of them.
+constexpr uint32_t TUNE_WHOLE_PAIRS_ONLY = 1u << 21;
+constexpr uint32_t TUNE_ODD_LAST_TILE_ONLY = 1u << 22;
+}  // namespace tc
+
 uint32_t tune_word();  // the switches the kernels read, packed (see sm100_common.cuh)
 
 // Which kernel family the automatic choice (impl = 0) takes: 1 CUDA cores, 2 tcgen05 one CTA per tile,

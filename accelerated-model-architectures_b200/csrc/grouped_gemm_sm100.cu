@@ -24,6 +24,8 @@ namespace tc {
 struct Shared {
     uint8_t* stage_base;  // 1024-byte aligned
     int* tile_prefix;     // [E + 1]
+    int* odd_prefix;      // [E + 1] experts with an odd number of row tiles in front of each expert (rows GEMM,
+                          // odd-last-tile launches only)
     uint64_t* full;       // [STAGES]
     uint64_t* empty;      // [STAGES]
     uint64_t* acc_full;   // [2]
@@ -40,6 +42,8 @@ __device__ __forceinline__ Shared carve_smem(uint8_t* raw) {
     s.stage_base = base;
     uint8_t* p = base + static_cast<size_t>(STAGES) * STAGE_BYTES;
     s.tile_prefix = reinterpret_cast<int*>(p);
+    p += (MAX_EXPERTS + 1) * sizeof(int);
+    s.odd_prefix = reinterpret_cast<int*>(p);
     p += (MAX_EXPERTS + 1) * sizeof(int);
     p = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 7) & ~static_cast<uintptr_t>(7));
     s.full = reinterpret_cast<uint64_t*>(p);
@@ -129,6 +133,23 @@ __device__ __forceinline__ RowsWork decode_rows(const int* tile_prefix, int E, i
     return r;
 }
 
+// The work items of a launch that takes only the last row tile of every expert with an odd number of them (the
+// whole pairs of tiles went to the CTA-pair kernel): expert-major, all column tiles of that one row tile.
+__device__ __forceinline__ RowsWork decode_odd_rows(const int* tile_prefix, const int* odd_prefix, int E, int n_tiles,
+                                                    int64_t w) {
+    int lo = 0, hi = E;  // invariant: odd_prefix[lo] * n_tiles <= w < odd_prefix[hi] * n_tiles
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (static_cast<int64_t>(odd_prefix[mid]) * n_tiles <= w) lo = mid;
+        else hi = mid;
+    }
+    RowsWork r;
+    r.e = lo;
+    r.n_tile = static_cast<int>(w - static_cast<int64_t>(odd_prefix[lo]) * n_tiles);
+    r.m_tile = tile_prefix[lo + 1] - 1;
+    return r;
+}
+
 template <typename T, int WL, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -141,19 +162,36 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     for (int i = threadIdx.x; i <= E; i += blockDim.x) s.tile_prefix[i] = g_tile_prefix[i];
+    const bool odd_only = (tune & TUNE_ODD_LAST_TILE_ONLY) != 0;
+    if (odd_only) {
+        __syncthreads();
+        if (threadIdx.x == 32) {
+            int run = 0;
+            for (int e = 0; e < E; ++e) {
+                s.odd_prefix[e] = run;
+                run += (s.tile_prefix[e + 1] - s.tile_prefix[e]) & 1;
+            }
+            s.odd_prefix[E] = run;
+        }
+    }
     const uint32_t tmem_base = prologue(s, warp, lane);
 
     constexpr bool B_MN = (WL == W_KN);
     const int half_n = n / 2;  // SwiGLU: width of the activation
     const int n_tiles = (EPI == EPI_SWIGLU) ? (half_n + 127) / 128 : (n + BN - 1) / BN;
     const int k_blocks = (kd + BK - 1) / BK;
-    const int64_t total = static_cast<int64_t>(s.tile_prefix[E] - s.tile_prefix[0]) * n_tiles;
+    const int64_t total =
+        static_cast<int64_t>(odd_only ? s.odd_prefix[E] : s.tile_prefix[E] - s.tile_prefix[0]) * n_tiles;
+    auto decode = [&](int64_t w) {
+        return odd_only ? decode_odd_rows(s.tile_prefix, s.odd_prefix, E, n_tiles, w)
+                        : decode_rows(s.tile_prefix, E, n_tiles, w);
+    };
 
     if (warp == 0) {
         if (lane == 0) {
             uint32_t it = 0;
             for (int64_t w = blockIdx.x; w < total; w += gridDim.x) {
-                const RowsWork wk = decode_rows(s.tile_prefix, E, n_tiles, w);
+                const RowsWork wk = decode(w);
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
                     const int st = it % STAGES;
@@ -218,13 +256,13 @@ rows_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         uint8_t* peer_stage = (parts == 1) ? s.peer_stage + (warp - 2) * PEER_STAGE_WARP_BYTES : nullptr;
         uint32_t lt = 0;
         for (int64_t w = blockIdx.x; w < total; w += gridDim.x, ++lt) {
-            const RowsWork wk = decode_rows(s.tile_prefix, E, n_tiles, w);
+            const RowsWork wk = decode(w);
             const uint32_t buf = lt & 1u;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const int64_t r = static_cast<int64_t>(wk.m_tile) * BM + row_in_tile;
             if ((EPI == EPI_DSWIGLU || EPI == EPI_DSWIGLU_PACKED) && (tune & TUNE_GU_PREFETCH) &&
                 w + gridDim.x < total) {
-                const RowsWork nx = decode_rows(s.tile_prefix, E, n_tiles, w + gridDim.x);
+                const RowsWork nx = decode(w + gridDim.x);
                 prefetch_gate_up<T, EPI>(aux, aux_stride, static_cast<int64_t>(nx.m_tile) * BM + row_in_tile,
                                          nx.n_tile, n, part, chunks);
             }
@@ -378,7 +416,7 @@ static int launch_rows(const RowsGemmArgs& g, const CUtensorMap& ta, const CUten
     kernel<<<num_sms(), threads, SMEM_BYTES, g.stream>>>(
         ta, tb, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map, g.out_peers,
         g.peer_world, g.peer_rows_cap, g.tile_prefix, g.num_experts, static_cast<int>(g.kd), static_cast<int>(g.n),
-        idesc, tune_word(), g.device_status);
+        idesc, tune_word() | g.tune_extra, g.device_status);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -259,9 +259,10 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     __syncthreads();
     if (threadIdx.x == 32) {
         int run = 0;
+        const int round_up = (tune & TUNE_WHOLE_PAIRS_ONLY) ? 0 : 1;  // an odd last tile: half a pair, or left out
         for (int e = 0; e < E; ++e) {
             s.pair_prefix[e] = run;
-            run += (s.tile_prefix[e + 1] - s.tile_prefix[e] + 1) >> 1;
+            run += (s.tile_prefix[e + 1] - s.tile_prefix[e] + round_up) >> 1;
         }
         s.pair_prefix[E] = run;
     }
@@ -906,7 +907,7 @@ static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUte
     kernel<<<pair_grid(), threads, SMEM, g.stream>>>(
         ta, tb, tgu, tdgu, static_cast<T*>(g.out), g.out_stride, static_cast<T*>(g.aux), g.aux_stride, g.row_map,
         g.out_peers, g.peer_world, g.peer_rows_cap, g.tile_prefix, g.num_experts, static_cast<int>(g.kd),
-        static_cast<int>(g.n), idesc, tune_word(), g.device_status);
+        static_cast<int>(g.n), idesc, tune_word() | g.tune_extra, g.device_status);
     return static_cast<int>(cudaGetLastError());
 }
 

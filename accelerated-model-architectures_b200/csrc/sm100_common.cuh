@@ -32,7 +32,8 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64 x 64 box of an MN-major oper
 constexpr int PEER_STAGE_WARP_BYTES = 32 * 128;
 constexpr int PEER_STAGE_BYTES = 4 * PEER_STAGE_WARP_BYTES;
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + static_cast<size_t>(STAGES) * STAGE_BYTES +
-                              (MAX_EXPERTS + 1) * sizeof(int) + 256 /*barriers*/ + PEER_STAGE_BYTES;
+                              2 * (MAX_EXPERTS + 1) * sizeof(int) /*tile tables*/ + 256 /*barriers*/ +
+                              PEER_STAGE_BYTES;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------

@@ -23,7 +23,7 @@ IMPL_AUTO, IMPL_SIMT, IMPL_TC, IMPL_TC_PAIR = 0, 1, 2, 3
 DEV_ID_OUT_OF_RANGE, DEV_WAIT_TIMEOUT, DEV_BAD_TILE = 1, 2, 4
 ABI_VERSION = 3
 TUNE_GU_PREFETCH, TUNE_TMA_PREFETCH, TUNE_TMA_PREFETCH_MASK, TUNE_EPI_WARPS, TUNE_PLAIN_PAIRS, TUNE_DW_DYNAMIC = 0, 1, 2, 3, 4, 5
-TUNE_DSWIGLU_STAGED = 6
+TUNE_DSWIGLU_STAGED, TUNE_ODD_TAIL = 6, 7
 
 _DTYPE_CODES = {
     torch.float32: F32,

@@ -433,11 +433,13 @@ class KernelStats:
 STATS = KernelStats()
 
 
-def _wrap(op, name: str, kernels: int):
+def _wrap(op, name: str, kernels):
+    """`kernels`: how many kernels one call launches (an int, or a function of the call's arguments)."""
+
     def call(*args, tag: str | None = None):
         if not STATS.enabled:
             return op(*args)
-        STATS.launches += kernels
+        STATS.launches += kernels(*args) if callable(kernels) else kernels
         if not STATS.timing:
             return op(*args)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -459,7 +461,20 @@ gather_rows_ = _wrap(_gather_rows_op, "gather_rows", 1)
 spread_rows_ = _wrap(_spread_rows_op, "spread_rows", 1)
 combine_rows_ = _wrap(_combine_rows_op, "combine_rows", 1)
 combine_bwd_ = _wrap(_combine_bwd_op, "combine_bwd", 1)
-grouped_gemm_rows_ = _wrap(_grouped_gemm_rows_op, "grouped_gemm_rows", 1)
+def _rows_gemm_kernels(a, w, w_layout, out, aux, row_map, tile_expert, tile_prefix, kd, n, epilogue, impl,
+                       out_peers=None, peer_rows_cap=0) -> int:
+    """The automatic choice runs a rows GEMM of large experts as two launches: the CTA-pair kernel on the whole
+    pairs of 128-row tiles and the one-CTA kernel on the odd last tiles (with up to 16 experts; not when the rows go
+    to other ranks; XMA_B200_ODD_TAIL = 0 never, 2 for any number of experts)."""
+    split = os.environ.get("XMA_B200_ODD_TAIL", "1")
+    if impl != _lib.IMPL_AUTO or out_peers is not None or split == "0" or (split == "1" and w.size(0) > 16):
+        return 1
+    choice = lib.xma_b200_grouped_gemm_choice(0, dtype_code(a.dtype), w.size(0), tile_expert.numel(), kd, n, w_layout,
+                                              epilogue, 0)
+    return 2 if choice == _lib.IMPL_TC_PAIR else 1
+
+
+grouped_gemm_rows_ = _wrap(_grouped_gemm_rows_op, "grouped_gemm_rows", _rows_gemm_kernels)
 grouped_gemm_dw_ = _wrap(_grouped_gemm_dw_op, "grouped_gemm_dw", 1)
 ep_plan_ = _wrap(_ep_plan_op, "ep_plan", 1)
 ep_dispatch_ = _wrap(_ep_dispatch_op, "ep_dispatch", 1)

@@ -214,8 +214,14 @@ int xma_b200_grouped_gemm_choice(int kind, int dtype, int num_experts, int64_t t
  * time, instead of reading and writing them with one row per thread, when the activation width is a multiple of 32
  * and there are at most 192 experts: bit 0 = backward (gate|up read, d gate|d up written), bit 1 = forward
  * (gate|up and the activation written; only for reductions shorter than 4096 unless bit 2 is set); default 3.
+ * key 7: with the automatic choice (impl 0) a rows GEMM of large experts runs as two launches, the CTA-pair kernel
+ * on the whole pairs of 128-row tiles of every expert and the one-CTA kernel on the last tile of the experts that
+ * have an odd number of them (1, the default: with up to 16 experts, where it was measured to pay; 2: with any
+ * number), or as one launch of the CTA-pair kernel, which then computes a 256-row tile for an odd last tile (0);
+ * rows stored into other ranks' buffers always take one launch.
  * The environment variables XMA_B200_GU_PREFETCH, XMA_B200_TMA_PREFETCH, XMA_B200_TMA_PREFETCH_MASK,
- * XMA_B200_EPI_WARPS, XMA_B200_PLAIN_PAIRS, XMA_B200_DW_DYNAMIC and XMA_B200_DSWIGLU_STAGED set the initial values.
+ * XMA_B200_EPI_WARPS, XMA_B200_PLAIN_PAIRS, XMA_B200_DW_DYNAMIC, XMA_B200_DSWIGLU_STAGED and XMA_B200_ODD_TAIL set
+ * the initial values.
  * Stands where the reference has its autotune configurations (scatter_kernel.py:12-52). */
 int xma_b200_tuning_set(int key, int value);
 

@@ -209,6 +209,55 @@ def test_dw_gemm_ticket_order_matches_fixed_stride():
         assert_close_rel(out[1][e].cpu(), exp, REL_TOL[dtype], f"dW[{e}]")
 
 
+@pytest.mark.parametrize("counts,kd,inter", [([1100, 1025, 1280, 2049, 1024, 1153], 256, 320),
+                                             ([4097, 4096, 0, 4225], 192, 128)])
+def test_automatic_choice_splits_odd_last_tiles_off(counts, kd, inter):
+    """With experts of eight and more 128-row tiles the automatic choice takes the CTA-pair kernel; an expert with an
+    odd number of tiles then has its last tile computed by the one-CTA kernel in a second launch instead of as half
+    of a 256-row pair tile. Same arithmetic per output element: every epilogue gives the bits of the single launch."""
+    from xma import _lib, ops
+
+    dtype = torch.bfloat16
+    E, R = len(counts), int(sum(counts))
+    plan, _ = _plan(counts, E)
+    used = int(plan.pad_offsets[-1])
+    assert any(((c + 127) // 128) % 2 for c in counts)
+    assert _lib.lib.xma_b200_grouped_gemm_choice(0, _lib.BF16, E, plan.tile_expert.numel(), kd, 2 * inter, _lib.W_NK,
+                                                 _lib.EPI_SWIGLU, 0) == TC_PAIR
+    a, _ = _grouped(plan, R, kd, dtype, seed=3)
+    dys, _ = _grouped(plan, R, kd, dtype, seed=5)
+    rng = np.random.RandomState(4)
+    mk = lambda *s: torch.from_numpy((rng.standard_normal(s) * 0.05).astype(np.float32)).to(dtype).cuda()
+    w1, w2, wp = mk(E, 2 * inter, kd), mk(E, kd, inter), mk(E, inter, kd)
+    got = {}
+    for split in (2, 0):
+        previous = _lib.lib.xma_b200_tuning_set(_lib.TUNE_ODD_TAIL, split)
+        try:
+            nan = lambda width: torch.full((plan.row_cap, width), float("nan"), dtype=dtype, device="cuda")
+            gu, act, dgu, plain, scattered = nan(2 * inter), nan(inter), nan(2 * inter), nan(inter), nan(inter)
+            ops.grouped_gemm_rows_(a, w1, _lib.W_NK, act, gu, None, plan.tile_expert, plan.tile_prefix, kd, 2 * inter,
+                                   _lib.EPI_SWIGLU, 0)
+            ops.grouped_gemm_rows_(dys, w2, _lib.W_KN, dgu, gu, None, plan.tile_expert, plan.tile_prefix, kd, inter,
+                                   _lib.EPI_DSWIGLU, 0)
+            ops.grouped_gemm_rows_(a, wp, _lib.W_NK, plain, None, None, plan.tile_expert, plan.tile_prefix, kd, inter,
+                                   _lib.EPI_PLAIN, 0)
+            ops.grouped_gemm_rows_(a, wp, _lib.W_NK, scattered, None, plan.row_src, plan.tile_expert,
+                                   plan.tile_prefix, kd, inter, _lib.EPI_PLAIN, 0)
+            torch.cuda.synchronize()
+        finally:
+            _lib.lib.xma_b200_tuning_set(_lib.TUNE_ODD_TAIL, previous)
+        assert _lib.read_and_clear_device_status() == 0
+        got[split] = (gu[:used], act[:used], dgu[:used], plain[:used], scattered[:R])
+    for x, y, what in zip(got[2], got[0], ("gate|up", "activation", "d gate|d up", "plain", "scattered")):
+        assert torch.isfinite(x.float()).all(), what
+        assert torch.equal(x, y), what
+    pad = plan.pad_offsets.cpu().tolist()
+    e = max(range(E), key=lambda i: counts[i] % 256 if ((counts[i] + 127) // 128) % 2 else -1)  # an odd expert
+    r0, c = pad[e], counts[e]
+    exp = a[r0 : r0 + c].double().cpu() @ wp[e].double().cpu().t()
+    assert_close_rel(got[2][3][r0 : r0 + c].cpu(), exp, REL_TOL[dtype], "plain, rows of an odd expert")
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("counts,kd,inter", [([700, 0, 100, 1], 512, 1024), ([4097, 2049], 4096, 96),
                                              ([300, 129], 192, 288)])
