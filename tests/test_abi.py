@@ -54,6 +54,38 @@ def test_host_side_argument_errors_need_no_gpu():
     assert "dtype" in _lib.error_string(-2)
 
 
+def test_later_entry_points_reject_bad_arguments_without_a_gpu():
+    """pack / unpack_sequence, fused_residual_add_rmsnorm and the load-balancing loss: shape and pointer errors are
+    answered on the host, and an empty problem is a successful no-op."""
+    from xma import _lib
+
+    lib = _lib.lib
+    NULL, DTYPE, SHAPE = -1, -2, -3
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    for fn in (lib.xma_b200_pack_sequence, lib.xma_b200_unpack_sequence):
+        assert fn(p, p, p, _lib.I32, -1, 4, 8, 16, 1, None, None) == SHAPE
+        assert fn(p, p, p, _lib.I32, 0, 4, 8, 16, 1, None, None) == 0       # no sequences
+        assert fn(p, p, p, _lib.I32, 2, 4, 8, 0, 1, None, None) == 0        # empty rows
+        assert fn(p, p, None, _lib.I32, 2, 4, 8, 16, 1, None, None) == NULL  # no offsets
+        assert fn(p, None, p, _lib.I32, 2, 4, 8, 16, 1, None, None) == NULL  # no destination
+        assert fn(p, p, p, _lib.F32, 2, 4, 8, 16, 1, None, None) == DTYPE    # offsets must be int32 / int64
+    assert lib.xma_b200_pack_sequence(p, None, p, _lib.I32, 2, 4, 0, 16, 1, None, None) == 0  # nothing to write
+    # rmsnorm: empty problems, missing tensors, a residual without the output for the updated stream
+    f = ctypes.c_float
+    assert lib.xma_b200_rmsnorm_fwd(p, 8, None, 0, None, p, 8, None, 0, None, _lib.BF16, 0, 8, f(1e-5), f(1.0), None) == 0
+    assert lib.xma_b200_rmsnorm_fwd(None, 8, None, 0, None, p, 8, None, 0, None, _lib.BF16, 4, 8, f(1e-5), f(1.0), None) == NULL
+    assert lib.xma_b200_rmsnorm_fwd(p, 8, p, 8, None, p, 8, None, 0, None, _lib.BF16, 4, 8, f(1e-5), f(1.0), None) == NULL
+    assert lib.xma_b200_rmsnorm_fwd(p, 8, None, 0, None, p, 8, None, 0, None, _lib.I32, 4, 8, f(1e-5), f(1.0), None) == DTYPE
+    assert lib.xma_b200_rmsnorm_bwd(p, 8, None, p, 8, None, 0, None, p, 8, None, 0, p, 0, _lib.BF16, 4, 8, f(1e-5), f(1.0), None) == SHAPE
+    assert lib.xma_b200_rmsnorm_bwd_partial_rows(10) == 10 and lib.xma_b200_rmsnorm_bwd_partial_rows(10 ** 9) >= 148
+    # load-balancing loss: more than 1024 experts, a row stride shorter than a row, no logits
+    assert lib.xma_b200_router_prob_sums(p, _lib.BF16, 8, 4, 2000, ctypes.cast(buf, ctypes.POINTER(f)), 4, None) == SHAPE
+    assert lib.xma_b200_router_prob_sums(p, _lib.BF16, 4, 4, 8, ctypes.cast(buf, ctypes.POINTER(f)), 4, None) == SHAPE
+    assert lib.xma_b200_load_balancing_loss_bwd(None, _lib.BF16, 8, 4, 8, None, None, None) == NULL
+    assert lib.xma_b200_load_balancing_loss_bwd(None, _lib.BF16, 8, 0, 8, None, None, None) == 0
+
+
 def test_expert_parallel_entry_points_reject_bad_arguments_without_a_gpu():
     from xma._lib import lib
 
