@@ -22,13 +22,14 @@ enum WeightLayout { W_NK = 0, W_KN = 1 };
 //                 (g, u, g, u, ...) in aux and in the weight rows, as swiglu_packed expects.
 //   EPI_DSWIGLU_STAGED : internal (CTA-pair kernel): EPI_DSWIGLU with gate|up fetched and d gate|d up stored by TMA
 //                    through shared memory, 32 columns at a time
+//   EPI_DSWIGLU_PACKED_STAGED : internal (CTA-pair kernel): the same for the interleaved layout (one 32 x 64 box)
 //   EPI_SWIGLU_STAGED : internal (CTA-pair kernel): EPI_SWIGLU with gate|up and the activation stored by TMA
 //                    through shared memory, 32 columns at a time
 //   EPI_PLAIN_PEER : internal (chosen when out_peers is set): plain store of each row into the buffer of
 //                 the rank that row_map names.
 enum Epilogue {
     EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_DSWIGLU = 2, EPI_SWIGLU_PACKED = 3, EPI_DSWIGLU_PACKED = 4, EPI_PLAIN_PEER = 5,
-    EPI_DSWIGLU_STAGED = 6, EPI_SWIGLU_STAGED = 7
+    EPI_DSWIGLU_STAGED = 6, EPI_SWIGLU_STAGED = 7, EPI_DSWIGLU_PACKED_STAGED = 8
 };
 
 struct RowsGemmArgs {

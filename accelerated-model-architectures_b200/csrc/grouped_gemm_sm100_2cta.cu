@@ -248,7 +248,8 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                      int64_t peer_rows_cap, const int* __restrict__ g_tile_prefix, int E, int kd, int n,
                      uint32_t idesc, uint32_t tune, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    constexpr bool STAGED = (EPI == EPI_DSWIGLU_STAGED || EPI == EPI_SWIGLU_STAGED);
+    constexpr bool STAGED =
+        (EPI == EPI_DSWIGLU_STAGED || EPI == EPI_SWIGLU_STAGED || EPI == EPI_DSWIGLU_PACKED_STAGED);
     constexpr bool IS_SWIGLU = (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_STAGED);
     const Shared2 s = carve_smem2<STAGED>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -438,12 +439,21 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         const int quarter = warp & 3;
         uint8_t* wst = s.gu_stage + (warp - 2) * GU_WARP_BYTES;
         uint64_t* wbar = s.gu_full + (warp - 2) * 2;
+        // Interleaved layout (gate, up, gate, up, ... along the columns): the 32 activation columns of a chunk are
+        // one box of 64 columns (128-byte swizzle: a row's eight 16-byte pieces sit at piece ^ (row & 7)).
+        constexpr bool PACKED = (EPI == EPI_DSWIGLU_PACKED_STAGED);
         auto chunk_boxes = [&](bool load, uint32_t qi, int64_t row, int col) {  // lane 0
             if (load) {
                 uint8_t* dst = wst + (qi & 1u) * GU_BUF_BYTES;
                 mbar_expect_tx(&wbar[qi & 1u], GU_BUF_BYTES);
-                tma_load_2d(dst, &tm_gu, &wbar[qi & 1u], col, static_cast<int>(row));
-                tma_load_2d(dst + GU_HALF_BYTES, &tm_gu, &wbar[qi & 1u], n + col, static_cast<int>(row));
+                if (PACKED) {
+                    tma_load_2d(dst, &tm_gu, &wbar[qi & 1u], 2 * col, static_cast<int>(row));
+                } else {
+                    tma_load_2d(dst, &tm_gu, &wbar[qi & 1u], col, static_cast<int>(row));
+                    tma_load_2d(dst + GU_HALF_BYTES, &tm_gu, &wbar[qi & 1u], n + col, static_cast<int>(row));
+                }
+            } else if (PACKED) {
+                tma_prefetch_2d(&tm_gu, 2 * col, static_cast<int>(row));
             } else {
                 tma_prefetch_2d(&tm_gu, col, static_cast<int>(row));
                 tma_prefetch_2d(&tm_gu, n + col, static_cast<int>(row));
@@ -490,36 +500,64 @@ rows_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     if (!ok) break;
                     uint32_t v[32];
                     tmem_ld32(taddr + c * 32, v);
-                    uint8_t* bp = wst + (q & 1u) * GU_BUF_BYTES + lane * (GU_BOX_COLS * 2);
-                    const int sw = (lane >> 1) & 3;
-                    uint4 gq[4], uq[4];
+                    if constexpr (PACKED) {
+                        uint8_t* bp = wst + (q & 1u) * GU_BUF_BYTES + lane * (GU_BOX_COLS * 4);
+                        const int sw = lane & 7;
+                        uint4 pq[8];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        gq[i] = *reinterpret_cast<const uint4*>(bp + ((i ^ sw) << 4));
-                        uq[i] = *reinterpret_cast<const uint4*>(bp + GU_HALF_BYTES + ((i ^ sw) << 4));
-                    }
-                    tmem_ld_wait();
+                        for (int i = 0; i < 8; ++i) pq[i] = *reinterpret_cast<const uint4*>(bp + ((i ^ sw) << 4));
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float gg[8], uu[8], dg[8], du[8];
-                        unpack8<T>(gq[i], gg);
-                        unpack8<T>(uq[i], uu);
+                        for (int i = 0; i < 8; ++i) {  // 4 activation columns = 8 interleaved values
+                            float gu[8], dd[8];
+                            unpack8<T>(pq[i], gu);
 #pragma unroll
-                        for (int t = 0; t < 8; ++t) {
-                            const float d = __uint_as_float(v[8 * i + t]);
-                            const float sg = fast_sigmoid(gg[t]);
-                            dg[t] = d * uu[t] * sg * (1.0f + gg[t] * (1.0f - sg));
-                            du[t] = d * gg[t] * sg;
+                            for (int t = 0; t < 4; ++t) {
+                                const float d = __uint_as_float(v[4 * i + t]);
+                                const float g = gu[2 * t], u = gu[2 * t + 1];
+                                const float sg = fast_sigmoid(g);
+                                dd[2 * t] = d * u * sg * (1.0f + g * (1.0f - sg));
+                                dd[2 * t + 1] = d * g * sg;
+                            }
+                            *reinterpret_cast<uint4*>(bp + ((i ^ sw) << 4)) = pack8<T>(dd);
                         }
-                        *reinterpret_cast<uint4*>(bp + ((i ^ sw) << 4)) = pack8<T>(dg);
-                        *reinterpret_cast<uint4*>(bp + GU_HALF_BYTES + ((i ^ sw) << 4)) = pack8<T>(du);
+                    } else {
+                        uint8_t* bp = wst + (q & 1u) * GU_BUF_BYTES + lane * (GU_BOX_COLS * 2);
+                        const int sw = (lane >> 1) & 3;
+                        uint4 gq[4], uq[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            gq[i] = *reinterpret_cast<const uint4*>(bp + ((i ^ sw) << 4));
+                            uq[i] = *reinterpret_cast<const uint4*>(bp + GU_HALF_BYTES + ((i ^ sw) << 4));
+                        }
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            float gg[8], uu[8], dg[8], du[8];
+                            unpack8<T>(gq[i], gg);
+                            unpack8<T>(uq[i], uu);
+#pragma unroll
+                            for (int t = 0; t < 8; ++t) {
+                                const float d = __uint_as_float(v[8 * i + t]);
+                                const float sg = fast_sigmoid(gg[t]);
+                                dg[t] = d * uu[t] * sg * (1.0f + gg[t] * (1.0f - sg));
+                                du[t] = d * gg[t] * sg;
+                            }
+                            *reinterpret_cast<uint4*>(bp + ((i ^ sw) << 4)) = pack8<T>(dg);
+                            *reinterpret_cast<uint4*>(bp + GU_HALF_BYTES + ((i ^ sw) << 4)) = pack8<T>(du);
+                        }
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
                         const uint8_t* src = wst + (q & 1u) * GU_BUF_BYTES;
-                        tma_store_2d(&tm_dgu, src, n0 + c * GU_BOX_COLS, static_cast<int>(row0));
-                        tma_store_2d(&tm_dgu, src + GU_HALF_BYTES, n + n0 + c * GU_BOX_COLS, static_cast<int>(row0));
+                        if (PACKED) {
+                            tma_store_2d(&tm_dgu, src, 2 * (n0 + c * GU_BOX_COLS), static_cast<int>(row0));
+                        } else {
+                            tma_store_2d(&tm_dgu, src, n0 + c * GU_BOX_COLS, static_cast<int>(row0));
+                            tma_store_2d(&tm_dgu, src + GU_HALF_BYTES, n + n0 + c * GU_BOX_COLS,
+                                         static_cast<int>(row0));
+                        }
                         tma_store_commit();
                         // this buffer takes the chunk after next as soon as the store has read it
                         --ahead;
@@ -892,7 +930,8 @@ static int set_smem2(K kernel, size_t bytes = SMEM2_BYTES) {
 template <typename T, int WL, int EPI>
 static int launch_rows2(const RowsGemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu,
                         const CUtensorMap& tdgu) {
-    constexpr bool STAGED = (EPI == EPI_DSWIGLU_STAGED || EPI == EPI_SWIGLU_STAGED);
+    constexpr bool STAGED =
+        (EPI == EPI_DSWIGLU_STAGED || EPI == EPI_SWIGLU_STAGED || EPI == EPI_DSWIGLU_PACKED_STAGED);
     constexpr size_t SMEM = STAGED ? SMEM2_STAGED_BYTES : SMEM2_BYTES;
     auto kernel = rows_gemm_tc2_kernel<T, WL, EPI>;
     int rc = set_smem2(kernel, SMEM);
@@ -922,6 +961,16 @@ static bool staged_dswiglu_maps(const RowsGemmArgs& g, CUtensorMap* tgu, CUtenso
            cached_map(tdgu, g.dtype, g.out, 2 * g.n, rows_cap, g.out_stride, 32, GU_BOX_COLS);
 }
 
+// The same for the interleaved layout: one box of 64 interleaved columns (128-byte swizzle) per 32 activation columns.
+static bool staged_dswiglu_packed_maps(const RowsGemmArgs& g, CUtensorMap* tgu, CUtensorMap* tdgu) {
+    if (g.epilogue != EPI_DSWIGLU_PACKED || g.w_layout != W_KN || !(tuning().dswiglu_staged & 1)) return false;
+    if (g.n % GU_BOX_COLS || g.num_experts > STAGED_MAX_EXPERTS) return false;
+    if (g.aux_stride % 8 || g.out_stride % 8 || !is_aligned16(g.aux) || !is_aligned16(g.out)) return false;
+    const uint64_t rows_cap = static_cast<uint64_t>(g.tile_cap) * XMA_ROW_PAD;
+    return cached_map(tgu, g.dtype, g.aux, 2 * g.n, rows_cap, g.aux_stride, 32, 64) &&
+           cached_map(tdgu, g.dtype, g.out, 2 * g.n, rows_cap, g.out_stride, 32, 64);
+}
+
 // The same for the SwiGLU forward (maps: gate|up [rows, n] and the activation [rows, n / 2], both written).
 static bool staged_swiglu_maps(const RowsGemmArgs& g, CUtensorMap* tgu, CUtensorMap* tact) {
     if (g.epilogue != EPI_SWIGLU || g.w_layout != W_NK || !(tuning().dswiglu_staged & 2)) return false;
@@ -943,6 +992,8 @@ static int rows_dispatch2(const RowsGemmArgs& g, const CUtensorMap& ta, const CU
         CUtensorMap tgu, tdgu;
         if (staged_dswiglu_maps(g, &tgu, &tdgu)) return launch_rows2<T, W_KN, EPI_DSWIGLU_STAGED>(g, ta, tb, tgu, tdgu);
         if (staged_swiglu_maps(g, &tgu, &tdgu)) return launch_rows2<T, W_NK, EPI_SWIGLU_STAGED>(g, ta, tb, tgu, tdgu);
+        if (staged_dswiglu_packed_maps(g, &tgu, &tdgu))
+            return launch_rows2<T, W_KN, EPI_DSWIGLU_PACKED_STAGED>(g, ta, tb, tgu, tdgu);
     }
 #define XMA_ROWS2_CASE(WL, EPI) \
     if (g.w_layout == WL && g.epilogue == EPI) return launch_rows2<T, WL, EPI>(g, ta, tb, ta, ta)

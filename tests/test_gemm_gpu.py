@@ -290,12 +290,21 @@ def test_staged_swiglu_epilogues_match_row_per_thread_epilogues(dtype, counts, k
             in_place = gu.clone()
             ops.grouped_gemm_rows_(dys, w2, _lib.W_KN, in_place, in_place, None, plan.tile_expert, plan.tile_prefix,
                                    kd, inter, _lib.EPI_DSWIGLU, TC_PAIR)
+            # the interleaved layout (gate, up, gate, up, ... along the columns)
+            gu_p = torch.full((plan.row_cap, 2 * inter), float("nan"), dtype=dtype, device="cuda")
+            act_p = torch.full((plan.row_cap, inter), float("nan"), dtype=dtype, device="cuda")
+            ops.grouped_gemm_rows_(a, w1, _lib.W_NK, act_p, gu_p, None, plan.tile_expert, plan.tile_prefix, kd,
+                                   2 * inter, _lib.EPI_SWIGLU_PACKED, TC_PAIR)
+            dgu_p = torch.full((plan.row_cap, 2 * inter), float("nan"), dtype=dtype, device="cuda")
+            ops.grouped_gemm_rows_(dys, w2, _lib.W_KN, dgu_p, gu_p, None, plan.tile_expert, plan.tile_prefix, kd, inter,
+                                   _lib.EPI_DSWIGLU_PACKED, TC_PAIR)
             torch.cuda.synchronize()
         finally:
             _lib.lib.xma_b200_tuning_set(_lib.TUNE_DSWIGLU_STAGED, previous)
         assert _lib.read_and_clear_device_status() == 0
-        got[staged] = (gu[:used], act[:used], dgu[:used], in_place[:used])
-    for x, y, what in zip(got[7], got[0], ("gate|up", "activation", "d gate|d up", "d gate|d up in place")):
+        got[staged] = (gu[:used], act[:used], dgu[:used], in_place[:used], dgu_p[:used])
+    for x, y, what in zip(got[7], got[0], ("gate|up", "activation", "d gate|d up", "d gate|d up in place",
+                                           "d gate, d up interleaved")):
         assert torch.isfinite(x.float()).all(), what
         assert torch.equal(x, y), what
     assert torch.equal(got[7][2], got[7][3])
