@@ -212,7 +212,7 @@ int xma_b200_grouped_gemm_choice(int kind, int dtype, int num_experts, int64_t t
  * instead of a fixed stride (0/1, default 1);
  * key 6: the SwiGLU epilogues of the CTA-pair kernel move their tiles through shared memory by TMA, 32 columns at a
  * time, instead of reading and writing them with one row per thread, when the activation width is a multiple of 32
- * and there are at most 192 experts: bit 0 = backward (gate|up read, d gate|d up written), bit 1 = forward
+ * and there are at most 192 experts: bit 0 = backward (gate|up read, d gate|d up written; both layouts), bit 1 = forward
  * (gate|up and the activation written; only for reductions shorter than 4096 unless bit 2 is set); default 3.
  * key 7: with the automatic choice (impl 0) a rows GEMM of large experts runs as two launches, the CTA-pair kernel
  * on the whole pairs of 128-row tiles of every expert and the one-CTA kernel on the last tile of the experts that
