@@ -160,6 +160,38 @@ def test_no_cpu_fallback():
     assert continuous_count(torch.zeros(8, dtype=torch.int32), 1).tolist() == [8]
 
 
+def test_no_cpu_fallback_in_the_later_functions():
+    """fused_residual_add_rmsnorm, load_balancing_loss, pack_sequence / unpack_sequence: the reference's argument
+    checks apply first, CPU tensors are refused loudly, a backend other than cuda raises ValueError."""
+    import xma
+    from xma.functional import fused_residual_add_rmsnorm, load_balancing_loss, pack_sequence, unpack_sequence
+
+    x, w = torch.zeros(4, 8), torch.ones(8)
+    with pytest.raises(RuntimeError):
+        fused_residual_add_rmsnorm(x, None, w, 1e-5)
+    with pytest.raises(AssertionError):
+        fused_residual_add_rmsnorm(torch.zeros(8), None, w, 1e-5)  # x should be 2D
+    with pytest.raises(ValueError):
+        fused_residual_add_rmsnorm(x, None, w, 1e-5, kernel_backend=xma.KernelBackend.triton)
+    with pytest.raises(RuntimeError):
+        load_balancing_loss(torch.zeros(4, 8), 2)
+    with pytest.raises(AssertionError):
+        load_balancing_loss(torch.zeros(4, 8), 9)  # top-k above the number of experts
+    padded, cu = torch.zeros(2, 4, 3), torch.tensor([0, 2, 5], dtype=torch.int32)
+    with pytest.raises(RuntimeError):
+        pack_sequence([padded], cu, 5)
+    with pytest.raises(RuntimeError):
+        unpack_sequence([torch.zeros(5, 3)], cu, 2, 4)
+    with pytest.raises(AssertionError):
+        pack_sequence([padded], cu, 5, "middle")
+    with pytest.raises(AssertionError):
+        pack_sequence(padded, cu, 5)  # a list or tuple of tensors, as in the reference
+    with pytest.raises(AssertionError):
+        unpack_sequence([torch.zeros(5, 3)], cu, 3, 4)  # batch_size must match cu_seqlens
+    with pytest.raises(ValueError):
+        pack_sequence([padded], cu, 5, kernel_backend=xma.KernelBackend.torch)
+
+
 def test_state_dict_layout_matches_reference():
     """Parameter/buffer names and shapes of xma/layers/moe/__init__.py:22-43,122-160."""
     from xma.layers import MoE, SwiGLU
