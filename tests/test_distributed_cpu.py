@@ -185,6 +185,18 @@ def _peer_worker(rank: int, world: int, port: int, results) -> None:
         assert ex._held == held  # fits: nothing reallocated
         ex.ensure(385, 10)
         assert ex.recv_cap == 512 and ex.home_cap == 256 and ex._held != held
+        # 5. the expert groups of the pipelined exchange: contiguous groups of this rank's experts with their padded
+        #    row ranges, at most one group per expert, one group when nothing is known about the rows per expert
+        ep.ops.ep_plan_ = lambda *args, **kwargs: None
+        counts = torch.zeros(world, 4 * world, dtype=torch.int32)
+        padded = [128, 256, 128, 512]
+        route = ep._PeerRoute(counts, rank, 1024, ex, local_padded=padded, parts=2)
+        assert route.parts == [(0, 2, 0, 384), (2, 4, 384, 1024)]
+        assert (route.e_local, route.tile_expert.numel(), route.send_delta.numel()) == (4, 1024 // 128 + 4, 4 * world)
+        route = ep._PeerRoute(counts, rank, 1024, ex, local_padded=padded, parts=9)
+        assert route.parts == [(0, 1, 0, 128), (1, 2, 128, 384), (2, 3, 384, 512), (3, 4, 512, 1024)]
+        assert ep._PeerRoute(counts, rank, 1024, ex, local_padded=padded, parts=1).parts == [(0, 4, 0, 1024)]
+        assert ep._PeerRoute(counts, rank, 1024, ex, local_padded=None, parts=3).parts == [(0, 4, 0, 1024)]
         ex.close()
         assert ex._held == [] and ex.recv_rows is None
         results[rank] = "ok"
