@@ -150,3 +150,31 @@ def test_sequence_packing_oracle_matches_reference(name, side):
     assert np.array_equal(sp.pack_backward(inp["dpacked"].numpy(), cu, S, side), gold[key + "pack_dx"])
     assert np.array_equal(sp.unpack(inp["p"].numpy(), cu, S, side), gold[key + "unpack"])
     assert np.array_equal(sp.unpack_backward(inp["dpadded"].numpy(), cu, side), gold[key + "unpack_dx"])
+
+
+def test_sequence_packing_oracle_round_trips():
+    """Size-independent properties of the restatement on random ragged batches: unpacking what was packed gives the
+    input with its padding zeroed, packing what was unpacked gives the packed input back, and the two padding sides
+    differ only in where a sequence sits in its row."""
+    from oracle import sequence_packing_oracle as sp
+
+    rng = np.random.RandomState(11)
+    for _ in range(25):
+        B, S = int(rng.randint(1, 7)), int(rng.randint(1, 12))
+        lens = rng.randint(0, S + 1, size=B)
+        cu = [0] + np.cumsum(lens).tolist()
+        trailing = tuple(rng.randint(1, 4, size=int(rng.randint(0, 3))).tolist())
+        x = rng.standard_normal((B, S, *trailing)).astype(np.float32)
+        p = rng.standard_normal((cu[-1], *trailing)).astype(np.float32)
+        for side in ("left", "right"):
+            packed = sp.pack(x, cu, side)
+            assert packed.shape == (cu[-1], *trailing)
+            back = sp.unpack(packed, cu, S, side)
+            pos = np.arange(S)[None, :]
+            valid = (pos >= S - lens[:, None]) if side == "left" else (pos < lens[:, None])
+            mask = valid.reshape(B, S, *([1] * len(trailing)))
+            assert np.array_equal(back, np.where(mask, x, 0))
+            assert np.array_equal(sp.pack(sp.unpack(p, cu, S, side), cu, side), p)
+        left, right = sp.unpack(p, cu, S, "left"), sp.unpack(p, cu, S, "right")
+        for b in range(B):
+            assert np.array_equal(left[b, S - lens[b]:], right[b, :lens[b]])
